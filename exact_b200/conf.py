@@ -1,0 +1,50 @@
+"""Global quantisation config: the same mutable singleton as the reference's exact/exact/conf.py:1-24,
+plus the explicit noise key the B200 kernels use instead of torch's global CUDA generator."""
+
+
+class QuantizationConfig:
+    def __init__(self):
+        # --- fields of the reference (conf.py:3-21) ---
+        self.compress_activation = True
+        self.activation_compression_bits = [2]
+        self.initial_bits = 8
+        self.stochastic = True
+        self.use_gradient = False
+        self.simulate = False
+        self.enable_quantized_bn = True
+        self.kept_frac = 1.0
+        self.single_precision = True
+        self.dropout2 = False
+        self.empty_cache_threshold = None
+        self.swap = False
+        self.amp = False
+        self.debug_memory_op_forward = False
+        self.debug_memory_op_backward = False
+        self.debug_remove_bn = False
+        self.debug_remove_relu = False
+        self.debug_remove_dropout = False
+        # --- additions ---
+        # Philox key and running offset for stochastic rounding, dropout and projection signs.  Every
+        # call that draws noise takes the next offset, so a run is reproduced by (seed, call order).
+        self.seed = 0
+        self._offset = 0
+        # Global index of this process's first node row (multiple of 8) when rows are sharded across
+        # GPUs: keys the noise by global row so that shards reproduce the single-GPU stream.
+        self.row_offset = 0
+        # Fuse projection + quantise + pack into one kernel when the shape allows it.
+        self.fused_rp = True
+        # Do not produce compressed copies that no backward formula reads (the SpMM's dense operand
+        # when edge values need no gradient).  Outputs and gradients are unaffected.
+        self.skip_dead_saves = True
+
+    def manual_seed(self, seed):
+        self.seed = int(seed)
+        self._offset = 0
+
+    def next_offset(self):
+        off = self._offset
+        self._offset += 1
+        return off
+
+
+config = QuantizationConfig()

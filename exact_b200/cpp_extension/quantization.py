@@ -1,0 +1,199 @@
+"""Stand-in for the reference's `exact.cpp_extension.quantization` module
+(exact/exact/cpp_extension/quantization.cc:137-143): same function names and argument meaning, each
+call forwarded to libexact_b200.so through the C ABI."""
+import torch
+
+from .. import _lib
+from ..conf import config
+
+
+def _check_cuda_float(t, name, dim=None, dtypes=(torch.float32,)):
+    # ext_common.h:2-32: CUDA, contiguous, rank, dtype
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor!")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous!")
+    if dim is not None and t.dim() != dim:
+        raise RuntimeError(f"The dimension of {name} is not correct!")
+    if t.dtype not in dtypes:
+        raise RuntimeError(f"The type of {name} is not correct!")
+
+
+def _dt(t):
+    return _lib.DTYPE_F32 if t.dtype == torch.float32 else _lib.DTYPE_BF16
+
+
+def packed_numel(N, D, bits):
+    """Elements of the int8 tensor the reference returns: ceil(N/(8/bits))*D + 1
+    (quantization_cuda_kernel.cu:110-113)."""
+    return int(_lib.load().exact_packed_bytes(N, D, bits)) + 1
+
+
+def quantize_pack(data, bits, noise=None, seed=None, offset=None, row_offset=None, want_f32_stats=False):
+    """Fused row statistics + stochastic quantise + bit-pack.  One kernel, one read of `data`.
+    -> (packed int8 [G*D+1], scale bf16 [N], min bf16 [N][, scale f32, min f32])."""
+    _check_cuda_float(data, "data", 2, (torch.float32, torch.bfloat16))
+    if bits not in (1, 2, 4, 8):
+        raise RuntimeError("bits must be 1, 2, 4 or 8")
+    N, D = data.shape
+    if noise is not None:
+        _check_cuda_float(noise, "noise", 2)
+        if tuple(noise.shape) != (N, D):
+            raise RuntimeError("noise must have the shape of data")
+    lib = _lib.load()
+    packed = torch.empty(packed_numel(N, D, bits), dtype=torch.int8, device=data.device)
+    scale = torch.empty(N, dtype=torch.bfloat16, device=data.device)
+    mn = torch.empty(N, dtype=torch.bfloat16, device=data.device)
+    sf = mf = None
+    if want_f32_stats:
+        sf = torch.empty(N, dtype=torch.float32, device=data.device)
+        mf = torch.empty(N, dtype=torch.float32, device=data.device)
+    if noise is None:
+        seed = config.seed if seed is None else seed
+        offset = config.next_offset() if offset is None else offset
+    else:
+        seed = offset = 0
+    row_offset = config.row_offset if row_offset is None else row_offset
+    rc = lib.exact_quantize_pack(_lib.ptr(data), _dt(data), N, D, bits, _lib.ptr(noise), seed, offset,
+                                 row_offset, _lib.ptr(packed), _lib.ptr(scale), _lib.ptr(mn),
+                                 _lib.ptr(sf), _lib.ptr(mf), _lib.stream_ptr())
+    _lib.check(rc, "exact_quantize_pack")
+    if want_f32_stats:
+        return packed, scale, mn, sf, mf
+    return packed, scale, mn
+
+
+def pack_single_precision(data, min, max, scale, bits, stochastic, noise=None, seed=None, offset=None,
+                          row_offset=None):
+    """quantization.cc:37-48.  `max` is accepted and ignored, as in the reference kernel; `stochastic`
+    must be true (quantization_cuda_kernel.cu:123).  `noise` (optional, [N,D] fp32) replaces the
+    Philox draw."""
+    _check_cuda_float(data, "data", 2, (torch.float32, torch.bfloat16))
+    _check_cuda_float(min, "min", 1)
+    _check_cuda_float(max, "max", 1)
+    _check_cuda_float(scale, "scale", 1)
+    if 8 % bits != 0 or bits not in (1, 2, 4, 8):
+        raise RuntimeError("bits must be 1, 2, 4 or 8")
+    if not stochastic:
+        raise RuntimeError("stochastic must be true")
+    N, D = data.shape
+    packed = torch.empty(packed_numel(N, D, bits), dtype=torch.int8, device=data.device)
+    if noise is None:
+        seed = config.seed if seed is None else seed
+        offset = config.next_offset() if offset is None else offset
+    else:
+        seed = offset = 0
+    row_offset = config.row_offset if row_offset is None else row_offset
+    rc = _lib.load().exact_pack_single_precision(
+        _lib.ptr(data), _dt(data), _lib.ptr(min), _lib.ptr(scale), N, D, bits, _lib.ptr(noise), seed,
+        offset, row_offset, _lib.ptr(packed), _lib.stream_ptr())
+    _lib.check(rc, "exact_pack_single_precision")
+    return packed
+
+
+def unpack_single_precision(data, bits, scale, min, N, group_size):
+    """quantization.cc:50-62.  scale/min may be fp32 (reference signature) or bf16 (the stored
+    statistics; widening happens in the kernel).  Returns fp32 [N, group_size]."""
+    if not data.is_cuda or not data.is_contiguous() or data.dim() != 1 or data.dtype != torch.int8:
+        raise RuntimeError("The type of data is not correct!")
+    _check_cuda_float(scale, "scale", 1, (torch.float32, torch.bfloat16))
+    _check_cuda_float(min, "min", 1, (torch.float32, torch.bfloat16))
+    if scale.dtype != min.dtype:
+        raise RuntimeError("scale and min must have the same dtype")
+    if bits not in (1, 2, 4, 8):
+        raise RuntimeError("bits must be 1, 2, 4 or 8")
+    lib = _lib.load()
+    need = int(lib.exact_packed_bytes(N, group_size, bits))
+    if data.numel() < need or scale.numel() < N or min.numel() < N:
+        raise RuntimeError("packed stream or statistics shorter than N x group_size requires")
+    out = torch.empty((N, group_size), dtype=torch.float32, device=data.device)
+    rc = lib.exact_unpack_single_precision(_lib.ptr(data), bits, _lib.ptr(scale), _lib.ptr(min), _dt(scale),
+                                           N, group_size, _lib.ptr(out), _lib.stream_ptr())
+    _lib.check(rc, "exact_unpack_single_precision")
+    return out
+
+
+class _ActQuantizedReLU(torch.autograd.Function):
+    """quantization.cc:66-79."""
+
+    @staticmethod
+    def forward(ctx, input):
+        lib = _lib.load()
+        n = input.numel()
+        out = torch.empty_like(input)
+        mask = torch.empty(int(lib.exact_mask_words(n)), dtype=torch.int32, device=input.device)
+        _lib.check(lib.exact_act_quantized_relu_forward(_lib.ptr(input), n, _lib.ptr(out), _lib.ptr(mask),
+                                                        _lib.stream_ptr()), "exact_act_quantized_relu_forward")
+        ctx.save_for_backward(mask)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (mask,) = ctx.saved_tensors
+        grad_output = grad_output.contiguous()
+        gin = torch.empty_like(grad_output)
+        lib = _lib.load()
+        _lib.check(lib.exact_act_quantized_relu_backward(_lib.ptr(grad_output), _lib.ptr(mask), grad_output.numel(),
+                                                         _lib.ptr(gin), _lib.stream_ptr()),
+                   "exact_act_quantized_relu_backward")
+        return gin
+
+
+def act_quantized_relu(input):
+    """quantization.cc:81-84."""
+    _check_cuda_float(input, "input")
+    return _ActQuantizedReLU.apply(input)
+
+
+class _ActQuantizedDropout(torch.autograd.Function):
+    """quantization.cc:111-129."""
+
+    @staticmethod
+    def forward(ctx, input, p, uniforms):
+        lib = _lib.load()
+        n = input.numel()
+        out = torch.empty_like(input)
+        mask = torch.empty(int(lib.exact_mask_words(n)), dtype=torch.int32, device=input.device)
+        if uniforms is None:
+            seed, offset = config.seed, config.next_offset()
+        else:
+            seed = offset = 0
+        # rows are the sharded dimension: element 0 of this shard is global element row_offset * row_len
+        index_offset = config.row_offset * (n // input.shape[0]) if (input.dim() >= 2 and n) else 0
+        _lib.check(lib.exact_act_quantized_dropout_forward(_lib.ptr(input), n, p, _lib.ptr(uniforms), seed, offset,
+                                                           index_offset, _lib.ptr(out), _lib.ptr(mask),
+                                                           _lib.stream_ptr()),
+                   "exact_act_quantized_dropout_forward")
+        ctx.save_for_backward(mask)
+        ctx.p = p
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (mask,) = ctx.saved_tensors
+        grad_output = grad_output.contiguous()
+        gin = torch.empty_like(grad_output)
+        lib = _lib.load()
+        _lib.check(lib.exact_act_quantized_dropout_backward(_lib.ptr(grad_output), _lib.ptr(mask),
+                                                            grad_output.numel(), ctx.p, _lib.ptr(gin),
+                                                            _lib.stream_ptr()),
+                   "exact_act_quantized_dropout_backward")
+        return gin, None, None
+
+
+def act_quantized_dropout(input, p, train, uniforms=None):
+    """quantization.cc:131-134; eval mode returns the input tensor itself (quantization.cc:115-117).
+    `uniforms` (optional, fp32, shape of input) replaces the Philox draw."""
+    _check_cuda_float(input, "input")
+    if not train:
+        return input
+    if uniforms is not None:
+        _check_cuda_float(uniforms, "uniforms")
+        if uniforms.numel() != input.numel():
+            raise RuntimeError("uniforms must have the shape of input")
+    return _ActQuantizedDropout.apply(input, float(p), uniforms)
+
+
+def act_quantized_leaky_relu(input, slope):
+    raise NotImplementedError("act_quantized_leaky_relu serves only the GAT layers, which are outside the "
+                              "GCN/GraphSAGE path this library accelerates")

@@ -1,0 +1,79 @@
+"""Stand-in for the reference's `exact.cpp_extension.spmm` module (exact/exact/cpp_extension/spmm.cc:243-252):
+spmm_{sum,mean}_{fw,bw} with the reference's argument lists, forwarded to the C ABI."""
+import torch
+
+from .. import _lib
+
+
+def _spmm(rowptr, col, value, mat, reduce):
+    """spmm.cc:12-18 -> spmm_cuda.cu:106-170."""
+    if not rowptr.is_cuda or not col.is_cuda or not mat.is_cuda:
+        raise RuntimeError("rowptr, col and mat must be CUDA tensors")
+    if rowptr.dim() != 1 or col.dim() != 1:
+        raise RuntimeError("Input mismatch")
+    if value is not None and (value.dim() != 1 or value.size(0) != col.size(0)):
+        raise RuntimeError("Input mismatch")
+    if mat.dim() != 2:
+        raise RuntimeError("mat must be [N, K] (batched operands are not used by the GCN/SAGE layers)")
+    if mat.dtype != torch.float32:
+        raise RuntimeError("mat must be float32")
+    if rowptr.dtype != col.dtype or col.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("rowptr and col must both be int32 or both int64")
+    mat = mat.contiguous()
+    rowptr = rowptr.contiguous()
+    col = col.contiguous()
+    if value is not None:
+        value = value.detach().to(torch.float32).contiguous()
+    M = rowptr.numel() - 1
+    K = mat.size(1)
+    out = torch.empty((M, K), dtype=mat.dtype, device=mat.device)
+    rc = _lib.load().exact_spmm(_lib.ptr(rowptr), _lib.ptr(col), 4 if col.dtype == torch.int32 else 8,
+                                _lib.ptr(value), _lib.ptr(mat), M, K, _lib.REDUCE[reduce], _lib.ptr(out),
+                                _lib.stream_ptr())
+    _lib.check(rc, "exact_spmm")
+    return out
+
+
+def spmm_sum_fw(row, rowptr, col, value, colptr, csr2csc, mat):
+    """spmm.cc:31-55."""
+    return _spmm(rowptr, col, value, mat, "sum")
+
+
+def spmm_mean_fw(row, rowptr, col, value, rowcount, colptr, csr2csc, mat):
+    """spmm.cc:84-113."""
+    return _spmm(rowptr, col, value, mat, "mean")
+
+
+def _value_grad_unsupported():
+    raise NotImplementedError("gradient with respect to edge values (spmm_value_bw) is not part of the "
+                              "GCN/GraphSAGE path: their adjacency values never require grad")
+
+
+def spmm_sum_bw(row, rowptr, col, value, colptr, csr2csc, mat, grad_out, has_value, value_requires_grad,
+                mat_requires_grad, transposed=None):
+    """spmm.cc:57-79.  `transposed` = (colptr, row[csr2csc], value[csr2csc]) when the caller caches it."""
+    if has_value and value_requires_grad:
+        _value_grad_unsupported()
+    grad_mat = None
+    if mat_requires_grad:
+        if transposed is None:
+            w = value.index_select(0, csr2csc) if has_value else None
+            transposed = (colptr, row.index_select(0, csr2csc), w)
+        grad_mat = _spmm(transposed[0], transposed[1], transposed[2], grad_out, "sum")
+    return None, grad_mat
+
+
+def spmm_mean_bw(row, rowptr, col, value, rowcount, colptr, csr2csc, mat, grad_out, has_value,
+                 value_requires_grad, mat_requires_grad, transposed=None):
+    """spmm.cc:115-139."""
+    if has_value and value_requires_grad:
+        _value_grad_unsupported()
+    grad_mat = None
+    if mat_requires_grad:
+        if transposed is None:
+            row_t = row.index_select(0, csr2csc)
+            cnt = rowcount.to(grad_out.dtype).index_select(0, row_t.to(torch.int64)).clamp_(1)
+            w = value.index_select(0, csr2csc).div(cnt) if has_value else cnt.pow_(-1)
+            transposed = (colptr, row_t, w)
+        grad_mat = _spmm(transposed[0], transposed[1], transposed[2], grad_out, "sum")
+    return None, grad_mat

@@ -1,0 +1,195 @@
+// 1-bit-mask activations: ReLU and dropout that keep one bit per element for backward.
+//
+// Replaces quantization.act_quantized_relu / act_quantized_dropout
+// (exact/exact/cpp_extension/quantization.cc:66-84, 111-134; kernels
+// quantization_cuda_kernel.cu:237-331, 442-594).
+//
+// A warp handles 128 consecutive elements per step: each lane loads one float4, and four
+// __ballot_sync calls turn the 128 predicates into four mask words.  Word 4*c + j, bit l holds
+// element 128*c + 4*l + j.  The layout is private: the reference's mask never leaves its extension
+// either (quantization.cc:71,92,119), only outputs and gradients are observable.
+#include "common.cuh"
+#include "exact_b200.h"
+
+namespace exb {
+
+enum MaskOp { OP_RELU = 0, OP_DROPOUT = 1 };
+
+struct MaskParams {
+  const float* x;       // forward input or grad_out
+  const float* u;       // supplied uniforms (dropout forward) or null
+  float* out;           // output or grad_in
+  uint32_t* mask;
+  long long n;
+  float p;              // dropout probability
+  float pinv;           // float(1 / (1 - p))
+  float p1m;            // float(1 - p)
+  uint32_t off_lo, off_hi;
+  unsigned long long q0;  // Philox block index of element 0 (global element index / 4)
+  PhiloxKey key;
+};
+
+template <bool ALIGNED>
+__device__ __forceinline__ void load4(const float* base, long long i, long long n, float (&v)[4]) {
+  if (ALIGNED && i + 4 <= n) {
+    const float4 t = __ldcs(reinterpret_cast<const float4*>(base + i));
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; j++) v[j] = (i + j < n) ? __ldcs(base + i + j) : 0.f;
+  }
+}
+template <bool ALIGNED>
+__device__ __forceinline__ void store4(float* base, long long i, long long n, const float (&v)[4]) {
+  if (ALIGNED && i + 4 <= n) {
+    __stcs(reinterpret_cast<float4*>(base + i), make_float4(v[0], v[1], v[2], v[3]));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+      if (i + j < n) __stcs(base + i + j, v[j]);
+  }
+}
+
+template <int OP, bool ALIGNED>
+__global__ void __launch_bounds__(256) mask_forward_kernel(const __grid_constant__ MaskParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long nchunks = (p.n + 127) >> 7;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long c = warp0; c < nchunks; c += nwarps) {
+    const long long i = (c << 7) + 4 * lane;
+    float v[4], o[4];
+    bool keep[4];
+    load4<ALIGNED>(p.x, i, p.n, v);
+    if (OP == OP_RELU) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        keep[j] = v[j] > 0.f;           // quantization_cuda_kernel.cu:253
+        o[j] = keep[j] ? v[j] : 0.f;
+      }
+    } else {
+      float u[4];
+      if (p.u != nullptr) {
+        load4<ALIGNED>(p.u, i, p.n, u);
+      } else {
+        const unsigned long long q = p.q0 + (unsigned long long)((c << 5) + lane);  // global element index / 4
+        uint32_t w[4];
+        philox4x32_10((uint32_t)q, (uint32_t)(q >> 32), p.off_lo, p.off_hi, p.key, w);
+#pragma unroll
+        for (int j = 0; j < 4; j++) u[j] = u32_to_unit(w[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        keep[j] = (u[j] > p.p) && (i + j < p.n);  // quantization_cuda_kernel.cu:466-469
+        // quantization_cuda_kernel.cu:490: src * keep * pinv, two fp32 multiplies
+        o[j] = __fmul_rn(__fmul_rn(v[j], keep[j] ? 1.f : 0.f), p.pinv);
+      }
+    }
+    store4<ALIGNED>(p.out, i, p.n, o);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const uint32_t w = __ballot_sync(0xffffffffu, keep[j]);
+      if (lane == j) p.mask[(c << 2) + j] = w;
+    }
+  }
+}
+
+template <int OP, bool ALIGNED>
+__global__ void __launch_bounds__(256) mask_backward_kernel(const __grid_constant__ MaskParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long nchunks = (p.n + 127) >> 7;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long c = warp0; c < nchunks; c += nwarps) {
+    const long long i = (c << 7) + 4 * lane;
+    float g[4], o[4];
+    load4<ALIGNED>(p.x, i, p.n, g);
+    const uint4 mw = __ldg(reinterpret_cast<const uint4*>(p.mask) + c);
+    const uint32_t m[4] = {mw.x, mw.y, mw.z, mw.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const bool keep = (m[j] >> lane) & 1u;
+      if (OP == OP_RELU) {
+        o[j] = keep ? g[j] : 0.f;                      // quantization_cuda_kernel.cu:303-308
+      } else {
+        o[j] = keep ? __fdiv_rn(g[j], p.p1m) : 0.f;    // quantization_cuda_kernel.cu:565-569
+      }
+    }
+    store4<ALIGNED>(p.out, i, p.n, o);
+  }
+}
+
+static bool aligned16(const void* a) { return (reinterpret_cast<uintptr_t>(a) & 15) == 0; }
+
+template <int OP>
+static int launch_mask(bool forward, const MaskParams& p, cudaStream_t st) {
+  if (p.n == 0) return EXB_OK;
+  EXB_REQUIRE(p.x && p.out && p.mask, "mask activation: null pointer");
+  EXB_REQUIRE(aligned16(p.mask), "mask activation: mask must be 16-byte aligned");
+  const bool al = aligned16(p.x) && aligned16(p.out) && (p.u == nullptr || aligned16(p.u));
+  const long long nchunks = (p.n + 127) >> 7;
+  long long blocks = (nchunks + 7) / 8;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (forward) {
+    if (al) mask_forward_kernel<OP, true><<<(int)blocks, 256, 0, st>>>(p);
+    else mask_forward_kernel<OP, false><<<(int)blocks, 256, 0, st>>>(p);
+  } else {
+    if (al) mask_backward_kernel<OP, true><<<(int)blocks, 256, 0, st>>>(p);
+    else mask_backward_kernel<OP, false><<<(int)blocks, 256, 0, st>>>(p);
+  }
+  EXB_CUDA_OK(cudaGetLastError());
+  return EXB_OK;
+}
+
+}  // namespace exb
+
+using namespace exb;
+
+extern "C" {
+
+int64_t exact_mask_words(int64_t n) { return n <= 0 ? 0 : ((n + 127) / 128) * 4; }
+
+int exact_act_quantized_relu_forward(const float* x, int64_t n, float* out, uint32_t* mask, void* stream) {
+  EXB_REQUIRE(n >= 0, "relu: negative size");
+  MaskParams p{};
+  p.x = x; p.out = out; p.mask = mask; p.n = n;
+  return launch_mask<OP_RELU>(true, p, (cudaStream_t)stream);
+}
+
+int exact_act_quantized_relu_backward(const float* grad_out, const uint32_t* mask, int64_t n,
+                                      float* grad_in, void* stream) {
+  EXB_REQUIRE(n >= 0, "relu: negative size");
+  MaskParams p{};
+  p.x = grad_out; p.out = grad_in; p.mask = const_cast<uint32_t*>(mask); p.n = n;
+  return launch_mask<OP_RELU>(false, p, (cudaStream_t)stream);
+}
+
+int exact_act_quantized_dropout_forward(const float* x, int64_t n, float prob, const float* uniforms,
+                                        uint64_t seed, uint64_t offset, int64_t index_offset, float* out,
+                                        uint32_t* mask, void* stream) {
+  EXB_REQUIRE(n >= 0, "dropout: negative size");
+  EXB_REQUIRE(index_offset >= 0 && index_offset % 4 == 0, "dropout: index_offset must be a non-negative multiple of 4");
+  EXB_REQUIRE(prob >= 0.f && prob <= 1.f, "dropout: p must be in [0, 1] (got %f)", (double)prob);
+  MaskParams p{};
+  p.x = x; p.u = uniforms; p.out = out; p.mask = mask; p.n = n;
+  p.p = prob;
+  p.pinv = (float)(1.0 / (1.0 - (double)prob));  // quantization_cuda_kernel.cu:455
+  p.p1m = (float)(1.0 - (double)prob);
+  p.off_lo = (uint32_t)offset; p.off_hi = (uint32_t)(offset >> 32);
+  p.q0 = (unsigned long long)index_offset >> 2;
+  p.key = make_philox_key(seed);
+  return launch_mask<OP_DROPOUT>(true, p, (cudaStream_t)stream);
+}
+
+int exact_act_quantized_dropout_backward(const float* grad_out, const uint32_t* mask, int64_t n,
+                                         float prob, float* grad_in, void* stream) {
+  EXB_REQUIRE(n >= 0, "dropout: negative size");
+  MaskParams p{};
+  p.x = grad_out; p.out = grad_in; p.mask = const_cast<uint32_t*>(mask); p.n = n;
+  p.p = prob;
+  p.p1m = (float)(1.0 - (double)prob);  // quantization.cc:120
+  return launch_mask<OP_DROPOUT>(false, p, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,120 @@
+/*
+ * exact_b200.h -- C ABI of libexact_b200.so: the activation-compression hot path of EXACT
+ * (zirui-ray-liu/Exact) as hand-written CUDA kernels for NVIDIA B200 (sm_100a).
+ *
+ * The reference exposes this path as pybind11 torch-extension functions taking at::Tensor.  Each
+ * entry point below names the reference function it stands in for (paths relative to the reference
+ * checkout) and takes the same operands as plain device pointers and sizes.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer on the current CUDA device unless stated otherwise.
+ *   - Nothing is allocated or freed here: the caller owns inputs, outputs and scratch.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  Kernels are only
+ *     enqueued; the call does not synchronise.
+ *   - Return value 0 = success.  Non-zero: 1 bad argument, 2 CUDA runtime error, 3 unsupported
+ *     shape, 4 device-side status.  exact_last_error() gives the message (thread-local).
+ *   - Tensors are dense row-major ("contiguous"), as the reference requires
+ *     (exact/exact/cpp_extension/ext_common.h:2-32).
+ */
+#ifndef EXACT_B200_H_
+#define EXACT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define EXACT_API __attribute__((visibility("default")))
+#else
+#define EXACT_API
+#endif
+
+enum { EXACT_DTYPE_F32 = 0, EXACT_DTYPE_BF16 = 1 };
+enum { EXACT_REDUCE_SUM = 0, EXACT_REDUCE_MEAN = 1 };
+
+/* Library version (major * 100 + minor) and the last error message of the calling thread. */
+EXACT_API int exact_version(void);
+EXACT_API const char* exact_last_error(void);
+
+/* Bytes of the packed stream for an [N, D] activation at `bits` per element: ceil(N / (8/bits)) * D.
+ * The reference allocates one more byte and never writes it (quantization_cuda_kernel.cu:110-113);
+ * callers that mirror its tensor shape allocate exact_packed_bytes() + 1. */
+EXACT_API int64_t exact_packed_bytes(int64_t N, int64_t D, int bits);
+
+/* Fused quantize_activation.  Replaces the chain exact/exact/ops.py:69-83 -> ops.py:61-66 (row
+ * min/max) -> ops.py:36-40 (scale = reciprocal(max - min) * (2^bits - 1)) ->
+ * quantization.pack_single_precision (quantization.cc:37-48, quantization_cuda_kernel.cu:63-155) ->
+ * ops.py:80-81 (statistics stored as bf16), in one pass over x.
+ *   x          [N, D], fp32 or bf16 (dtype = EXACT_DTYPE_*); bf16 is widened to fp32 first
+ *   noise      [N, D] fp32 uniform noise added before rounding, or NULL to draw Philox4x32-10 noise
+ *              keyed by (seed, offset, global row, column)
+ *   row_offset global index of row 0 (multiple of 8) so that row shards draw the noise of the whole
+ *   packed     [exact_packed_bytes(N, D, bits)] out
+ *   scale_bf16, min_bf16  [N] bf16 bit patterns out (either may be NULL)
+ *   scale_f32, min_f32    [N] the fp32 statistics the codes were computed with (either may be NULL) */
+EXACT_API int exact_quantize_pack(const void* x, int dtype, int64_t N, int64_t D, int bits,
+                                  const float* noise, uint64_t seed, uint64_t offset,
+                                  int64_t row_offset, uint8_t* packed, uint16_t* scale_bf16,
+                                  uint16_t* min_bf16, float* scale_f32, float* min_f32, void* stream);
+
+/* quantization.pack_single_precision(data, min, max, scale, bits, stochastic)
+ * (quantization.cc:37-48; kernel quantization_cuda_kernel.cu:63-94) with caller-computed fp32 row
+ * statistics.  `max` is unused by the reference kernel and is not taken.  Noise as above. */
+EXACT_API int exact_pack_single_precision(const void* data, int dtype, const float* min,
+                                          const float* scale, int64_t N, int64_t D, int bits,
+                                          const float* noise, uint64_t seed, uint64_t offset,
+                                          int64_t row_offset, uint8_t* packed, void* stream);
+
+/* quantization.unpack_single_precision(data, bits, scale, min, N, group_size)
+ * (quantization.cc:50-62; kernel quantization_cuda_kernel.cu:158-185): out[n, d] = code / scale[n] +
+ * min[n].  scale/min are fp32 (the reference signature) or bf16 bit patterns (stats_dtype), which
+ * folds the widening of exact/exact/ops.py:94-96 into the kernel.  out is [N, D] fp32. */
+EXACT_API int exact_unpack_single_precision(const uint8_t* packed, int bits, const void* scale,
+                                            const void* min, int stats_dtype, int64_t N, int64_t D,
+                                            float* out, void* stream);
+
+/* Number of 32-bit mask words the 1-bit-mask activations need for n elements. */
+EXACT_API int64_t exact_mask_words(int64_t n);
+
+/* quantization.act_quantized_relu forward / backward (quantization.cc:66-84;
+ * quantization_cuda_kernel.cu:237-331): out = x > 0 ? x : 0 and a 1-bit mask; grad_in = bit ?
+ * grad_out : 0.  The mask layout is private to this library (the reference's never leaves its
+ * extension either). */
+EXACT_API int exact_act_quantized_relu_forward(const float* x, int64_t n, float* out, uint32_t* mask,
+                                               void* stream);
+EXACT_API int exact_act_quantized_relu_backward(const float* grad_out, const uint32_t* mask, int64_t n,
+                                                float* grad_in, void* stream);
+
+/* quantization.act_quantized_dropout forward / backward (quantization.cc:111-134;
+ * quantization_cuda_kernel.cu:442-594): keep = u > p, out = (x * keep) * float(1 / (1 - p));
+ * grad_in = keep ? grad_out / float(1 - p) : 0.  `uniforms` [n] supplies u, or NULL draws
+ * Philox4x32-10 uniforms in (0, 1] keyed by (seed, offset, (index_offset + element index) / 4);
+ * index_offset (multiple of 4) is the global index of element 0 when rows are sharded. */
+EXACT_API int exact_act_quantized_dropout_forward(const float* x, int64_t n, float p,
+                                                  const float* uniforms, uint64_t seed, uint64_t offset,
+                                                  int64_t index_offset, float* out, uint32_t* mask,
+                                                  void* stream);
+EXACT_API int exact_act_quantized_dropout_backward(const float* grad_out, const uint32_t* mask,
+                                                   int64_t n, float p, float* grad_in, void* stream);
+
+/* spmm.spmm_sum_fw / spmm_mean_fw (spmm.cc:31-55, 84-113 -> spmm_cuda.cu:27-170, reducer.cuh):
+ * out[r, :] = reduce_{e in row r} value[e] * mat[col[e], :].  rowptr [M+1] and col [nnz] are int32
+ * (idx_bytes = 4) or int64 (8); value [nnz] fp32 or NULL (all ones); mat [*, K]; out [M, K].
+ * Mean divides by max(row length, 1).  The gradient with respect to mat (spmm.cc:57-79, 115-139) is
+ * this same call on the transposed structure with reduce = sum. */
+EXACT_API int exact_spmm(const void* rowptr, const void* col, int idx_bytes, const float* value,
+                         const float* mat, int64_t M, int64_t K, int reduce, float* out, void* stream);
+
+/* The random matrix of input2rp (exact/exact/ops.py:107-118, gen_rad_mat at ops.py:112-114):
+ * out [D, k] row-major fp32, entries +-1/sqrt(k).  Sign i (row-major index) is bit i % 128 of the
+ * Philox4x32-10 block with counter (i / 128, offset) and key `seed`, instead of a draw from torch's
+ * global generator, so that every rank and the CPU oracle regenerate the same matrix. */
+EXACT_API int exact_rademacher(uint64_t seed, uint64_t offset, int64_t D, int64_t k, float* out,
+                               void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EXACT_B200_H_ */

@@ -1,0 +1,130 @@
+"""GPU parity of the layer stack (QLinear, QBatchNorm1d, QGCNConv, QSAGEConv, QModule) against the
+CPU restatement in oracle/gnn.py, which draws the same Philox noise in the same order."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import oracle
+from oracle import gnn as O
+from exact_b200 import QModule, config, graphs, models
+from exact_b200.layers import QLinear
+from helpers import normal
+
+pytestmark = pytest.mark.gpu
+
+
+def relfro(a, b):
+    a, b = a.detach().cpu().double(), b.detach().cpu().double()
+    return float((a - b).norm() / (b.norm() + 1e-30))
+
+
+def adj_numpy(adj):
+    rowptr, col, val = adj.csr()
+    return (rowptr.cpu().numpy().astype(np.int64), col.cpu().numpy().astype(np.int64),
+            None if val is None else val.cpu().numpy())
+
+
+def reset_config(bits=2, kept_frac=1.0, seed=0):
+    config.compress_activation = True
+    config.simulate = False
+    config.activation_compression_bits = [bits]
+    config.kept_frac = kept_frac
+    config.row_offset = 0
+    config.manual_seed(seed)
+
+
+@pytest.mark.parametrize("kept_frac", [1.0, 0.125])
+@pytest.mark.parametrize("bits", [2, 8])
+def test_qlinear_gradients(bits, kept_frac):
+    reset_config(bits, kept_frac, seed=7)
+    N, D, O_ = 1000, 128, 64
+    x = torch.from_numpy(normal(N, D, 1))
+    lin = QLinear(D, O_).cuda().train()
+    g = torch.from_numpy(normal(N, O_, 2))
+    xg = x.cuda().requires_grad_()
+    out = lin(xg)
+    out.backward(g.cuda())
+    cfg = O.Cfg(bits, kept_frac, True, seed=7)
+    w, b = lin.weight.detach().cpu().requires_grad_(), lin.bias.detach().cpu().requires_grad_()
+    xc = x.clone().requires_grad_()
+    ref = O.OQLinear.apply(cfg, xc, w, b, None)
+    ref.backward(g)
+    assert relfro(out, ref) < 1e-5
+    assert relfro(xg.grad, xc.grad) < 1e-5
+    assert relfro(lin.bias.grad, b.grad) < 1e-5
+    # x_hat is identical on both sides (same noise, same R), so only GEMM rounding differs
+    assert relfro(lin.weight.grad, w.grad) < 1e-4
+    # and the compressed gradient is close to the exact one (the reference prints this, test_op.py:322-330)
+    exact_gw = g.t() @ x
+    assert relfro(lin.weight.grad, exact_gw) < (0.6 if kept_frac < 1 else 0.3)
+
+
+def run_model(cfg_name, nodes, seed, kept_frac=None):
+    c = dict(graphs.CONFIGS[cfg_name])
+    if kept_frac is not None:
+        c["kept_frac"] = kept_frac
+    reset_config(c["bits"], c["kept_frac"], seed)
+    adj = graphs.build_graph(c, seed=seed, device="cpu", nodes=nodes)
+    if c["gcn_norm"]:
+        from exact_b200 import gcn_norm
+        adj = gcn_norm(adj, add_self_loops=False)
+    n = adj.size(0)
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, c["feats"], generator=gen)
+    y = torch.randint(c["classes"], (n,), generator=gen)
+    torch.manual_seed(seed)
+    cls = models.GCN if c["model"] == "gcn" else models.SAGE
+    kw = dict(dropout=c["dropout"], batch_norm=c["batch_norm"])
+    net = QModule(cls(c["feats"], c["hidden"], c["classes"], c["layers"], **kw)).cuda().train()
+    params = {k: v.detach().cpu().clone() for k, v in net.state_dict().items()
+              if "running" not in k and "num_batches" not in k}
+    config.manual_seed(seed)
+    out = net(x.cuda(), adj.cuda())
+    loss = F.cross_entropy(out, y.cuda())
+    loss.backward()
+    grads = {k: p.grad for k, p in net.model.named_parameters()}
+    ocfg = O.Cfg(c["bits"], c["kept_frac"], True, seed=seed)
+    oloss, oout, ograds = O.train_step(ocfg, c["model"], params, x, adj_numpy(adj), y, c["layers"],
+                                       c["batch_norm"], c["dropout"])
+    return loss.item(), out, grads, oloss, oout, ograds
+
+
+def test_config1_gcn_two_layers_forward_backward():
+    """BASELINE config 1, second half: 2-layer GCN 128->64->16 on a 4,096-node Erdos-Renyi graph."""
+    loss, out, grads, oloss, oout, ograds = run_model("cfg1", None, seed=3)
+    assert abs(loss - oloss) < 1e-4 * abs(oloss)
+    assert relfro(out, oout) < 1e-5
+    for k, g in grads.items():
+        assert relfro(g, ograds[k]) < 2e-2, k
+
+
+def test_gcn_with_bn_dropout_small():
+    loss, out, grads, oloss, oout, ograds = run_model("cfg2", 3000, seed=4)
+    assert abs(loss - oloss) < 1e-4 * abs(oloss)
+    assert relfro(out, oout) < 1e-4
+    for k, g in grads.items():
+        assert relfro(g, ograds[k]) < 5e-2, k
+
+
+@pytest.mark.parametrize("cfg_name,nodes", [("cfg3", 2000), ("cfg4", 3000)])
+def test_sage_projection_small(cfg_name, nodes):
+    loss, out, grads, oloss, oout, ograds = run_model(cfg_name, nodes, seed=5)
+    assert abs(loss - oloss) < 1e-4 * abs(oloss)
+    assert relfro(out, oout) < 1e-4
+    for k, g in grads.items():
+        assert relfro(g, ograds[k]) < 5e-2, k
+
+
+def test_eval_mode_bypasses_compression_and_state_dict_prefix():
+    reset_config()
+    net = QModule(models.GCN(16, 8, 4, 2, dropout=0.5, batch_norm=True)).cuda()
+    assert all(not k.startswith("model.") for k in net.state_dict())
+    net.load_state_dict(net.state_dict())
+    adj = graphs.erdos_renyi(64, 4, 0).cuda()
+    x = torch.randn(64, 16, device="cuda")
+    net.eval()
+    with torch.no_grad():
+        a = net(x, adj)
+        b = net(x, adj)
+    assert torch.equal(a, b)

@@ -1,0 +1,63 @@
+"""Pins the oracle (and through it the B200 kernels) to the reference's own unmodified CUDA kernels,
+when those have been built into oracle/_ref/ (oracle/build_ref.py).  Skipped otherwise."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import normal, random_csr, relu_normal
+
+pytestmark = pytest.mark.gpu
+REF = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref")
+
+
+def _ref(name):
+    if not os.path.exists(os.path.join(REF, name + ".so")):
+        pytest.skip(f"{name}.so not built (python oracle/build_ref.py)")
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    return __import__(name)
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4, 8])
+@pytest.mark.parametrize("shape", [(4096, 128), (37, 13), (131, 76), (50, 602), (1000, 256)])
+def test_reference_pack_unpack_equal_oracle(shape, bits):
+    rq = _ref("ref_quantization")
+    N, D = shape
+    x = relu_normal(N, D, 101)
+    xt = torch.from_numpy(x).cuda()
+    mn, mx = xt.min(1)[0], xt.max(1)[0]
+    scale = (2 ** bits - 1) / (mx - mn)
+    torch.manual_seed(1234 + bits)
+    offset = int(torch.cuda.default_generators[torch.cuda.current_device()].get_offset())
+    packed = rq.pack_single_precision(xt, mn, mx, scale, bits, True)
+    torch.cuda.synchronize()
+    omn, omx, osc = oracle.row_stats(x, bits)
+    assert np.array_equal(scale.cpu().numpy().view(np.int32), osc.view(np.int32))
+    noise = oracle.noise_reference_pack(1234 + bits, offset, N, D, bits)
+    ours = oracle.pack(x, omn, osc, noise, bits, use_fma=True)
+    ref = packed.cpu().numpy().view(np.uint8)[:-1]
+    assert np.array_equal(ref, ours)
+    sb, mb = scale.to(torch.bfloat16), mn.to(torch.bfloat16)
+    up = rq.unpack_single_precision(packed, bits, sb.float(), mb.float(), N, D)
+    ref_up = oracle.unpack(ours, oracle.bf16_to_f32(oracle.f32_to_bf16(osc)),
+                           oracle.bf16_to_f32(oracle.f32_to_bf16(omn)), N, D, bits)
+    assert np.array_equal(up.cpu().numpy(), ref_up)
+
+
+@pytest.mark.parametrize("reduce", ["sum", "mean"])
+@pytest.mark.parametrize("with_values", [True, False])
+def test_reference_spmm_equals_oracle(reduce, with_values):
+    rs = _ref("ref_spmm")
+    rowptr, col, val = random_csr(10000, 10000, 50000, 3, with_values)
+    mat = normal(10000, 128, 4)
+    t = lambda a: torch.from_numpy(a).cuda()
+    v = t(val) if with_values else None
+    if reduce == "sum":
+        out = rs.spmm_sum_fw(None, t(rowptr), t(col), v, None, None, t(mat))
+    else:
+        out = rs.spmm_mean_fw(None, t(rowptr), t(col), v, None, None, None, t(mat))
+    assert np.array_equal(out.cpu().numpy(), oracle.spmm(rowptr, col, val, mat, reduce))

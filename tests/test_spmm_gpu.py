@@ -1,0 +1,79 @@
+"""GPU parity of the CSR SpMM (sum / mean, forward and dense-operand gradient) against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from exact_b200 import SparseTensor, config, qmatmul
+from exact_b200.cpp_extension import spmm as S
+from helpers import normal, random_csr
+
+pytestmark = pytest.mark.gpu
+
+
+def t(a, dtype=None):
+    x = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return x if dtype is None else x.to(dtype)
+
+
+@pytest.mark.parametrize("idx", [torch.int64, torch.int32])
+@pytest.mark.parametrize("reduce", ["sum", "mean"])
+@pytest.mark.parametrize("with_values", [True, False])
+@pytest.mark.parametrize("K", [128, 602, 256, 100, 40, 16, 13, 1])
+def test_forward_bit_exact(K, with_values, reduce, idx):
+    # test/test_op.py:506-562 shapes: 10,000 nodes, 50,000 edges
+    rowptr, col, val = random_csr(10000, 10000, 50000, 3, with_values)
+    mat = normal(10000, K, 4)
+    fn = S.spmm_sum_fw if reduce == "sum" else S.spmm_mean_fw
+    args = (None, t(rowptr, idx), t(col, idx), None if val is None else t(val))
+    out = fn(*args, None, None, t(mat)) if reduce == "sum" else fn(*args, None, None, None, t(mat))
+    ref = oracle.spmm(rowptr, col, val, mat, reduce)
+    # same per-row summation order and one FMA per edge as the oracle: bit-exact
+    assert np.array_equal(out.cpu().numpy(), ref)
+
+
+def test_hub_rows_and_empty_rows():
+    n, K = 3000, 256
+    rng = np.random.default_rng(9)
+    hub = np.stack([np.zeros(2500, np.int64), rng.choice(n, 2500, replace=False)])
+    rest = rng.integers(0, n, (2, 6000))
+    rest = rest[:, rest[0] > 100]        # rows 1..100 empty
+    e = np.concatenate([hub, rest], 1)
+    key = np.unique(e[0] * n + e[1])
+    row, col = key // n, key % n
+    rowptr = np.zeros(n + 1, np.int64)
+    np.cumsum(np.bincount(row, minlength=n), out=rowptr[1:])
+    mat = normal(n, K, 10)
+    for reduce in ("sum", "mean"):
+        fn = S.spmm_sum_fw if reduce == "sum" else S.spmm_mean_fw
+        extra = (None, None) if reduce == "sum" else (None, None, None)
+        out = fn(None, t(rowptr), t(col), None, *extra, t(mat))
+        assert np.array_equal(out.cpu().numpy(), oracle.spmm(rowptr, col, None, mat, reduce))
+
+
+@pytest.mark.parametrize("reduce", ["sum", "mean"])
+@pytest.mark.parametrize("with_values", [True, False])
+def test_qmatmul_forward_and_grad(reduce, with_values):
+    config.compress_activation = True
+    config.kept_frac = 1.0
+    n, K = 5000, 128
+    rowptr, col, val = random_csr(n, n, 40000, 5, with_values)
+    row = np.repeat(np.arange(n), np.diff(rowptr))
+    adj = SparseTensor(row=t(row), col=t(col), value=None if val is None else t(val), sparse_sizes=(n, n),
+                       is_sorted=True)
+    mat = normal(n, K, 6)
+    g = normal(n, K, 7)
+    x = t(mat).requires_grad_()
+    out = qmatmul(adj, x, reduce)
+    out.backward(t(g))
+    assert np.array_equal(out.detach().cpu().numpy(), oracle.spmm(rowptr, col, val, mat, reduce))
+    ref_g = oracle.spmm_bw_mat(rowptr, col, val, g, n, reduce)
+    np.testing.assert_allclose(x.grad.cpu().numpy(), ref_g, rtol=1e-6, atol=1e-6)
+    # and against torch's own sparse product
+    A = torch.sparse_csr_tensor(t(rowptr), t(col), t(val) if with_values else torch.ones(col.size, device="cuda"),
+                                size=(n, n))
+    dense = A.to_dense()
+    if reduce == "mean":
+        dense = dense / torch.from_numpy(np.maximum(np.diff(rowptr), 1)).cuda().float()[:, None]
+    torch.testing.assert_close(out.detach(), dense @ t(mat), rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(x.grad, dense.t() @ t(g), rtol=1e-4, atol=1e-4)
