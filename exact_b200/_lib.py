@@ -81,3 +81,47 @@ def ptr(t):
 def stream_ptr():
     import torch
     return torch.cuda.current_stream().cuda_stream
+
+
+# ---- launch accounting and optional per-kernel CUDA-event timing ----------------------------------
+LAUNCHES = 0      # kernels of this library launched so far (each kernel-launching entry point = 1)
+TIMER = None      # a KernelTimer while a benchmark wants per-kernel device times
+
+
+class KernelTimer:
+    """Brackets every library call with CUDA events on the launching stream.  summary() synchronises
+    and returns, per entry point: launches, total ms, algorithmic bytes."""
+
+    def __init__(self):
+        self.records = {}
+
+    def bracket(self, name, nbytes, thunk):
+        import torch
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        rc = thunk()
+        b.record()
+        self.records.setdefault(name, []).append((a, b, nbytes))
+        return rc
+
+    def summary(self):
+        import torch
+        torch.cuda.synchronize()
+        out = {}
+        for name, recs in self.records.items():
+            ms = [a.elapsed_time(b) for a, b, _ in recs]
+            out[name] = {"launches": len(recs), "ms": sum(ms), "bytes": sum(r[2] for r in recs)}
+        return out
+
+
+def invoke(name, nbytes, *args):
+    """Call entry point `name`; count it as one kernel launch; raise on a non-zero return code."""
+    global LAUNCHES
+    fn = getattr(load(), name)
+    LAUNCHES += 1
+    if TIMER is not None:
+        rc = TIMER.bracket(name, nbytes, lambda: fn(*args))
+    else:
+        rc = fn(*args)
+    check(rc, name)

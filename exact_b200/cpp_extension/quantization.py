@@ -54,10 +54,10 @@ def quantize_pack(data, bits, noise=None, seed=None, offset=None, row_offset=Non
     else:
         seed = offset = 0
     row_offset = config.row_offset if row_offset is None else row_offset
-    rc = lib.exact_quantize_pack(_lib.ptr(data), _dt(data), N, D, bits, _lib.ptr(noise), seed, offset,
-                                 row_offset, _lib.ptr(packed), _lib.ptr(scale), _lib.ptr(mn),
-                                 _lib.ptr(sf), _lib.ptr(mf), _lib.stream_ptr())
-    _lib.check(rc, "exact_quantize_pack")
+    nbytes = N * D * data.element_size() + packed.numel() - 1 + 4 * N
+    _lib.invoke("exact_quantize_pack", nbytes, _lib.ptr(data), _dt(data), N, D, bits, _lib.ptr(noise), seed,
+                offset, row_offset, _lib.ptr(packed), _lib.ptr(scale), _lib.ptr(mn), _lib.ptr(sf), _lib.ptr(mf),
+                _lib.stream_ptr())
     if want_f32_stats:
         return packed, scale, mn, sf, mf
     return packed, scale, mn
@@ -84,10 +84,9 @@ def pack_single_precision(data, min, max, scale, bits, stochastic, noise=None, s
     else:
         seed = offset = 0
     row_offset = config.row_offset if row_offset is None else row_offset
-    rc = _lib.load().exact_pack_single_precision(
-        _lib.ptr(data), _dt(data), _lib.ptr(min), _lib.ptr(scale), N, D, bits, _lib.ptr(noise), seed,
-        offset, row_offset, _lib.ptr(packed), _lib.stream_ptr())
-    _lib.check(rc, "exact_pack_single_precision")
+    nbytes = N * D * data.element_size() + packed.numel() - 1 + 8 * N
+    _lib.invoke("exact_pack_single_precision", nbytes, _lib.ptr(data), _dt(data), _lib.ptr(min), _lib.ptr(scale),
+                N, D, bits, _lib.ptr(noise), seed, offset, row_offset, _lib.ptr(packed), _lib.stream_ptr())
     return packed
 
 
@@ -107,9 +106,9 @@ def unpack_single_precision(data, bits, scale, min, N, group_size):
     if data.numel() < need or scale.numel() < N or min.numel() < N:
         raise RuntimeError("packed stream or statistics shorter than N x group_size requires")
     out = torch.empty((N, group_size), dtype=torch.float32, device=data.device)
-    rc = lib.exact_unpack_single_precision(_lib.ptr(data), bits, _lib.ptr(scale), _lib.ptr(min), _dt(scale),
-                                           N, group_size, _lib.ptr(out), _lib.stream_ptr())
-    _lib.check(rc, "exact_unpack_single_precision")
+    nbytes = need + 2 * N * scale.element_size() + 4 * N * group_size
+    _lib.invoke("exact_unpack_single_precision", nbytes, _lib.ptr(data), bits, _lib.ptr(scale), _lib.ptr(min),
+                _dt(scale), N, group_size, _lib.ptr(out), _lib.stream_ptr())
     return out
 
 
@@ -122,8 +121,8 @@ class _ActQuantizedReLU(torch.autograd.Function):
         n = input.numel()
         out = torch.empty_like(input)
         mask = torch.empty(int(lib.exact_mask_words(n)), dtype=torch.int32, device=input.device)
-        _lib.check(lib.exact_act_quantized_relu_forward(_lib.ptr(input), n, _lib.ptr(out), _lib.ptr(mask),
-                                                        _lib.stream_ptr()), "exact_act_quantized_relu_forward")
+        _lib.invoke("exact_act_quantized_relu_forward", 8 * n + n // 8, _lib.ptr(input), n, _lib.ptr(out),
+                    _lib.ptr(mask), _lib.stream_ptr())
         ctx.save_for_backward(mask)
         return out
 
@@ -132,10 +131,9 @@ class _ActQuantizedReLU(torch.autograd.Function):
         (mask,) = ctx.saved_tensors
         grad_output = grad_output.contiguous()
         gin = torch.empty_like(grad_output)
-        lib = _lib.load()
-        _lib.check(lib.exact_act_quantized_relu_backward(_lib.ptr(grad_output), _lib.ptr(mask), grad_output.numel(),
-                                                         _lib.ptr(gin), _lib.stream_ptr()),
-                   "exact_act_quantized_relu_backward")
+        n = grad_output.numel()
+        _lib.invoke("exact_act_quantized_relu_backward", 8 * n + n // 8, _lib.ptr(grad_output), _lib.ptr(mask), n,
+                    _lib.ptr(gin), _lib.stream_ptr())
         return gin
 
 
@@ -160,10 +158,8 @@ class _ActQuantizedDropout(torch.autograd.Function):
             seed = offset = 0
         # rows are the sharded dimension: element 0 of this shard is global element row_offset * row_len
         index_offset = config.row_offset * (n // input.shape[0]) if (input.dim() >= 2 and n) else 0
-        _lib.check(lib.exact_act_quantized_dropout_forward(_lib.ptr(input), n, p, _lib.ptr(uniforms), seed, offset,
-                                                           index_offset, _lib.ptr(out), _lib.ptr(mask),
-                                                           _lib.stream_ptr()),
-                   "exact_act_quantized_dropout_forward")
+        _lib.invoke("exact_act_quantized_dropout_forward", 8 * n + n // 8, _lib.ptr(input), n, p, _lib.ptr(uniforms),
+                    seed, offset, index_offset, _lib.ptr(out), _lib.ptr(mask), _lib.stream_ptr())
         ctx.save_for_backward(mask)
         ctx.p = p
         return out
@@ -173,11 +169,9 @@ class _ActQuantizedDropout(torch.autograd.Function):
         (mask,) = ctx.saved_tensors
         grad_output = grad_output.contiguous()
         gin = torch.empty_like(grad_output)
-        lib = _lib.load()
-        _lib.check(lib.exact_act_quantized_dropout_backward(_lib.ptr(grad_output), _lib.ptr(mask),
-                                                            grad_output.numel(), ctx.p, _lib.ptr(gin),
-                                                            _lib.stream_ptr()),
-                   "exact_act_quantized_dropout_backward")
+        n = grad_output.numel()
+        _lib.invoke("exact_act_quantized_dropout_backward", 8 * n + n // 8, _lib.ptr(grad_output), _lib.ptr(mask),
+                    n, ctx.p, _lib.ptr(gin), _lib.stream_ptr())
         return gin, None, None
 
 

@@ -27,10 +27,12 @@ def _spmm(rowptr, col, value, mat, reduce):
     M = rowptr.numel() - 1
     K = mat.size(1)
     out = torch.empty((M, K), dtype=mat.dtype, device=mat.device)
-    rc = _lib.load().exact_spmm(_lib.ptr(rowptr), _lib.ptr(col), 4 if col.dtype == torch.int32 else 8,
-                                _lib.ptr(value), _lib.ptr(mat), M, K, _lib.REDUCE[reduce], _lib.ptr(out),
-                                _lib.stream_ptr())
-    _lib.check(rc, "exact_spmm")
+    ib = 4 if col.dtype == torch.int32 else 8
+    nnz = col.numel()
+    # no-reuse bound: every edge gathers a full K-row; plus indices, values, row pointers and the output
+    nbytes = nnz * K * 4 + nnz * (ib + (4 if value is not None else 0)) + (M + 1) * ib + M * K * 4
+    _lib.invoke("exact_spmm", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), _lib.ptr(mat), M, K,
+                _lib.REDUCE[reduce], _lib.ptr(out), _lib.stream_ptr())
     return out
 
 

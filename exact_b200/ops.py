@@ -113,8 +113,7 @@ def _rademacher(rows, cols, device, dtype, seed=None, offset=None):
     out = torch.empty((rows, cols), dtype=torch.float32, device=device)
     seed = config.seed if seed is None else seed
     offset = config.next_offset() if offset is None else offset
-    _lib.check(_lib.load().exact_rademacher(seed, offset, rows, cols, _lib.ptr(out), _lib.stream_ptr()),
-               "exact_rademacher")
+    _lib.invoke("exact_rademacher", rows * cols * 4, seed, offset, rows, cols, _lib.ptr(out), _lib.stream_ptr())
     return out if dtype == torch.float32 else out.to(dtype)
 
 

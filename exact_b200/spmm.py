@@ -8,7 +8,14 @@ from .qscheme import QScheme
 
 
 def qmatmul(src, other, reduce="sum", quantized=None, randmat=None, scheme=None):
-    """spmm.py:55-89."""
+    """spmm.py:55-89.  A row-sharded adjacency (exact_b200.dist.ShardedSparseTensor) takes the
+    all-gather + local-SpMM route instead."""
+    from .dist import ShardedSparseTensor, sharded_spmm
+    if isinstance(src, ShardedSparseTensor):
+        if reduce in ["sum", "add"]:
+            reduce = "sum"
+        assert reduce == src.reduce, "the shard was built for a different reduction"
+        return sharded_spmm.apply(src, other, reduce)
     rowptr, col, value = src.csr()
     has_value = value is not None
     st = src.storage

@@ -172,10 +172,9 @@ def test_oracle_reproduces_reference_kernels():
         up = oracle.unpack(packed, s32, m32, N, D, bits)
         if small:
             assert np.array_equal(packed, z[f"pack{i}_packed"]), f"packed case {i}"
-            assert np.array_equal(up, z[f"pack{i}_unpacked"]), f"unpacked case {i}"
         else:
-            assert hashlib.sha256(packed.tobytes()).digest() == z[f"pack{i}_packed"].tobytes()
-            assert hashlib.sha256(up.tobytes()).digest() == z[f"pack{i}_unpacked"].tobytes()
+            assert hashlib.sha256(packed.tobytes()).digest() == z[f"pack{i}_packed"].tobytes(), f"packed case {i}"
+        assert hashlib.sha256(up.tobytes()).digest() == z[f"pack{i}_unpacked"].tobytes(), f"unpacked case {i}"
     from golden.make_ref_vectors import SPMM_CASES, make_graph
     for i, (n, K, nnz, seed) in enumerate(SPMM_CASES):
         rowptr, col, val = make_graph(n, nnz, seed)
@@ -183,4 +182,5 @@ def test_oracle_reproduces_reference_kernels():
         for red in ("sum", "mean"):
             for hv in (1, 0):
                 out = oracle.spmm(rowptr, col, val if hv else None, mat, red)
-                assert np.array_equal(out, z[f"spmm{i}_{red}_{hv}"]), f"spmm case {i} {red} {hv}"
+                assert hashlib.sha256(out.tobytes()).digest() == z[f"spmm{i}_{red}_{hv}"].tobytes(), \
+                    f"spmm case {i} {red} {hv}"

@@ -48,6 +48,29 @@ def test_reference_pack_unpack_equal_oracle(shape, bits):
     assert np.array_equal(up.cpu().numpy(), ref_up)
 
 
+def test_fma_contraction_in_reference_pack():
+    """quantization_cuda_kernel.cu:89 is compiled with nvcc's default -fmad=true.  On an input large
+    enough for the two variants to differ, the reference's binary must match the FMA variant of the
+    oracle and not the uncontracted one."""
+    rq = _ref("ref_quantization")
+    N, D, bits = 40000, 256, 8
+    x = relu_normal(N, D, 202)
+    xt = torch.from_numpy(x).cuda()
+    mn, mx = xt.min(1)[0], xt.max(1)[0]
+    scale = (2 ** bits - 1) / (mx - mn)
+    torch.manual_seed(99)
+    offset = int(torch.cuda.default_generators[torch.cuda.current_device()].get_offset())
+    ref = rq.pack_single_precision(xt, mn, mx, scale, bits, True).cpu().numpy().view(np.uint8)[:-1]
+    omn, omx, osc = oracle.row_stats(x, bits)
+    noise = oracle.noise_reference_pack(99, offset, N, D, bits)
+    fma = oracle.pack(x, omn, osc, noise, bits, use_fma=True)
+    nofma = oracle.pack(x, omn, osc, noise, bits, use_fma=False)
+    assert np.array_equal(ref, fma)
+    if not np.array_equal(fma, nofma):
+        assert not np.array_equal(ref, nofma)
+    print("bytes on which the two variants differ:", int((fma != nofma).sum()))
+
+
 @pytest.mark.parametrize("reduce", ["sum", "mean"])
 @pytest.mark.parametrize("with_values", [True, False])
 def test_reference_spmm_equals_oracle(reduce, with_values):
