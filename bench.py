@@ -1,0 +1,363 @@
+#!/usr/bin/env python
+"""Benchmark of the activation-compression hot path on B200.
+
+  python bench.py --gpus N --steps K --warmup W            this library (CUDA kernels, C ABI)
+  python bench.py --impl reference --gpus N --steps K ...   the CPU restatement of the reference's
+                                                            math on the box's host cores
+
+Metric: full-batch GNN epoch/s (the reference's own throughput definition,
+mem_speed_bench/arxiv/train_full_batch.py:251-267: one epoch = zero_grad, forward, loss, backward,
+optimizer step over the whole graph).  Default workload: the 3-layer GraphSAGE on a synthetic
+2,449,029-node power-law graph, INT2 activations with kept_frac 0.125 -- the configuration the
+1/2/4/8-GPU scaling is quoted on; node rows are partitioned across the N ranks (strong scaling).
+One JSON line is printed by rank 0; it also carries the pack / unpack kernel bandwidths against the
+HBM roofline, the roofline of the dominant kernel, the CPU baseline and the end-to-end (host buffers)
+number.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            with open(p) as f:
+                d = json.load(f)
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def workload_name(c, nodes):
+    return (f"{c['model']}{c['layers']}_{nodes}n_{c['feats']}f_{c['hidden']}h_{c['classes']}c_int{c['bits']}"
+            f"_kf{c['kept_frac']}")
+
+
+# ----------------------------------------------------------------------------------------------------
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    import exact_b200
+    from exact_b200 import QModule, _lib, config, graphs, models
+    from exact_b200 import dist as xdist
+    from exact_b200.cpp_extension import quantization as Q
+
+    rank, world, local = xdist.init_process_group_from_env()
+    assert world == args.gpus or world == 1, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    dev = torch.device("cuda", local)
+    c = dict(graphs.CONFIGS[args.workload])
+    nodes = args.nodes or c["nodes"]
+    hbm_peak, peak_kind = measured_peaks()
+
+    # ---- synthetic inputs (same seed on every rank) --------------------------------------------------
+    t0 = time.time()
+    full = graphs.build_graph(c, seed=0, device=dev, nodes=None if nodes == c["nodes"] else nodes)
+    if c["gcn_norm"]:
+        full = exact_b200.gcn_norm(full, add_self_loops=False)
+    n = full.size(0)
+    nnz = full.nnz()
+    reduce = "mean" if c["model"] == "sage" else "sum"
+    if world > 1:
+        adj = xdist.shard_graph(full, reduce, rank, world)
+        r0, r1 = adj.row_start, adj.row_end
+    else:
+        full.fill_cache_()
+        full.to_int32_()
+        full.storage.transposed(reduce)   # the SpMM backward's structure, built once
+        adj, r0, r1 = full, 0, n
+        config.row_offset = 0
+    del full
+    torch.cuda.empty_cache()
+    g = torch.Generator().manual_seed(1)
+    # features live in pinned host memory (the end-to-end leg copies them in every step)
+    x_host = torch.empty((r1 - r0, c["feats"]), dtype=torch.float32).pin_memory()
+    gd = torch.Generator(device=dev).manual_seed(1 + rank)
+    x_dev = torch.randn((r1 - r0, c["feats"]), device=dev, generator=gd)
+    x_host.copy_(x_dev)
+    y = torch.randint(c["classes"], (n,), generator=g)[r0:r1].to(dev)
+    torch.manual_seed(0)
+    cls = models.GCN if c["model"] == "gcn" else models.SAGE
+    config.compress_activation = True
+    config.activation_compression_bits = [c["bits"]]
+    config.kept_frac = c["kept_frac"]
+    config.manual_seed(0)
+    net = QModule(cls(c["feats"], c["hidden"], c["classes"], c["layers"], dropout=c["dropout"],
+                      batch_norm=c["batch_norm"])).to(dev).train()
+    opt = torch.optim.Adam(net.parameters(), lr=0.002)
+    params = list(net.parameters())
+    setup_s = time.time() - t0
+
+    def step(x):
+        opt.zero_grad(set_to_none=True)
+        out = net(x, adj)
+        loss = F.cross_entropy(out, y, reduction="sum") / n
+        loss.backward()
+        xdist.allreduce_gradients(params)
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        ms = torch.tensor([a.elapsed_time(b)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- device-resident leg ---------------------------------------------------------------------
+    for _ in range(args.warmup):
+        step(x_dev)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.LAUNCHES
+    _lib.TIMER = _lib.KernelTimer()
+    ms = timed(lambda: step(x_dev), args.steps)
+    ksum = _lib.TIMER.summary()
+    _lib.TIMER = None
+    launches = _lib.LAUNCHES - launches0
+
+    # ---- end-to-end leg: features come from pinned host memory, the loss goes back to the host ------
+    x_in = torch.empty_like(x_dev)
+
+    def e2e_step():
+        x_in.copy_(x_host, non_blocking=True)
+        return step(x_in).item()
+
+    e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- pack / unpack kernels against the HBM roofline (first half of the metric) -------------------
+    kern = {}
+    if rank == 0 and not args.no_kernels:
+        kern = kernel_bandwidths(torch, Q, _lib, dev, hbm_peak)
+
+    if rank != 0:
+        return
+    # dominant kernel of the epoch by device time
+    top = max(ksum.items(), key=lambda kv: kv[1]["ms"]) if ksum else None
+    roofline = None
+    if top:
+        name, r = top
+        per_ms = r["ms"] / r["launches"]
+        achieved = r["bytes"] / r["launches"] / (per_ms * 1e-3) / 1e9
+        roofline = {"kernel": name, "bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak,
+                    "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
+                    "traffic": None, "launches_per_step": r["launches"] / args.steps,
+                    "ms_per_launch": round(per_ms, 4),
+                    "share_of_step": round(r["ms"] / ms, 4),
+                    "bytes_model": "no-reuse bound: nnz*K*4 gather + indices + output"}
+    cpu = None
+    if args.gpus == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(c, args.cpu_nodes)
+    value = args.steps / (ms * 1e-3)
+    line = {
+        "metric": "full_batch_gnn_epoch_per_s", "value": round(value, 4), "unit": "epoch/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(c, n), "nodes": n, "directed_edges": nnz, "parallelism": f"rows/{world}",
+                   "l2": "inputs larger than L2" if n * c["hidden"] * 4 > 126e6 else "working set fits L2",
+                   "setup_s": round(setup_s, 1)},
+        "e2e": {"value": round(args.steps / (ms_e2e * 1e-3), 4), "unit": "epoch/s",
+                "h2d_bytes_per_step": x_host.numel() * 4 * world, "d2h_bytes_per_step": 4 * world},
+        "gpu_launches": launches,
+        "kernel_ms_per_step": {k: round(v["ms"] / args.steps, 3) for k, v in sorted(ksum.items())},
+        "roofline": roofline, "kernels": kern, "cpu_baseline": cpu, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def kernel_bandwidths(torch, Q, _lib, dev, hbm_peak, N=1_000_000, D=128, reps=20):
+    """Achieved GB/s of the fused quantise+pack and of unpack+dequantise, INT{1,2,4,8}, fp32 in, on a
+    10^6 x 128 activation (512 MB: larger than L2), CUDA events on the launching stream."""
+    out = {}
+    gen = torch.Generator(device=dev).manual_seed(3)
+    x = torch.randn(N, D, device=dev, generator=gen).relu_()
+    for bits in (1, 2, 4, 8):
+        pk, sb, mb = Q.quantize_pack(x, bits, seed=1, offset=0)
+        pack_bytes = N * D * 4 + (pk.numel() - 1) + 4 * N
+        unpack_bytes = (pk.numel() - 1) + 4 * N + N * D * 4
+        for kind, call, nbytes in (("pack", lambda: Q.quantize_pack(x, bits, seed=1, offset=0), pack_bytes),
+                                   ("unpack", lambda: Q.unpack_single_precision(pk, bits, sb, mb, N, D), unpack_bytes)):
+            for _ in range(3):
+                call()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                call()
+            b.record()
+            torch.cuda.synchronize()
+            gbs = nbytes * reps / (a.elapsed_time(b) * 1e-3) / 1e9
+            out[f"{kind}_int{bits}"] = {"GB/s": round(gbs, 1), "frac": round(gbs / hbm_peak, 4)}
+    out["shape"] = f"{N}x{D} fp32"
+    return out
+
+
+# ----------------------------------------------------------------------------------------------------
+def cpu_epoch(c, nodes, steps, warmup):
+    """Times the CPU restatement (oracle/ + torch CPU GEMMs) of one training epoch on a graph of
+    `nodes` nodes with the workload's mean degree; returns seconds per step."""
+    import torch
+
+    import oracle
+    from oracle import gnn as O
+    from exact_b200 import graphs, gcn_norm, models
+
+    oracle.build()
+    torch.set_num_threads(os.cpu_count())
+    adj = graphs.build_graph(c, seed=0, device="cpu", nodes=nodes)
+    if c["gcn_norm"]:
+        adj = gcn_norm(adj, add_self_loops=False)
+    n = adj.size(0)
+    rowptr, col, val = adj.csr()
+    adj_np = (rowptr.numpy(), col.numpy(), None if val is None else val.numpy())
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(n, c["feats"], generator=g)
+    y = torch.randint(c["classes"], (n,), generator=g)
+    torch.manual_seed(0)
+    cls = models.GCN if c["model"] == "gcn" else models.SAGE
+    ref_model = cls(c["feats"], c["hidden"], c["classes"], c["layers"], dropout=c["dropout"], batch_norm=c["batch_norm"])
+    params = {}
+    for k, v in ref_model.state_dict().items():
+        if "running" in k or "num_batches" in k:
+            continue
+        params[k] = v.t().contiguous() if (c["model"] == "gcn" and k.endswith("weight") and v.dim() == 2) else v
+    cfg = O.Cfg(c["bits"], c["kept_frac"], True, seed=0)
+    times = []
+    for i in range(warmup + steps):
+        t = time.perf_counter()
+        O.train_step(cfg, c["model"], params, x, adj_np, y, c["layers"], c["batch_norm"], c["dropout"])
+        if i >= warmup:
+            times.append(time.perf_counter() - t)
+    return sum(times) / len(times), n, adj.nnz()
+
+
+def cpu_baseline(c, cpu_nodes):
+    sec, n, nnz = cpu_epoch(c, cpu_nodes, steps=1, warmup=1)
+    scale = c["nodes"] / n
+    return {"value": round(1.0 / (sec * scale), 6), "unit": "epoch/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"one epoch on a {n}-node / {nnz}-edge graph of the same mean degree took {sec:.2f} s on the "
+                      f"host; scaled by {scale:.1f}x nodes to the full graph"}
+
+
+def run_reference(args):
+    """The reference has no CPU implementation of this path (its kernels are CUDA only), so the arm times
+    the CPU restatement of its math (oracle/) with all host threads on a bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from exact_b200 import graphs
+    c = dict(graphs.CONFIGS[args.workload])
+    sec, n, nnz = cpu_epoch(c, args.cpu_nodes, steps=args.steps, warmup=min(args.warmup, 1))
+    scale = (args.nodes or c["nodes"]) / n
+    value = 1.0 / (sec * scale)
+    sample = (f"{args.steps} epochs on a {n}-node / {nnz}-edge sample of the workload ({sec:.2f} s each), "
+              f"scaled by {scale:.1f}x nodes")
+    line = {"impl": "reference", "metric": "full_batch_gnn_epoch_per_s", "value": round(value, 6), "unit": "epoch/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * scale * 1e3, 1),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(c, args.nodes or c["nodes"]), "nodes": args.nodes or c["nodes"]},
+            "cpu_baseline": {"value": round(value, 6), "unit": "epoch/s", "cores": os.cpu_count(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": round(value, 6), "unit": "epoch/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="cfg4", choices=["cfg1", "cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--nodes", type=int, default=None, help="shrink the graph to this many nodes (same mean degree)")
+    ap.add_argument("--cpu-nodes", type=int, default=200000, help="nodes of the bounded sample the CPU baseline runs")
+    ap.add_argument("--no-kernels", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

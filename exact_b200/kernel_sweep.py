@@ -1,0 +1,125 @@
+"""Kernel sweep: achieved GB/s of the pack / unpack (and SpMM) kernels against the HBM roofline over
+bit widths, row counts, column counts and input dtypes (the kernel-level benchmark configuration).
+
+  python -m exact_b200.kernel_sweep                          # default grid, one JSON line per case
+  python -m exact_b200.kernel_sweep --op pack --N 1000000 --D 128 --bits 2 --reps 3   # one case (for ncu)
+
+Timing: CUDA events on the launching stream, 3 warm-up launches, inputs larger than L2 or an L2 flush
+between launches (a 256 MB write) when they are not."""
+import argparse
+import json
+import os
+
+import torch
+
+from . import _lib
+from .cpp_extension import quantization as Q
+from .cpp_extension import spmm as S
+
+
+def _peak():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def _time(call, reps, flush):
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    ms = []
+    for _ in range(reps):
+        if flush is not None:
+            flush.fill_(1.0)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        call()
+        b.record()
+        torch.cuda.synchronize()
+        ms.append(a.elapsed_time(b))
+    ms.sort()
+    return ms[len(ms) // 2]
+
+
+def run_case(op, N, D, bits, dtype, reps, noise):
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(N, D, device=dev, generator=g).relu_().to(dtype)
+    eb = x.element_size()
+    flush = torch.empty(64 * 1024 * 1024, device=dev) if N * D * eb < 256e6 else None
+    u = torch.rand(N, D, device=dev, generator=g) if noise else None
+    pk, sb, mb = Q.quantize_pack(x, bits, noise=u, seed=1, offset=0)
+    G = pk.numel() - 1
+    if op == "pack":
+        nbytes = N * D * eb + G + 4 * N + (N * D * 4 if noise else 0)
+        call = lambda: Q.quantize_pack(x, bits, noise=u, seed=1, offset=0)
+    elif op == "unpack":
+        nbytes = G + 4 * N + N * D * 4
+        call = lambda: Q.unpack_single_precision(pk, bits, sb, mb, N, D)
+    else:
+        raise ValueError(op)
+    ms = _time(call, reps, flush)
+    peak, kind = _peak()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"op": op, "N": N, "D": D, "bits": bits, "dtype": str(dtype).replace("torch.", ""),
+            "supplied_noise": bool(noise), "ms": round(ms, 4), "GB/s": round(gbs, 1), "frac": round(gbs / peak, 4),
+            "peak": peak, "peak_kind": kind}
+
+
+def run_spmm(nodes, avg_deg, K, reps, reduce):
+    from . import graphs
+    dev = torch.device("cuda")
+    adj = graphs.rmat(nodes, int(nodes * avg_deg / 2), 0, dev, self_loops=False)
+    adj.to_int32_()
+    rowptr, col, _ = adj.csr()
+    x = torch.randn(nodes, K, device=dev)
+    call = lambda: S._spmm(rowptr, col, None, x, reduce)
+    ms = _time(call, reps, None)
+    nnz = col.numel()
+    nbytes = nnz * K * 4 + nnz * 4 + (nodes + 1) * 4 + nodes * K * 4
+    peak, kind = _peak()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"op": "spmm_" + reduce, "nodes": nodes, "nnz": nnz, "K": K, "ms": round(ms, 4), "GB/s": round(gbs, 1),
+            "frac": round(gbs / peak, 4), "peak": peak, "peak_kind": kind,
+            "perfect_reuse_GB/s": round((2 * nodes * K * 4 + nnz * 4) / (ms * 1e-3) / 1e9, 1)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm"])
+    ap.add_argument("--N", type=int, nargs="*", default=[100_000, 1_000_000, 10_000_000])
+    ap.add_argument("--D", type=int, nargs="*", default=[64, 128, 256, 602])
+    ap.add_argument("--bits", type=int, nargs="*", default=[1, 2, 4, 8])
+    ap.add_argument("--dtype", nargs="*", default=["float32", "bfloat16"])
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--noise", action="store_true", help="supply the noise tensor instead of drawing Philox noise")
+    ap.add_argument("--nodes", type=int, default=1_000_000)
+    ap.add_argument("--avg-deg", type=float, default=50.0)
+    ap.add_argument("--K", type=int, nargs="*", default=[256])
+    ap.add_argument("--max-bytes", type=float, default=12e9, help="skip cases whose input exceeds this")
+    a = ap.parse_args()
+    _lib.load()
+    if a.op == "spmm":
+        for K in a.K:
+            print(json.dumps(run_spmm(a.nodes, a.avg_deg, K, a.reps, "mean")), flush=True)
+        return
+    ops = ["pack", "unpack"] if a.op == "all" else [a.op]
+    for dt in a.dtype:
+        dtype = getattr(torch, dt)
+        for N in a.N:
+            for D in a.D:
+                if N * D * 4 > a.max_bytes:
+                    continue
+                for bits in a.bits:
+                    for op in ops:
+                        if op == "unpack" and dtype != torch.float32:
+                            continue
+                        print(json.dumps(run_case(op, N, D, bits, dtype, a.reps, a.noise)), flush=True)
+                torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

@@ -163,8 +163,7 @@ def gcn_forward(cfg, params, x, adj, n_layers, batch_norm, dropout):
         if batch_norm:
             h = OBatchNorm.apply(cfg, h, params[f"bns.{i}.weight"], params[f"bns.{i}.bias"], 1e-5)
         x = OReLU.apply(h)
-        if dropout > 0:
-            x = ODropout.apply(cfg, x, dropout)
+        x = ODropout.apply(cfg, x, dropout)   # the models always call their Dropout module, p = 0 included
 
 
 def sage_forward(cfg, params, x, adj, n_layers, dropout):
@@ -178,8 +177,7 @@ def sage_forward(cfg, params, x, adj, n_layers, dropout):
         if i == n_layers - 1:
             return h
         x = OReLU.apply(h)
-        if dropout > 0:
-            x = ODropout.apply(cfg, x, dropout)
+        x = ODropout.apply(cfg, x, dropout)   # the models always call their Dropout module, p = 0 included
 
 
 def train_step(cfg, model, params, x, adj, y, n_layers, batch_norm=False, dropout=0.0):
