@@ -99,6 +99,47 @@ __device__ __forceinline__ float u32_to_unit(uint32_t r) {
   return __fmaf_rn((float)r, 2.3283064365386963e-10f, 1.1641532182693481e-10f);
 }
 
+// Two fp32 lanes in one 64-bit register and the paired arithmetic of sm_100 (each lane rounds exactly
+// like the scalar instruction).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float a, float b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 f2_sub(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// 16-bit field of a Philox word -> the float 1 + h * 2^-23 (bits 0x3F80:h), by one byte permute.
+// noise16_to_unit() turns a pair of those into (h + 0.5) * 2^-16 with one paired FMA:
+// (1 + h 2^-23) * 128 - (128 - 2^-17), exact.
+__device__ __forceinline__ float u16_lo_to_1p(uint32_t w) { return __uint_as_float(__byte_perm(w, 0x3f800000u, 0x7610)); }
+__device__ __forceinline__ float u16_hi_to_1p(uint32_t w) { return __uint_as_float(__byte_perm(w, 0x3f800000u, 0x7632)); }
+__device__ __forceinline__ f32x2 noise16_to_unit(f32x2 one_plus) {
+  return f2_fma(one_plus, f2_pack(128.f, 128.f), f2_pack(-127.99999237060546875f, -127.99999237060546875f));
+}
+
 // NaN-propagating min/max (torch.min / torch.max semantics) and their warp-wide forms.  redux.sync on
 // f32 is an sm_100a instruction.
 __device__ __forceinline__ float min_nan(float a, float b) {

@@ -181,3 +181,49 @@ def test_full_size_round_trip_properties():
     step = (x.max(1)[0] - x.min(1)[0]) / 3
     assert bool(((xh - x).abs() <= step[:, None] * 1.001 + 1e-6).all())
     assert torch.equal(mf, x.min(1)[0])
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_unpack_division_is_ieee_for_any_scale(bits):
+    """The dequantise uses a reciprocal-based quotient for ordinary scales and the division sequence
+    otherwise; both must equal the oracle's IEEE division: scales across the whole float range,
+    infinities (constant rows), denormals, negative and NaN scales."""
+    N, D = 4096, 64
+    rng = np.random.default_rng(91)
+    wpt = 8 // bits
+    packed = rng.integers(0, 256, size=(N // wpt) * D, dtype=np.uint8)
+    bits32 = rng.integers(0, 2 ** 32, size=N, dtype=np.uint64).astype(np.uint32)
+    scale = bits32.view(np.float32).copy()           # every exponent, both signs, some NaN/inf
+    scale[:64] = np.float32(np.inf)
+    scale[64:128] = np.float32(1e-41)                # denormal
+    scale[128:2048] = rng.uniform(0.01, 300.0, 1920).astype(np.float32)   # the ordinary range
+    mn = rng.standard_normal(N).astype(np.float32)
+    ref = oracle.unpack(packed, scale, mn, N, D, bits)
+    pk = torch.from_numpy(np.concatenate([packed, np.zeros(1, np.uint8)]).view(np.int8)).cuda()
+    out = Q.unpack_single_precision(pk, bits, dev(scale), dev(mn), N, D).cpu().numpy()
+    assert np.array_equal(out.view(np.uint32)[~np.isnan(ref)], ref.view(np.uint32)[~np.isnan(ref)])
+    assert np.array_equal(np.isnan(out), np.isnan(ref))
+
+
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("D", [128, 602])
+def test_philox_path_with_constant_inf_and_nan_rows(bits, D):
+    """Full tiles with Philox noise take a conversion-free rounding path unless a row of the tile is
+    constant (scale = inf), or holds an infinity (scale = 0) or a NaN; those tiles must still equal the
+    oracle bit for bit."""
+    N = 4096
+    x = relu_normal(N, D, 93)
+    x[8:16] = 0.0                 # a whole tile of constant rows (all-zero activations)
+    x[37] = 1.25                  # a constant row inside an otherwise ordinary tile
+    x[100, 5] = np.inf
+    x[203, 7] = -np.inf
+    x[300, 9] = np.nan
+    x[401] = np.float32(3e38); x[401, 0] = np.float32(-3e38)   # range overflows to inf
+    x[500, :] = np.float32(1e-39); x[500, 3] = np.float32(2e-39)  # denormal range -> scale = inf
+    seed, offset = 11, 5
+    packed, sb, mb, sf, mf = Q.quantize_pack(dev(x), bits, seed=seed, offset=offset, row_offset=0, want_f32_stats=True)
+    u = oracle.noise_b200(seed, offset, N, D)
+    op, osb, omb, osf, omf = oracle.quantize_activation(x, u, bits)
+    assert np.array_equal(sf.cpu().numpy().view(np.uint32)[~np.isnan(osf)], osf.view(np.uint32)[~np.isnan(osf)])
+    assert np.array_equal(np.isnan(sf.cpu().numpy()), np.isnan(osf))
+    assert np.array_equal(u8(packed)[:-1], op)
