@@ -33,6 +33,8 @@ class QuantizationConfig:
         self.row_offset = 0
         # Fuse projection + quantise + pack into one kernel when the shape allows it.
         self.fused_rp = True
+        # SpMM: rows with more edges than this are cut into pieces that separate warps sum (0: never).
+        self.spmm_long_row = 512
         # Do not produce compressed copies that no backward formula reads (the SpMM's dense operand
         # when edge values need no gradient).  Outputs and gradients are unaffected.
         self.skip_dead_saves = True

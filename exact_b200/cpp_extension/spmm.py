@@ -1,8 +1,48 @@
 """Stand-in for the reference's `exact.cpp_extension.spmm` module (exact/exact/cpp_extension/spmm.cc:243-252):
 spmm_{sum,mean}_{fw,bw} with the reference's argument lists, forwarded to the C ABI."""
+import weakref
+
 import torch
 
 from .. import _lib
+from ..conf import config
+
+_PLANS = {}  # id(rowptr tensor) -> (weak reference to it, {threshold: plan or None})
+
+
+def _plans_of(rowptr):
+    key = id(rowptr)
+    hit = _PLANS.get(key)
+    if hit is not None and hit[0]() is rowptr:
+        return hit[1]
+    per = {}
+    _PLANS[key] = (weakref.ref(rowptr, lambda _r, k=key: _PLANS.pop(k, None)), per)
+    return per
+
+
+def long_row_plan(rowptr, threshold):
+    """Pieces of the rows with more than `threshold` edges (see exact_spmm_split in the header), built
+    once per row-pointer tensor with torch ops and cached.  None when there is no such row."""
+    per = _plans_of(rowptr)
+    if threshold in per:
+        return per[threshold]
+    rp = rowptr.to(torch.int64)
+    deg = rp[1:] - rp[:-1]
+    long_row = torch.nonzero(deg > threshold).flatten()
+    plan = None
+    if long_row.numel() > 0:
+        pieces = (deg[long_row] + threshold - 1) // threshold
+        ptr = torch.zeros(long_row.numel() + 1, dtype=torch.int64, device=rowptr.device)
+        torch.cumsum(pieces, 0, out=ptr[1:])
+        item_row = torch.repeat_interleave(long_row, pieces)
+        within = torch.arange(item_row.numel(), device=rowptr.device) - torch.repeat_interleave(ptr[:-1], pieces)
+        begin = rp[item_row] + within * threshold
+        end = torch.minimum(begin + threshold, rp[item_row + 1])
+        plan = {"long_row": long_row.to(torch.int32), "long_item_ptr": ptr.to(torch.int32),
+                "item_row": item_row.to(torch.int32), "item_begin": begin.contiguous(), "item_end": end.contiguous(),
+                "n_items": int(item_row.numel()), "n_long": int(long_row.numel())}
+    per[threshold] = plan
+    return plan
 
 
 def _spmm(rowptr, col, value, mat, reduce):
@@ -31,8 +71,18 @@ def _spmm(rowptr, col, value, mat, reduce):
     nnz = col.numel()
     # no-reuse bound: every edge gathers a full K-row; plus indices, values, row pointers and the output
     nbytes = nnz * K * 4 + nnz * (ib + (4 if value is not None else 0)) + (M + 1) * ib + M * K * 4
-    _lib.invoke("exact_spmm", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), _lib.ptr(mat), M, K,
-                _lib.REDUCE[reduce], _lib.ptr(out), _lib.stream_ptr())
+    thr = int(config.spmm_long_row)
+    plan = long_row_plan(rowptr, thr) if thr > 0 else None
+    if plan is None:
+        _lib.invoke("exact_spmm", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), _lib.ptr(mat), M, K,
+                    _lib.REDUCE[reduce], _lib.ptr(out), _lib.stream_ptr())
+    else:
+        scratch = torch.empty((plan["n_items"], K), dtype=torch.float32, device=mat.device)
+        _lib.invoke("exact_spmm_split", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), _lib.ptr(mat),
+                    M, K, _lib.REDUCE[reduce], thr, _lib.ptr(plan["item_row"]), _lib.ptr(plan["item_begin"]),
+                    _lib.ptr(plan["item_end"]), plan["n_items"], _lib.ptr(plan["long_row"]),
+                    _lib.ptr(plan["long_item_ptr"]), plan["n_long"], _lib.ptr(scratch), _lib.ptr(out),
+                    _lib.stream_ptr())
     return out
 
 

@@ -4,11 +4,18 @@
 // gradient of spmm_sum_bw / spmm_mean_bw (exact/exact/cpp_extension/spmm.cc:31-139; kernel
 // spmm_cuda.cu:27-104; reducer.cuh:43-85).
 //
-// One warp owns one output row and a tile of 32*KVT*VEC columns.  Column indices (pre-multiplied to
-// element offsets) and edge values are fetched 32 at a time with one coalesced load and staged in
-// shared memory; every lane then walks the staged list and gathers VEC-wide (128-bit when K % 4 == 0)
-// slices of the neighbour rows, four edges in flight at a time.  Edges are accumulated in CSR order
-// with one FMA per edge, which is the reference's summation order (spmm_cuda.cu:86-93).
+// One warp owns one output row and a tile of 32*KVT*VEC columns.  Column indices and edge values are
+// fetched 32 at a time with one coalesced load and staged in shared memory; every lane then walks
+// the staged list and gathers VEC-wide (128-bit when K % 4 == 0) slices of the neighbour rows, eight
+// edges in flight at a time.  Edges are accumulated in CSR order with one FMA (or add) per edge and
+// element, which is the reference's summation order (spmm_cuda.cu:86-93), so rows handled this way
+// are bit-identical to it.
+//
+// Power-law graphs have rows with 10^4..10^5 edges; a single warp walking such a row is the whole
+// kernel's critical path.  Rows longer than a threshold are therefore left out of the row kernel and
+// cut into items of at most `threshold` edges; one warp per item writes a partial sum to caller-owned
+// scratch, and a last small kernel adds each long row's partials in order.  Only those rows differ
+// from the reference's summation order (by regrouping, within fp32 rounding).
 #include "common.cuh"
 #include "exact_b200.h"
 
@@ -22,9 +29,20 @@ struct SpmmParams {
   float* out;
   long long M, K;
   int mean;
+  long long long_threshold;  // rows with more edges are skipped by the row kernel (0: none)
+  // long-row items
+  const int* item_row;
+  const long long* item_begin;
+  const long long* item_end;
+  long long n_items;
+  const int* long_row;
+  const int* long_item_ptr;
+  long long n_long;
+  float* scratch;  // [n_items, K]
 };
 
 constexpr int kSpmmWarps = 4;
+constexpr int kEdgeUnroll = 8;
 
 template <int VEC>
 __device__ __forceinline__ void ldg_vec(const float* p, float (&o)[VEC]);
@@ -41,15 +59,96 @@ __device__ __forceinline__ void ldg_vec<2>(const float* p, float (&o)[2]) {
 template <>
 __device__ __forceinline__ void ldg_vec<1>(const float* p, float (&o)[1]) { o[0] = __ldg(p); }
 
-template <typename IdxT, int VEC, int KVT, bool HAS_VAL>
+template <int VEC>
+__device__ __forceinline__ void st_vec(float* p, const float (&a)[VEC]) {
+  if (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(a[0], a[1 % VEC], a[2 % VEC], a[3 % VEC]);
+  else if (VEC == 2) *reinterpret_cast<float2*>(p) = make_float2(a[0], a[1 % VEC]);
+  else p[0] = a[0];
+}
+
+// acc += sum over edges [begin, end) of val[e] * mat[col[e], column tile], in edge order.
+// FULL: every lane's KVT chunks lie inside K (no column predicate in the inner loop).
+template <typename IdxT, int VEC, int KVT, bool HAS_VAL, bool FULL>
+__device__ __forceinline__ void accumulate_edges(const SpmmParams& p, long long begin, long long end,
+                                                 const long long (&coff)[KVT], const bool (&cvalid)[KVT],
+                                                 uint32_t* s_idx, float* s_val, int lane,
+                                                 float (&acc)[KVT][VEC]) {
+  const IdxT* __restrict__ col = reinterpret_cast<const IdxT*>(p.col);
+  const unsigned long long row_bytes = (unsigned long long)p.K * 4ull;
+  const char* __restrict__ mat0 = reinterpret_cast<const char*>(p.mat + coff[0]);
+  for (long long base = begin; base < end; base += 32) {
+    const long long e = base + lane;
+    uint32_t idx = 0;
+    float v = 0.f;
+    if (e < end) {
+      idx = (uint32_t)col[e];
+      if (HAS_VAL) v = __ldg(p.val + e);
+    }
+    __syncwarp();
+    s_idx[lane] = idx;
+    if (HAS_VAL) s_val[lane] = v;
+    __syncwarp();
+    const int cnt = (end - base) < 32 ? (int)(end - base) : 32;
+    int i = 0;
+    // full groups of kEdgeUnroll edges: all gathers issued before the first add
+    for (; i + kEdgeUnroll <= cnt; i += kEdgeUnroll) {
+      float m[kEdgeUnroll][KVT][VEC];
+      float w[kEdgeUnroll];
+#pragma unroll
+      for (int u = 0; u < kEdgeUnroll; u++) {
+        const float* src = reinterpret_cast<const float*>(mat0 + (unsigned long long)s_idx[i + u] * row_bytes);
+        if (HAS_VAL) w[u] = s_val[i + u];
+#pragma unroll
+        for (int j = 0; j < KVT; j++)
+          if (FULL || cvalid[j]) ldg_vec<VEC>(src + j * (32 * VEC), m[u][j]);
+      }
+#pragma unroll
+      for (int u = 0; u < kEdgeUnroll; u++) {
+#pragma unroll
+        for (int j = 0; j < KVT; j++) {
+          if (FULL || cvalid[j]) {
+#pragma unroll
+            for (int x = 0; x < VEC; x++) {
+              if (HAS_VAL) acc[j][x] = __fmaf_rn(w[u], m[u][j][x], acc[j][x]);
+              else acc[j][x] = __fadd_rn(acc[j][x], m[u][j][x]);
+            }
+          }
+        }
+      }
+    }
+    // remainder, one edge at a time
+    for (; i < cnt; i++) {
+      const float* src = reinterpret_cast<const float*>(mat0 + (unsigned long long)s_idx[i] * row_bytes);
+      const float w = HAS_VAL ? s_val[i] : 1.f;
+      float m[KVT][VEC];
+#pragma unroll
+      for (int j = 0; j < KVT; j++)
+        if (FULL || cvalid[j]) ldg_vec<VEC>(src + j * (32 * VEC), m[j]);
+#pragma unroll
+      for (int j = 0; j < KVT; j++) {
+        if (FULL || cvalid[j]) {
+#pragma unroll
+          for (int x = 0; x < VEC; x++) {
+            if (HAS_VAL) acc[j][x] = __fmaf_rn(w, m[j][x], acc[j][x]);
+            else acc[j][x] = __fadd_rn(acc[j][x], m[j][x]);
+          }
+        }
+      }
+    }
+  }
+}
+
+enum SpmmMode { MODE_ROWS = 0, MODE_ITEMS = 1 };
+
+// MODE_ROWS: warp per row (rows longer than long_threshold are skipped when it is non-zero).
+// MODE_ITEMS: warp per long-row item, partial sums to scratch.
+template <typename IdxT, int VEC, int KVT, bool HAS_VAL, bool FULL, int MODE>
 __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_csr_kernel(const __grid_constant__ SpmmParams p) {
-  __shared__ long long s_off[kSpmmWarps][32];
+  __shared__ uint32_t s_idx[kSpmmWarps][32];
   __shared__ float s_val[kSpmmWarps][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long row = (long long)blockIdx.x * kSpmmWarps + warp;
-  if (row >= p.M) return;
+  const long long unit = (long long)blockIdx.x * kSpmmWarps + warp;
   const IdxT* __restrict__ rowptr = reinterpret_cast<const IdxT*>(p.rowptr);
-  const IdxT* __restrict__ col = reinterpret_cast<const IdxT*>(p.col);
   const long long K = p.K;
 
   long long coff[KVT];
@@ -59,75 +158,76 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_csr_kernel(const __grid_
     coff[j] = ((long long)blockIdx.y * (32 * KVT) + lane + 32 * j) * VEC;
     cvalid[j] = coff[j] < K;
   }
-
-  const long long start = (long long)rowptr[row], end = (long long)rowptr[row + 1];
   float acc[KVT][VEC];
 #pragma unroll
   for (int j = 0; j < KVT; j++)
 #pragma unroll
     for (int e = 0; e < VEC; e++) acc[j][e] = 0.f;
 
-  for (long long base = start; base < end; base += 32) {
-    const long long e = base + lane;
-    long long off = 0;
-    float v = 0.f;
-    if (e < end) {
-      off = (long long)col[e] * K;
-      if (HAS_VAL) v = __ldg(p.val + e);
-    }
-    __syncwarp();
-    s_off[warp][lane] = off;
-    if (HAS_VAL) s_val[warp][lane] = v;
-    __syncwarp();
-    const int cnt = (end - base) < 32 ? (int)(end - base) : 32;
-    for (int i = 0; i < cnt; i += 4) {
-      float m[4][KVT][VEC];
-      float w[4];
-#pragma unroll
-      for (int u = 0; u < 4; u++) {
-        if (i + u < cnt) {
-          const float* src = p.mat + s_off[warp][i + u];
-          if (HAS_VAL) w[u] = s_val[warp][i + u];
-#pragma unroll
-          for (int j = 0; j < KVT; j++)
-            if (cvalid[j]) ldg_vec<VEC>(src + coff[j], m[u][j]);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; u++) {
-        if (i + u < cnt) {
-#pragma unroll
-          for (int j = 0; j < KVT; j++) {
-            if (cvalid[j]) {
-#pragma unroll
-              for (int x = 0; x < VEC; x++) {
-                if (HAS_VAL) acc[j][x] = __fmaf_rn(w[u], m[u][j][x], acc[j][x]);
-                else acc[j][x] = __fadd_rn(acc[j][x], m[u][j][x]);
-              }
-            }
-          }
-        }
-      }
-    }
+  long long begin, end;
+  float* dst;
+  long long count = 0;
+  if (MODE == MODE_ROWS) {
+    if (unit >= p.M) return;
+    begin = (long long)rowptr[unit];
+    end = (long long)rowptr[unit + 1];
+    count = end - begin;
+    if (p.long_threshold > 0 && count > p.long_threshold) return;
+    dst = p.out + unit * K;
+  } else {
+    if (unit >= p.n_items) return;
+    begin = p.item_begin[unit];
+    end = p.item_end[unit];
+    dst = p.scratch + unit * K;
   }
+  accumulate_edges<IdxT, VEC, KVT, HAS_VAL, FULL>(p, begin, end, coff, cvalid, s_idx[warp], s_val[warp], lane, acc);
 
-  if (p.mean) {
-    const long long cnt = end - start;
-    const float dv = (float)(cnt > 0 ? cnt : 1);  // reducer.cuh:75-76
+  if (MODE == MODE_ROWS && p.mean) {
+    const float dv = (float)(count > 0 ? count : 1);  // reducer.cuh:75-76
 #pragma unroll
     for (int j = 0; j < KVT; j++)
 #pragma unroll
       for (int x = 0; x < VEC; x++) acc[j][x] = __fdiv_rn(acc[j][x], dv);
   }
-  float* orow = p.out + row * K;
 #pragma unroll
-  for (int j = 0; j < KVT; j++) {
-    if (cvalid[j]) {
-      if (VEC == 4) *reinterpret_cast<float4*>(orow + coff[j]) = make_float4(acc[j][0], acc[j][1 % VEC], acc[j][2 % VEC], acc[j][3 % VEC]);
-      else if (VEC == 2) *reinterpret_cast<float2*>(orow + coff[j]) = make_float2(acc[j][0], acc[j][1 % VEC]);
-      else orow[coff[j]] = acc[j][0];
-    }
+  for (int j = 0; j < KVT; j++)
+    if (FULL || cvalid[j]) st_vec<VEC>(dst + coff[j], acc[j]);
+}
+
+// Adds the partial sums of each long row in item order and writes the row of the output.
+template <typename IdxT>
+__global__ void __launch_bounds__(128) spmm_long_reduce_kernel(const __grid_constant__ SpmmParams p) {
+  const long long i = blockIdx.x;
+  if (i >= p.n_long) return;
+  const IdxT* __restrict__ rowptr = reinterpret_cast<const IdxT*>(p.rowptr);
+  const long long row = p.long_row[i];
+  const int s0 = p.long_item_ptr[i], s1 = p.long_item_ptr[i + 1];
+  const long long cnt = (long long)rowptr[row + 1] - (long long)rowptr[row];
+  const float dv = (float)(cnt > 0 ? cnt : 1);
+  for (long long c = threadIdx.x; c < p.K; c += blockDim.x) {
+    float a = 0.f;
+    for (int s = s0; s < s1; s++) a = __fadd_rn(a, p.scratch[(long long)s * p.K + c]);
+    p.out[row * p.K + c] = p.mean ? __fdiv_rn(a, dv) : a;
   }
+}
+
+template <typename IdxT, int VEC, int KVT, bool HAS_VAL, bool FULL>
+static int launch_spmm_mode(const SpmmParams& p, cudaStream_t st) {
+  const long long C = p.K / VEC;
+  const unsigned gy = (unsigned)((C + 32 * KVT - 1) / (32 * KVT));
+  {
+    dim3 grid((unsigned)((p.M + kSpmmWarps - 1) / kSpmmWarps), gy);
+    spmm_csr_kernel<IdxT, VEC, KVT, HAS_VAL, FULL, MODE_ROWS><<<grid, kSpmmWarps * 32, 0, st>>>(p);
+    EXB_CUDA_OK(cudaGetLastError());
+  }
+  if (p.n_items > 0) {
+    dim3 grid((unsigned)((p.n_items + kSpmmWarps - 1) / kSpmmWarps), gy);
+    spmm_csr_kernel<IdxT, VEC, KVT, HAS_VAL, FULL, MODE_ITEMS><<<grid, kSpmmWarps * 32, 0, st>>>(p);
+    EXB_CUDA_OK(cudaGetLastError());
+    spmm_long_reduce_kernel<IdxT><<<(unsigned)p.n_long, 128, 0, st>>>(p);
+    EXB_CUDA_OK(cudaGetLastError());
+  }
+  return EXB_OK;
 }
 
 template <typename IdxT, int VEC, bool HAS_VAL>
@@ -135,40 +235,71 @@ static int launch_spmm_kvt(const SpmmParams& p, cudaStream_t st) {
   const long long C = p.K / VEC;
   const long long per32 = (C + 31) / 32;
   const int kvt = per32 >= 4 ? 4 : (per32 >= 2 ? 2 : 1);
-  dim3 grid((unsigned)((p.M + kSpmmWarps - 1) / kSpmmWarps), (unsigned)((C + 32 * kvt - 1) / (32 * kvt)));
-  if (kvt == 4) spmm_csr_kernel<IdxT, VEC, 4, HAS_VAL><<<grid, kSpmmWarps * 32, 0, st>>>(p);
-  else if (kvt == 2) spmm_csr_kernel<IdxT, VEC, 2, HAS_VAL><<<grid, kSpmmWarps * 32, 0, st>>>(p);
-  else spmm_csr_kernel<IdxT, VEC, 1, HAS_VAL><<<grid, kSpmmWarps * 32, 0, st>>>(p);
-  EXB_CUDA_OK(cudaGetLastError());
-  return EXB_OK;
+  const bool full = C % (32 * kvt) == 0;
+#define EXB_SPMM_CASE(KVT_)                                                                          \
+  if (kvt == KVT_) {                                                                                 \
+    return full ? launch_spmm_mode<IdxT, VEC, KVT_, HAS_VAL, true>(p, st)                            \
+                : launch_spmm_mode<IdxT, VEC, KVT_, HAS_VAL, false>(p, st);                          \
+  }
+  EXB_SPMM_CASE(4) EXB_SPMM_CASE(2) EXB_SPMM_CASE(1)
+#undef EXB_SPMM_CASE
+  return EXB_ERR_UNSUPPORTED;
 }
 
 template <typename IdxT, bool HAS_VAL>
 static int launch_spmm_vec(const SpmmParams& p, cudaStream_t st) {
-  const uintptr_t a = reinterpret_cast<uintptr_t>(p.mat) | reinterpret_cast<uintptr_t>(p.out);
+  uintptr_t a = reinterpret_cast<uintptr_t>(p.mat) | reinterpret_cast<uintptr_t>(p.out);
+  if (p.scratch) a |= reinterpret_cast<uintptr_t>(p.scratch);
   if (p.K % 4 == 0 && a % 16 == 0) return launch_spmm_kvt<IdxT, 4, HAS_VAL>(p, st);
   if (p.K % 2 == 0 && a % 8 == 0) return launch_spmm_kvt<IdxT, 2, HAS_VAL>(p, st);
   return launch_spmm_kvt<IdxT, 1, HAS_VAL>(p, st);
+}
+
+static int spmm_common(SpmmParams& p, int idx_bytes, int reduce, cudaStream_t st) {
+  EXB_REQUIRE(idx_bytes == 4 || idx_bytes == 8, "spmm: idx_bytes must be 4 or 8 (got %d)", idx_bytes);
+  EXB_REQUIRE(reduce == EXACT_REDUCE_SUM || reduce == EXACT_REDUCE_MEAN, "spmm: reduce must be sum or mean");
+  EXB_REQUIRE(p.M >= 0 && p.K >= 0, "spmm: negative shape");
+  if (p.M == 0 || p.K == 0) return EXB_OK;
+  EXB_REQUIRE(p.rowptr && p.mat && p.out, "spmm: null pointer");
+  EXB_REQUIRE((p.M + kSpmmWarps - 1) / kSpmmWarps <= 2147483647LL, "spmm: too many rows");
+  EXB_REQUIRE(p.K * 4 < (1LL << 32), "spmm: K too large");
+  p.mean = reduce == EXACT_REDUCE_MEAN;
+  if (idx_bytes == 4) {
+    return p.val ? launch_spmm_vec<int32_t, true>(p, st) : launch_spmm_vec<int32_t, false>(p, st);
+  }
+  return p.val ? launch_spmm_vec<int64_t, true>(p, st) : launch_spmm_vec<int64_t, false>(p, st);
 }
 
 }  // namespace exb
 
 using namespace exb;
 
-extern "C" int exact_spmm(const void* rowptr, const void* col, int idx_bytes, const float* value,
-                          const float* mat, int64_t M, int64_t K, int reduce, float* out, void* stream) {
-  EXB_REQUIRE(idx_bytes == 4 || idx_bytes == 8, "spmm: idx_bytes must be 4 or 8 (got %d)", idx_bytes);
-  EXB_REQUIRE(reduce == EXACT_REDUCE_SUM || reduce == EXACT_REDUCE_MEAN, "spmm: reduce must be sum or mean");
-  EXB_REQUIRE(M >= 0 && K >= 0, "spmm: negative shape");
-  if (M == 0 || K == 0) return EXB_OK;
-  EXB_REQUIRE(rowptr && mat && out, "spmm: null pointer");
-  EXB_REQUIRE((M + kSpmmWarps - 1) / kSpmmWarps <= 2147483647LL, "spmm: too many rows");
-  SpmmParams p;
+extern "C" {
+
+int exact_spmm(const void* rowptr, const void* col, int idx_bytes, const float* value, const float* mat,
+               int64_t M, int64_t K, int reduce, float* out, void* stream) {
+  SpmmParams p{};
   p.rowptr = rowptr; p.col = col; p.val = value; p.mat = mat; p.out = out; p.M = M; p.K = K;
-  p.mean = reduce == EXACT_REDUCE_MEAN;
-  cudaStream_t st = (cudaStream_t)stream;
-  if (idx_bytes == 4) {
-    return value ? launch_spmm_vec<int32_t, true>(p, st) : launch_spmm_vec<int32_t, false>(p, st);
-  }
-  return value ? launch_spmm_vec<int64_t, true>(p, st) : launch_spmm_vec<int64_t, false>(p, st);
+  return spmm_common(p, idx_bytes, reduce, (cudaStream_t)stream);
 }
+
+int exact_spmm_split(const void* rowptr, const void* col, int idx_bytes, const float* value, const float* mat,
+                     int64_t M, int64_t K, int reduce, int64_t long_threshold, const int32_t* item_row,
+                     const int64_t* item_begin, const int64_t* item_end, int64_t n_items,
+                     const int32_t* long_row, const int32_t* long_item_ptr, int64_t n_long, float* scratch,
+                     float* out, void* stream) {
+  EXB_REQUIRE(long_threshold > 0, "spmm_split: long_threshold must be positive");
+  EXB_REQUIRE(n_items >= 0 && n_long >= 0, "spmm_split: negative plan size");
+  if (n_items > 0)
+    EXB_REQUIRE(item_row && item_begin && item_end && long_row && long_item_ptr && scratch && n_long > 0,
+                "spmm_split: null plan array or scratch");
+  SpmmParams p{};
+  p.rowptr = rowptr; p.col = col; p.val = value; p.mat = mat; p.out = out; p.M = M; p.K = K;
+  p.long_threshold = long_threshold;
+  p.item_row = item_row; p.item_begin = reinterpret_cast<const long long*>(item_begin);
+  p.item_end = reinterpret_cast<const long long*>(item_end); p.n_items = n_items;
+  p.long_row = long_row; p.long_item_ptr = long_item_ptr; p.n_long = n_long; p.scratch = scratch;
+  return spmm_common(p, idx_bytes, reduce, (cudaStream_t)stream);
+}
+
+}  // extern "C"

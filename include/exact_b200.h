@@ -107,6 +107,23 @@ EXACT_API int exact_act_quantized_dropout_backward(const float* grad_out, const 
 EXACT_API int exact_spmm(const void* rowptr, const void* col, int idx_bytes, const float* value,
                          const float* mat, int64_t M, int64_t K, int reduce, float* out, void* stream);
 
+/* exact_spmm with long rows cut into pieces (no counterpart in the reference, whose kernel gives
+ * every row to one warp: spmm_cuda.cu:35-57).  Rows with more than long_threshold edges are left out
+ * of the row kernel; the caller lists them and their pieces:
+ *   long_row      [n_long]      int32  indices of the long rows, ascending
+ *   long_item_ptr [n_long + 1]  int32  pieces of long row i are items long_item_ptr[i] .. [i+1]
+ *   item_row      [n_items]     int32  row of each piece
+ *   item_begin / item_end [n_items] int64  edge range of each piece (at most long_threshold edges,
+ *                                      consecutive pieces of a row tile its edge range in order)
+ *   scratch       [n_items, K]  fp32   caller-owned; holds the partial sums of the pieces
+ * Rows up to the threshold are summed exactly as exact_spmm sums them; a long row is the in-order sum
+ * of its pieces' sums. */
+EXACT_API int exact_spmm_split(const void* rowptr, const void* col, int idx_bytes, const float* value,
+                               const float* mat, int64_t M, int64_t K, int reduce, int64_t long_threshold,
+                               const int32_t* item_row, const int64_t* item_begin, const int64_t* item_end,
+                               int64_t n_items, const int32_t* long_row, const int32_t* long_item_ptr,
+                               int64_t n_long, float* scratch, float* out, void* stream);
+
 /* The random matrix of input2rp (exact/exact/ops.py:107-118, gen_rad_mat at ops.py:112-114):
  * out [D, k] row-major fp32, entries +-1/sqrt(k).  Sign i (row-major index) is bit i % 128 of the
  * Philox4x32-10 block with counter (i / 128, offset) and key `seed`, instead of a draw from torch's

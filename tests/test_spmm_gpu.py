@@ -32,23 +32,41 @@ def test_forward_bit_exact(K, with_values, reduce, idx):
     assert np.array_equal(out.cpu().numpy(), ref)
 
 
-def test_hub_rows_and_empty_rows():
-    n, K = 3000, 256
+@pytest.mark.parametrize("with_values", [True, False])
+@pytest.mark.parametrize("K", [256, 100, 602])
+def test_hub_rows_and_empty_rows(K, with_values):
+    """A 2,500-edge hub row (cut into pieces summed by separate warps), ordinary rows and empty rows.
+    Rows up to the threshold keep the reference's summation order (bit-exact); the hub rows are a
+    regrouped fp32 sum (1e-5 of the row's largest entry)."""
+    n = 3000
     rng = np.random.default_rng(9)
     hub = np.stack([np.zeros(2500, np.int64), rng.choice(n, 2500, replace=False)])
+    hub2 = np.stack([np.full(700, 2999, np.int64), rng.choice(n, 700, replace=False)])
     rest = rng.integers(0, n, (2, 6000))
-    rest = rest[:, rest[0] > 100]        # rows 1..100 empty
-    e = np.concatenate([hub, rest], 1)
+    rest = rest[:, (rest[0] > 100) & (rest[0] < 2999)]        # rows 1..100 empty
+    e = np.concatenate([hub, hub2, rest], 1)
     key = np.unique(e[0] * n + e[1])
     row, col = key // n, key % n
     rowptr = np.zeros(n + 1, np.int64)
     np.cumsum(np.bincount(row, minlength=n), out=rowptr[1:])
+    val = rng.standard_normal(col.size).astype(np.float32) if with_values else None
     mat = normal(n, K, 10)
+    long = np.diff(rowptr) > 512
+    assert long.sum() == 2
     for reduce in ("sum", "mean"):
-        fn = S.spmm_sum_fw if reduce == "sum" else S.spmm_mean_fw
-        extra = (None, None) if reduce == "sum" else (None, None, None)
-        out = fn(None, t(rowptr), t(col), None, *extra, t(mat))
-        assert np.array_equal(out.cpu().numpy(), oracle.spmm(rowptr, col, None, mat, reduce))
+        ref = oracle.spmm(rowptr, col, val, mat, reduce)
+        for thr in (512, 0):
+            config.spmm_long_row = thr
+            out = S._spmm(t(rowptr), t(col), None if val is None else t(val), t(mat), reduce).cpu().numpy()
+            if thr == 0:
+                assert np.array_equal(out, ref)
+            else:
+                assert np.array_equal(out[~long], ref[~long])
+                # a regrouped fp32 sum of ~10^3 terms: error relative to the size of the row, not of
+                # each (possibly cancelling) element
+                err = np.abs(out[long] - ref[long]).max(1)
+                assert np.all(err <= 1e-5 * np.abs(ref[long]).max(1))
+    config.spmm_long_row = 512
 
 
 @pytest.mark.parametrize("reduce", ["sum", "mean"])
