@@ -16,6 +16,8 @@
 // cut into items of at most `threshold` edges; one warp per item writes a partial sum to caller-owned
 // scratch, and a last small kernel adds each long row's partials in order.  Only those rows differ
 // from the reference's summation order (by regrouping, within fp32 rounding).
+#include <mutex>
+
 #include "common.cuh"
 #include "exact_b200.h"
 
@@ -300,6 +302,46 @@ int exact_spmm_split(const void* rowptr, const void* col, int idx_bytes, const f
   p.item_end = reinterpret_cast<const long long*>(item_end); p.n_items = n_items;
   p.long_row = long_row; p.long_item_ptr = long_item_ptr; p.n_long = n_long; p.scratch = scratch;
   return spmm_common(p, idx_bytes, reduce, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// exact_spmm_split for callers that cannot allocate device memory: the partial sums of the long-row
+// pieces live in a fixed array inside the library image instead of a caller-supplied buffer.
+static __device__ __align__(256) float g_split_scratch[EXACT_SPMM_STATIC_SCRATCH_FLOATS];
+
+// The array's name is only a host-side handle; the device address the kernels need is looked up once
+// per device (with that device current) and remembered.
+static int static_scratch_address(float** out) {
+  static std::mutex mu;
+  static float* addr[64] = {nullptr};
+  int dev = 0;
+  EXB_CUDA_OK(cudaGetDevice(&dev));
+  EXB_REQUIRE(dev >= 0 && dev < 64, "spmm_split_static: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    EXB_CUDA_OK(cudaGetSymbolAddress(&p, g_split_scratch));
+    addr[dev] = static_cast<float*>(p);
+  }
+  *out = addr[dev];
+  return EXB_OK;
+}
+
+int exact_spmm_split_static(const void* rowptr, const void* col, int idx_bytes, const float* value,
+                            const float* mat, int64_t M, int64_t K, int reduce, int64_t long_threshold,
+                            const int32_t* item_row, const int64_t* item_begin, const int64_t* item_end,
+                            int64_t n_items, const int32_t* long_row, const int32_t* long_item_ptr,
+                            int64_t n_long, float* out, void* stream) {
+  EXB_REQUIRE(n_items >= 0 && K >= 0, "spmm_split_static: negative size");
+  EXB_REQUIRE(n_items * K <= (int64_t)EXACT_SPMM_STATIC_SCRATCH_FLOATS,
+              "spmm_split_static: %lld pieces x %lld columns need %lld floats of scratch, the built-in array holds %lld; "
+              "use exact_spmm_split with a caller-owned buffer",
+              (long long)n_items, (long long)K, (long long)(n_items * K), (long long)EXACT_SPMM_STATIC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  return exact_spmm_split(rowptr, col, idx_bytes, value, mat, M, K, reduce, long_threshold, item_row, item_begin,
+                          item_end, n_items, long_row, long_item_ptr, n_long, scratch, out, stream);
 }
 
 }  // extern "C"

@@ -124,6 +124,25 @@ EXACT_API int exact_spmm_split(const void* rowptr, const void* col, int idx_byte
                                int64_t n_items, const int32_t* long_row, const int32_t* long_item_ptr,
                                int64_t n_long, float* scratch, float* out, void* stream);
 
+/* exact_spmm_split without the scratch argument (no counterpart in the reference).  Meant for hosts
+ * that must not allocate device memory around the call -- a serving loop with a frozen memory plan, a
+ * plugin running inside another framework's allocator, a region being recorded for replay.  The
+ * partial sums go to an array of EXACT_SPMM_STATIC_SCRATCH_FLOATS floats (16 MiB) that is part of the
+ * library image: every GPU that loads the library holds it until the process exits.
+ *   - n_items * K must not exceed EXACT_SPMM_STATIC_SCRATCH_FLOATS; larger plans are refused (code 1).
+ *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress with
+ *     that device current) and keeps it; make that first call before recording or capturing anything.
+ *   - All calls on a device share the array: calls that may overlap on the GPU (different streams) race.
+ *     Nothing in it needs clearing -- every piece overwrites its own slice before it is read.
+ *   - No cudaMalloc / cudaFree or other allocating call is made. */
+#define EXACT_SPMM_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)
+EXACT_API int exact_spmm_split_static(const void* rowptr, const void* col, int idx_bytes, const float* value,
+                                      const float* mat, int64_t M, int64_t K, int reduce,
+                                      int64_t long_threshold, const int32_t* item_row,
+                                      const int64_t* item_begin, const int64_t* item_end, int64_t n_items,
+                                      const int32_t* long_row, const int32_t* long_item_ptr, int64_t n_long,
+                                      float* out, void* stream);
+
 /* The random matrix of input2rp (exact/exact/ops.py:107-118, gen_rad_mat at ops.py:112-114):
  * out [D, k] row-major fp32, entries +-1/sqrt(k).  Sign i (row-major index) is bit i % 128 of the
  * Philox4x32-10 block with counter (i / 128, offset) and key `seed`, instead of a draw from torch's
