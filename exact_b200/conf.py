@@ -33,6 +33,8 @@ class QuantizationConfig:
         self.row_offset = 0
         # Fuse projection + quantise + pack into one kernel when the shape allows it.
         self.fused_rp = True
+        # Read back (synchronising) the status word of kernels with bounded on-chip waits after each call.
+        self.check_device_status = False
         # SpMM: rows with more edges than this are cut into pieces that separate warps sum (0: never).
         self.spmm_long_row = 512
         # Do not produce compressed copies that no backward formula reads (the SpMM's dense operand

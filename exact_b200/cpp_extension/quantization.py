@@ -63,6 +63,44 @@ def quantize_pack(data, bits, noise=None, seed=None, offset=None, row_offset=Non
     return packed, scale, mn
 
 
+def rp_supported(D, k, dtype=torch.float32):
+    """Shapes the fused projection+pack kernel takes (others use the unfused chain)."""
+    return dtype == torch.float32 and D % 4 == 0 and (k + 15) // 16 * 16 <= 256
+
+
+def rp_quantize_pack(data, R, bits, seed=None, offset=None, row_offset=None, want_projection=False):
+    """Fused (data @ R) -> row statistics -> stochastic quantise -> pack, one tcgen05 kernel.
+    data [N, D] fp32, R [D, k] = +-1/sqrt(k).  -> (packed int8 [G*k+1], scale bf16 [N], min bf16 [N][, y fp32 [N,k]])."""
+    _check_cuda_float(data, "data", 2)
+    _check_cuda_float(R, "R", 2)
+    N, D = data.shape
+    k = R.shape[1]
+    if R.shape[0] != D:
+        raise RuntimeError("R must be [D, k]")
+    if bits not in (1, 2, 4, 8):
+        raise RuntimeError("bits must be 1, 2, 4 or 8")
+    if not rp_supported(D, k) or data.data_ptr() % 16 != 0:
+        raise _lib.ExactB200Error("rp_quantize_pack: unsupported shape (needs fp32, D % 4 == 0, k <= 256)")
+    lib = _lib.load()
+    ws = torch.empty(int(lib.exact_rp_workspace_bytes(D, k)), dtype=torch.uint8, device=data.device)
+    packed = torch.empty(packed_numel(N, k, bits), dtype=torch.int8, device=data.device)
+    scale = torch.empty(N, dtype=torch.bfloat16, device=data.device)
+    mn = torch.empty(N, dtype=torch.bfloat16, device=data.device)
+    y = torch.empty((N, k), dtype=torch.float32, device=data.device) if want_projection else None
+    seed = config.seed if seed is None else seed
+    offset = config.next_offset() if offset is None else offset
+    row_offset = config.row_offset if row_offset is None else row_offset
+    nbytes = N * D * 4 + D * k * 4 + packed.numel() - 1 + 4 * N
+    _lib.invoke("exact_rp_quantize_pack", nbytes, _lib.ptr(data), N, D, _lib.ptr(R), k, bits, seed, offset,
+                row_offset, _lib.ptr(ws), _lib.ptr(packed), _lib.ptr(scale), _lib.ptr(mn), _lib.ptr(y),
+                _lib.stream_ptr())
+    if config.check_device_status:
+        status = int(ws[:4].view(torch.int32).item())
+        if status != 0:
+            raise _lib.ExactB200Error(f"rp_quantize_pack: device status {status} (a bounded on-chip wait expired)")
+    return (packed, scale, mn, y) if want_projection else (packed, scale, mn)
+
+
 def pack_single_precision(data, min, max, scale, bits, stochastic, noise=None, seed=None, offset=None,
                           row_offset=None):
     """quantization.cc:37-48.  `max` is accepted and ignored, as in the reference kernel; `stochastic`

@@ -1,0 +1,481 @@
+// Fused random projection + quantise + pack:  packed(quantise(X @ R))  in one kernel.
+//
+// Replaces the chain input2rp -> quantize_activation of exact/exact/ops.py:142-149 (and :273-280,
+// layers.py:153-159): torch.matmul(input, rand_matrix) (ops.py:117, a cuBLAS SGEMM that writes the
+// [N, k] fp32 product to HBM), then two row reductions, the scale, pack_single_precision and the bf16
+// casts (ops.py:61-83).  Here the product never leaves the chip.
+//
+// Shape of the work.  X is [N, D] fp32 (row-major, so K-major for the MMA), R is [D, k] with entries
+// +-1/sqrt(k), k = ceil(kept_frac * D) is small (8..128).  The arithmetic intensity is 2k/4 flop per
+// byte of X, far below the tensor-core ridge: the kernel is bound by streaming X from HBM once, and the
+// tensor core is what makes the k multiply-adds per loaded element free.
+//
+// Structure (one CTA per SM, persistent over 128-row tiles, 6 warps):
+//   warp 0   TMA producer: cp.async.bulk.tensor 2D loads of a [128 x 32] fp32 box of X and a
+//            [kpad x 32] box of sign(R)^T into a ring of shared-memory stages (128-byte swizzle),
+//            completion on mbarriers.  No multicast anywhere.
+//   warp 1   MMA issuer: tcgen05.mma.cta_group::1.kind::tf32, M = 128, N = kpad, K = 8 per instruction,
+//            accumulating in TMEM; tcgen05.commit releases smem stages and publishes finished tiles.
+//            Two accumulator buffers in TMEM let the epilogue of tile i overlap the MMAs of tile i+1.
+//   warps 2-5  epilogue: tcgen05.ld 32x32b (thread = row), * 1/sqrt(k), row min / max, scale,
+//            Philox noise, quantise, bytes assembled across the 8/bits adjacent lanes with shuffles,
+//            packed stream + bf16 statistics to HBM.
+// The B operand holds +-1 (exact in tf32); 1/sqrt(k) is applied in fp32 in the epilogue.  X is
+// truncated to tf32 by the tensor core (10-bit mantissa): the product differs from the fp32 one by
+// about 1e-3 relative, inside the 1e-2 relative-Frobenius criterion of this operator.
+//
+// Every wait on an mbarrier is bounded (about one second of SM clock).  When a wait expires the CTA
+// raises an abort flag, all roles leave their loops, outstanding bulk copies are waited for (bounded),
+// TMEM is freed and a non-zero status word is left for the host.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "exact_b200.h"
+
+namespace exb {
+
+constexpr int kRpTileM = 128;       // rows per tile = MMA M
+constexpr int kRpTileK = 32;        // fp32 elements per smem row = 128 bytes = one swizzle atom
+constexpr int kRpThreads = 192;     // 6 warps
+constexpr int kRpMaxStages = 8;
+constexpr long long kWaitLimitCycles = 2000000000LL;
+
+struct RpParams {
+  uint8_t* packed;
+  uint16_t* scale_bf16;
+  uint16_t* min_bf16;
+  float* y_out;       // optional [N, k] fp32 copy of the projection (tests)
+  int* status;        // device word: 0 = ok
+  long long N;
+  long long row_offset;
+  int D, k, kpad, bits;
+  int num_tiles, kblocks, stages;
+  unsigned stage_bytes;
+  unsigned tmem_cols;
+  float inv_sqrt_k;
+  uint32_t off_lo, off_hi;
+  PhiloxKey key;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the abort flag is (or becomes) set.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem], tf32 inputs, fp32 accumulate.
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// The mbarrier gets one arrival when all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 16 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
+// 8-row groups are 1024 bytes apart (stride byte offset); descriptor version 1; layout type 2.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fffu);
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+// Instruction descriptor: fp32 accumulator, tf32 A and B, both K-major, N and M encoded.
+__host__ __device__ inline uint32_t umma_idesc_tf32(int M, int N) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// ---- the kernel -----------------------------------------------------------------------------------
+template <int BITS>
+__global__ void __launch_bounds__(kRpThreads, 1)
+rp_pack_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_rt,
+               const __grid_constant__ RpParams p) {
+  constexpr int WPT = 8 / BITS;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) unsigned long long s_full[kRpMaxStages];
+  __shared__ __align__(8) unsigned long long s_empty[kRpMaxStages];
+  __shared__ __align__(8) unsigned long long s_tfull[2];
+  __shared__ __align__(8) unsigned long long s_tempty[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // 1024-byte aligned stage ring
+  volatile int* abort_flag = &s_abort;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < p.stages; s++) {
+      mbar_init(smem_u32(&s_full[s]), 1);
+      mbar_init(smem_u32(&s_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(smem_u32(&s_tfull[b]), 1);
+      mbar_init(smem_u32(&s_tempty[b]), 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), p.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  const int first = blockIdx.x, step = gridDim.x;
+  const uint32_t a_bytes = kRpTileM * kRpTileK * 4;
+  const uint32_t b_bytes = (uint32_t)p.kpad * kRpTileK * 4;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = first; tile < p.num_tiles && ok; tile += step) {
+        for (int kb = 0; kb < p.kblocks; kb++, it++) {
+          const int s = it % p.stages;
+          const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+          if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t full = smem_u32(&s_full[s]);
+          const uint32_t dst = tiles_base + (uint32_t)s * p.stage_bytes;
+          mbar_arrive_expect_tx(full, a_bytes + b_bytes);
+          tma_load_2d(dst, &tm_x, kb * kRpTileK, tile * kRpTileM, full);
+          tma_load_2d(dst + a_bytes, &tm_rt, kb * kRpTileK, 0, full);
+        }
+      }
+      if (!ok) {
+        // leave no bulk copy in flight: wait (bounded) for every stage that was armed last
+        const long long t0 = clock64();
+        for (int j = 0; j < p.stages && j < it; j++) {
+          const int jt = it - 1 - j;
+          const uint32_t bar = smem_u32(&s_full[jt % p.stages]);
+          const uint32_t ph = (uint32_t)(jt / p.stages) & 1u;
+          while (!mbar_try_wait(bar, ph) && clock64() - t0 < kWaitLimitCycles) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_tf32(kRpTileM, p.kpad);
+      int it = 0, t = 0;
+      bool ok = true;
+      for (int tile = first; tile < p.num_tiles && ok; tile += step, t++) {
+        const int buf = t & 1;
+        const uint32_t tph = (uint32_t)(t >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&s_tempty[buf]), tph ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.kpad);
+        for (int kb = 0; kb < p.kblocks; kb++, it++) {
+          const int s = it % p.stages;
+          const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+          if (!mbar_wait(smem_u32(&s_full[s]), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = tiles_base + (uint32_t)s * p.stage_bytes;
+          const uint64_t a_desc = umma_desc_sw128(a_addr);
+          const uint64_t b_desc = umma_desc_sw128(a_addr + a_bytes);
+#pragma unroll
+          for (int k4 = 0; k4 < kRpTileK / 8; k4++) {
+            // advance 8 tf32 = 32 bytes along K inside the swizzle atom: +2 in the (addr >> 4) field
+            umma_tf32(d_tmem, a_desc + (uint64_t)(k4 * 2), b_desc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0);
+          }
+          umma_commit(smem_u32(&s_empty[s]));  // the stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(smem_u32(&s_tfull[buf]));  // the tile's accumulator is complete
+      }
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5, thread = row ----------------
+    const int quad = warp & 3;                 // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+    const int row_in_tile = quad * 32 + lane;
+    const float B = (float)((1 << BITS) - 1);
+    const int CB8 = (p.k + 7) >> 3;
+    int t = 0;
+    bool ok = true;
+    for (int tile = first; tile < p.num_tiles && ok; tile += step, t++) {
+      const int buf = t & 1;
+      const uint32_t tph = (uint32_t)(t >> 1) & 1u;
+      if (!mbar_wait(smem_u32(&s_tfull[buf]), tph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * p.kpad);
+      const long long n = (long long)tile * kRpTileM + row_in_tile;
+      const bool row_ok = n < p.N;
+
+      // pass 1: row min / max of y = acc / sqrt(k) over the k real columns
+      float lo = __int_as_float(0x7f800000), hi = __int_as_float(0xff800000);
+      for (int c0 = 0; c0 < p.kpad; c0 += 16) {
+        float v[16];
+        tmem_ld16(taddr + (uint32_t)c0, v);
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          if (c0 + j < p.k) {
+            const float y = __fmul_rn(v[j], p.inv_sqrt_k);
+            lo = min_nan(lo, y);
+            hi = max_nan(hi, y);
+          }
+        }
+      }
+      const float sc = __fmul_rn(__frcp_rn(__fsub_rn(hi, lo)), B);  // exact/exact/ops.py:39
+      if (row_ok) {
+        p.scale_bf16[n] = f32_to_bf16_bits(sc);
+        p.min_bf16[n] = f32_to_bf16_bits(lo);
+      }
+
+      // pass 2: quantise, assemble bytes over the WPT adjacent rows (= lanes), store
+      const long long gn = n + p.row_offset;
+      const int sh = (lane % WPT) * BITS;
+      const uint32_t keep = 0x01010101u * ((0xffu << sh) & 0xffu);
+      const long long g = n / WPT;
+      for (int c0 = 0; c0 < p.kpad; c0 += 16) {
+        float v[16];
+        tmem_ld16(taddr + (uint32_t)c0, v);
+        if (c0 >= p.k) continue;  // uniform: padded columns only
+        uint32_t code[16];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {  // two blocks of 8 columns, one Philox call each
+          const unsigned long long q = (unsigned long long)(gn * CB8 + ((c0 >> 3) + h));
+          uint32_t w[4];
+          philox4x32_10((uint32_t)q, (uint32_t)(q >> 32), p.off_lo, p.off_hi, p.key, w);
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const int c = h * 8 + j;
+            const float u = (j & 1) ? u16_hi_to_unit(w[j >> 1]) : u16_lo_to_unit(w[j >> 1]);
+            const float y = __fmul_rn(v[c], p.inv_sqrt_k);
+            if (p.y_out != nullptr && row_ok && c0 + c < p.k) p.y_out[n * p.k + c0 + c] = y;
+            // quantization_cuda_kernel.cu:89
+            const float tq = __fsub_rn(__fmaf_rn(__fsub_rn(y, lo), sc, u), 0.5f);
+            code[c] = (row_ok && c0 + c < p.k) ? (uint32_t)__float2int_rn(fmaxf(tq, 0.f)) : 0u;
+          }
+        }
+#pragma unroll
+        for (int wd = 0; wd < 4; wd++) {
+          const uint32_t t01 = __byte_perm(code[wd * 4], code[wd * 4 + 1], 0x0040);
+          const uint32_t t23 = __byte_perm(code[wd * 4 + 2], code[wd * 4 + 3], 0x0040);
+          uint32_t word = (__byte_perm(t01, t23, 0x5410) << sh) & keep;  // uint8 narrowing per byte
+#pragma unroll
+          for (int m = 1; m < WPT; m <<= 1) word |= __shfl_xor_sync(0xffffffffu, word, m);
+          const int c = c0 + wd * 4;
+          if ((lane % WPT) == 0 && row_ok && c < p.k) {
+            uint8_t* dst = p.packed + g * p.k + c;
+            if ((p.k & 3) == 0) {
+              *reinterpret_cast<uint32_t*>(dst) = word;
+            } else {
+#pragma unroll
+              for (int bb = 0; bb < 4; bb++)
+                if (c + bb < p.k) dst[bb] = (uint8_t)(word >> (8 * bb));
+            }
+          }
+        }
+      }
+      // this warp is done reading the accumulator buffer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_tempty[buf]));
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+  if (threadIdx.x == 0 && s_abort) atomicExch(p.status, 1);
+}
+
+// sign(R)^T, zero padded to [kpad, Dpad]; also clears the status word.
+__global__ void rp_prepare_kernel(const float* __restrict__ R, int D, int k, int kpad, int Dpad,
+                                  float* __restrict__ rt, int* status) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0) *status = 0;
+  if (i >= kpad * Dpad) return;
+  const int j = i / Dpad, d = i - j * Dpad;
+  float v = 0.f;
+  if (j < k && d < D) v = R[(long long)d * k + j] > 0.f ? 1.f : -1.f;
+  rt[i] = v;
+}
+
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  return fn;
+}
+
+static int make_map_2d(CUtensorMap* map, const void* base, unsigned long long inner, unsigned long long outer,
+                       unsigned long long pitch_bytes, unsigned box_inner, unsigned box_outer) {
+  auto enc = get_encode();
+  if (enc == nullptr) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return EXB_OK;
+}
+
+static int rp_dims(long long D, long long k, int* kpad, int* Dpad) {
+  *kpad = (int)((k + 15) / 16 * 16);
+  *Dpad = (int)((D + kRpTileK - 1) / kRpTileK * kRpTileK);
+  return 0;
+}
+
+}  // namespace exb
+
+using namespace exb;
+
+extern "C" {
+
+int64_t exact_rp_workspace_bytes(int64_t D, int64_t k) {
+  if (D <= 0 || k <= 0) return 256;
+  int kpad, Dpad;
+  rp_dims(D, k, &kpad, &Dpad);
+  return 256 + (int64_t)kpad * Dpad * 4;
+}
+
+int exact_rp_quantize_pack(const float* x, int64_t N, int64_t D, const float* R, int64_t k, int bits,
+                           uint64_t seed, uint64_t offset, int64_t row_offset, void* workspace,
+                           uint8_t* packed, uint16_t* scale_bf16, uint16_t* min_bf16, float* y_out,
+                           void* stream) {
+  EXB_REQUIRE(bits == 1 || bits == 2 || bits == 4 || bits == 8, "bits must be 1, 2, 4 or 8 (got %d)", bits);
+  EXB_REQUIRE(N >= 0 && D > 0 && k > 0, "rp_quantize_pack: bad shape");
+  EXB_REQUIRE(row_offset >= 0 && row_offset % 8 == 0, "rp_quantize_pack: row_offset must be a non-negative multiple of 8");
+  if (N == 0) return EXB_OK;
+  EXB_REQUIRE(x && R && workspace && packed && scale_bf16 && min_bf16, "rp_quantize_pack: null pointer");
+  int kpad, Dpad;
+  rp_dims(D, k, &kpad, &Dpad);
+  if (D % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+    return fail(EXB_ERR_UNSUPPORTED, "rp_quantize_pack: the TMA path needs 16-byte aligned rows (D %% 4 == 0); D = %lld", (long long)D);
+  if (kpad > 256) return fail(EXB_ERR_UNSUPPORTED, "rp_quantize_pack: k = %lld exceeds one MMA tile (256)", (long long)k);
+  EXB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "rp_quantize_pack: workspace must be 256-byte aligned");
+  EXB_REQUIRE((N + kRpTileM - 1) / kRpTileM < 2147483647LL / kRpTileM, "rp_quantize_pack: too many rows");
+  cudaStream_t st = (cudaStream_t)stream;
+  int* status = reinterpret_cast<int*>(workspace);
+  float* rt = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 256);
+
+  rp_prepare_kernel<<<(kpad * Dpad + 255) / 256, 256, 0, st>>>(R, (int)D, (int)k, kpad, Dpad, rt, status);
+  EXB_CUDA_OK(cudaGetLastError());
+
+  CUtensorMap tm_x, tm_rt;
+  int rc = make_map_2d(&tm_x, x, (unsigned long long)D, (unsigned long long)N, (unsigned long long)D * 4, kRpTileK, kRpTileM);
+  if (rc) return rc;
+  rc = make_map_2d(&tm_rt, rt, (unsigned long long)Dpad, (unsigned long long)kpad, (unsigned long long)Dpad * 4, kRpTileK, (unsigned)kpad);
+  if (rc) return rc;
+
+  RpParams p{};
+  p.packed = packed; p.scale_bf16 = scale_bf16; p.min_bf16 = min_bf16; p.y_out = y_out; p.status = status;
+  p.N = N; p.row_offset = row_offset; p.D = (int)D; p.k = (int)k; p.kpad = kpad; p.bits = bits;
+  p.num_tiles = (int)((N + kRpTileM - 1) / kRpTileM);
+  p.kblocks = Dpad / kRpTileK;
+  p.stage_bytes = (unsigned)(kRpTileM * kRpTileK * 4 + kpad * kRpTileK * 4);
+  int stages = (int)((200 * 1024) / p.stage_bytes);
+  if (stages > kRpMaxStages) stages = kRpMaxStages;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  unsigned cols = 32;
+  while (cols < (unsigned)(2 * kpad)) cols <<= 1;
+  p.tmem_cols = cols;
+  p.inv_sqrt_k = (float)(1.0 / sqrt((double)k));
+  p.off_lo = (uint32_t)offset; p.off_hi = (uint32_t)(offset >> 32);
+  p.key = make_philox_key(seed);
+  const size_t dyn = (size_t)stages * p.stage_bytes + 1024;
+  int grid = sm_count();
+  if (grid > p.num_tiles) grid = p.num_tiles;
+
+#define EXB_RP_LAUNCH(BITS_)                                                                                  \
+  {                                                                                                           \
+    EXB_CUDA_OK(cudaFuncSetAttribute(rp_pack_kernel<BITS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn)); \
+    rp_pack_kernel<BITS_><<<grid, kRpThreads, dyn, st>>>(tm_x, tm_rt, p);                                     \
+  }
+  switch (bits) {
+    case 1: EXB_RP_LAUNCH(1) break;
+    case 2: EXB_RP_LAUNCH(2) break;
+    case 4: EXB_RP_LAUNCH(4) break;
+    default: EXB_RP_LAUNCH(8) break;
+  }
+#undef EXB_RP_LAUNCH
+  EXB_CUDA_OK(cudaGetLastError());
+  return EXB_OK;
+}
+
+}  // extern "C"

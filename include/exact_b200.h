@@ -143,6 +143,24 @@ EXACT_API int exact_spmm_split_static(const void* rowptr, const void* col, int i
                                       const int32_t* long_row, const int32_t* long_item_ptr, int64_t n_long,
                                       float* out, void* stream);
 
+/* Fused random projection + quantise + pack: the chain input2rp -> quantize_activation of
+ * exact/exact/ops.py:142-149 (torch.matmul(input, rand_matrix), ops.py:117, then ops.py:61-83) as one
+ * TMA-fed tcgen05 (tf32) GEMM whose epilogue computes the row statistics and packs, so the [N, k]
+ * product never reaches HBM.
+ *   x [N, D] fp32 (D % 4 == 0, 16-byte aligned);  R [D, k] fp32 with entries +-1/sqrt(k) (only the
+ *   signs are read; 1/sqrt(k) is applied in fp32);  k <= 256.  Other shapes return code 3 and the
+ *   caller uses the unfused chain.
+ *   workspace: exact_rp_workspace_bytes(D, k) bytes, 256-byte aligned, caller-owned.  Its first int32
+ *   is a status word the kernels clear and set non-zero only if a bounded on-chip wait expired.
+ *   Noise: Philox4x32-10 keyed by (seed, offset); one call per (global row, block of 8 columns).
+ *   y_out (optional, [N, k] fp32): the projection as the epilogue saw it (1/sqrt(k) applied).
+ * packed / scale_bf16 / min_bf16 as in exact_quantize_pack with D := k. */
+EXACT_API int64_t exact_rp_workspace_bytes(int64_t D, int64_t k);
+EXACT_API int exact_rp_quantize_pack(const float* x, int64_t N, int64_t D, const float* R, int64_t k, int bits,
+                                     uint64_t seed, uint64_t offset, int64_t row_offset, void* workspace,
+                                     uint8_t* packed, uint16_t* scale_bf16, uint16_t* min_bf16, float* y_out,
+                                     void* stream);
+
 /* The random matrix of input2rp (exact/exact/ops.py:107-118, gen_rad_mat at ops.py:112-114):
  * out [D, k] row-major fp32, entries +-1/sqrt(k).  Sign i (row-major index) is bit i % 128 of the
  * Philox4x32-10 block with counter (i / 128, offset) and key `seed`, instead of a draw from torch's

@@ -139,6 +139,13 @@ def noise_b200(seed, offset, N, D, row_offset=0):
     return out
 
 
+def noise_b200_rows(seed, offset, N, k, row_offset=0):
+    """The stochastic-rounding noise of the B200 library's fused projection+pack kernel."""
+    out = np.zeros((N, k), np.float32)
+    lib().orc_noise_b200_rows(u64(seed), u64(offset), i64(row_offset), i64(N), i64(k), _p(out))
+    return out
+
+
 def uniform_b200(seed, offset, n):
     """The production dropout uniforms of the B200 library for (seed, offset)."""
     out = np.zeros(n, np.float32)

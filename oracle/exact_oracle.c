@@ -267,6 +267,29 @@ ORC_API void orc_noise_b200(uint64_t seed, uint64_t offset, int64_t row_offset, 
   }
 }
 
+/* Noise of the B200 library's fused projection+pack kernel, whose epilogue threads own rows: one
+ * Philox call per (global row, block of 8 columns), q = n * ceil(k/8) + c/8; element (n, c) takes
+ * word (c%8)/2, low half for even c. */
+ORC_API void orc_noise_b200_rows(uint64_t seed, uint64_t offset, int64_t row_offset, int64_t N, int64_t k,
+                                 float *noise) {
+  const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  const int64_t CB8 = (k + 7) / 8;
+#pragma omp parallel for schedule(static)
+  for (int64_t n = 0; n < N; n++) {
+    int64_t gn = n + row_offset;
+    for (int64_t cb = 0; cb < CB8; cb++) {
+      uint64_t q = (uint64_t)(gn * CB8 + cb);
+      uint32_t out[4];
+      philox4x32_10((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)offset, (uint32_t)(offset >> 32), k0, k1, out);
+      for (int j = 0; j < 8 && cb * 8 + j < k; j++) {
+        uint32_t w = out[j >> 1];
+        uint32_t h = (j & 1) ? (w >> 16) : (w & 0xffffu);
+        noise[n * k + cb * 8 + j] = ((float)h + 0.5f) * 1.52587890625e-05f;
+      }
+    }
+  }
+}
+
 /* Production dropout uniforms of the B200 library: one Philox call per 4 consecutive elements,
  * counter = (i/4 lo, i/4 hi, offset lo, offset hi), u = r * 2^-32 + 2^-33 in (0, 1]. */
 ORC_API void orc_uniform_b200(uint64_t seed, uint64_t offset, int64_t n, float *u) {
