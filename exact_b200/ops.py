@@ -139,6 +139,15 @@ def project_and_quantize(input, scheme, rp=True):
     (ops.py:142-149, 273-280; layers.py:153-159) -> (quantized, randmat, proj_shape)."""
     if config.kept_frac < 1.0 and rp:
         kept_acts = int(config.kept_frac * input.shape[1] + 0.999)
+        if (config.fused_rp and config.compress_activation and not config.simulate and not config.swap
+                and input.dim() == 2 and input.is_contiguous() and input.data_ptr() % 16 == 0
+                and ext_quantization.rp_supported(input.shape[1], kept_acts, input.dtype)):
+            # one kernel: projection GEMM (tcgen05) with the statistics + quantise + pack in its epilogue
+            with torch.no_grad():
+                randmat = _rademacher(input.shape[1], kept_acts, input.device, input.dtype)
+                q_bits = config.activation_compression_bits[0]
+                q_input, q_scale, q_min = ext_quantization.rp_quantize_pack(input, randmat, q_bits)
+            return (q_input, q_bits, q_scale, q_min), randmat, torch.Size([input.shape[0], kept_acts])
         dim_reduced_input, randmat = input2rp(input, kept_acts)
     else:
         dim_reduced_input, randmat = input, None

@@ -30,9 +30,15 @@ class Noise:
 
 
 class Cfg:
-    def __init__(self, bits=2, kept_frac=1.0, compress=True, seed=0):
+    def __init__(self, bits=2, kept_frac=1.0, compress=True, seed=0, fused_rp=False):
         self.bits, self.kept_frac, self.compress = bits, kept_frac, compress
         self.noise = Noise(seed)
+        # the B200 library's fused projection+pack kernel keys its noise by (row, block of 8 columns)
+        self.fused_rp = fused_rp
+
+
+def _rp_fused(cfg, D, k):
+    return cfg.fused_rp and D % 4 == 0 and (k + 15) // 16 * 16 <= 256
 
 
 def _np(t):
@@ -44,13 +50,18 @@ def compress(cfg, x, rp=True):
     x = _np(x)
     N, D = x.shape
     R = None
+    rows_keyed = False
     if cfg.kept_frac < 1.0 and rp:
         k = int(cfg.kept_frac * D + 0.999)
         R = oracle.rademacher(cfg.noise.seed, cfg.noise.next(), D, k)
         x = oracle.input2rp(x, R)
+        rows_keyed = _rp_fused(cfg, D, k) and cfg.compress
     if not cfg.compress:
         return ("raw", x.copy(), R, (N, D))
-    u = oracle.noise_b200(cfg.noise.seed, cfg.noise.next(), x.shape[0], x.shape[1])
+    if rows_keyed:
+        u = oracle.noise_b200_rows(cfg.noise.seed, cfg.noise.next(), x.shape[0], x.shape[1])
+    else:
+        u = oracle.noise_b200(cfg.noise.seed, cfg.noise.next(), x.shape[0], x.shape[1])
     packed, sb, mb, _, _ = oracle.quantize_activation(x, u, cfg.bits)
     return ("q", (packed, sb, mb, x.shape), R, (N, D))
 
