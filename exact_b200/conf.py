@@ -33,6 +33,9 @@ class QuantizationConfig:
         self.row_offset = 0
         # Fuse projection + quantise + pack into one kernel when the shape allows it.
         self.fused_rp = True
+        # qlinear backward with a projected activation: form (g^T Xq) R^T instead of g^T (Xq R^T).  Same
+        # result up to fp32 reassociation; the [N, D] reconstruction is never written.
+        self.grad_weight_in_projected_space = True
         # Read back (synchronising) the status word of kernels with bounded on-chip waits after each call.
         self.check_device_status = False
         # SpMM: rows with more edges than this are cut into pieces that separate warps sum (0: never).

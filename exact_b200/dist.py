@@ -45,6 +45,7 @@ class ShardedSparseTensor:
         self.t_col = t_col[f0:f1].to(index_dtype).contiguous()
         self.t_w = None if t_w is None else t_w[f0:f1].contiguous()
         self._gather_buf = {}
+        self._const_gather = None   # (tensor, version, gathered): input features do not change between epochs
 
     @property
     def local_rows(self):
@@ -79,7 +80,17 @@ class sharded_spmm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, adj, x, reduce):
         ctx.adj = adj
-        x_full = adj.gather(x.contiguous(), "fw")
+        if not x.requires_grad:
+            # a leaf that needs no gradient is the model's input features: in full-batch training the same
+            # tensor comes back every epoch, so its gathered copy is kept until the tensor is modified
+            c = adj._const_gather
+            if c is not None and c[0] is x and c[1] == x._version:
+                x_full = c[2]
+            else:
+                x_full = adj.gather(x.contiguous(), "fw_const").clone() if adj.world > 1 else x
+                adj._const_gather = (x, x._version, x_full)
+        else:
+            x_full = adj.gather(x.contiguous(), "fw")
         return ext_spmm._spmm(adj.rowptr, adj.col, adj.value, x_full, reduce)
 
     @staticmethod

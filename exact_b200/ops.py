@@ -180,13 +180,23 @@ class qlinear(Function):
     def backward(ctx, grad_output):
         quantized, weight, bias, randmat = ctx.saved
         ori_input_shape, q_input_shape, rp = ctx.other_args
+        grad_output = grad_output.contiguous()
         input = dequantize_activation(quantized, q_input_shape)
-        if config.kept_frac < 1.0 and rp:
-            input = rp2input(input, ori_input_shape, randmat)
+        projected = config.kept_frac < 1.0 and rp and randmat is not None
         del quantized, ctx.saved
         empty_cache(config.empty_cache_threshold)
-        grad_input, grad_weight, grad_bias = ext_backward_func.linear_backward(
-            grad_output.contiguous(), input, weight, bias)
+        if projected and config.grad_weight_in_projected_space:
+            # grad_W = g^T (Xq R^T) = (g^T Xq) R^T: the [N, D] reconstruction of ops.py:165-166 is never
+            # materialised and the large GEMM shrinks from 2*N*out*D to 2*N*out*k flops.
+            grad_weight = grad_output.t().mm(input).mm(randmat.t())
+            grad_input = grad_output.mm(weight) if ctx.needs_input_grad[0] else None
+            grad_bias = grad_output.sum(0) if bias is not None else None
+        else:
+            if projected:
+                input = rp2input(input, ori_input_shape, randmat)
+            grad_input, grad_weight, grad_bias = ext_backward_func.linear_backward(grad_output, input, weight, bias)
+            if not ctx.needs_input_grad[0]:
+                grad_input = None
         del input, grad_output
         empty_cache(config.empty_cache_threshold)
         return grad_input, grad_weight, grad_bias, None, None, None, None

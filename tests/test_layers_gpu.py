@@ -120,6 +120,25 @@ def test_sage_projection_small(cfg_name, nodes, fused_rp):
         assert relfro(g, ograds[k]) < (0.15 if fused_rp else 5e-2), k
 
 
+def test_grad_weight_in_projected_space_equals_reference_order():
+    """(g^T Xq) R^T against the reference's g^T (Xq R^T) (ops.py:164-169): same noise, same R."""
+    N, D, O_ = 3000, 256, 64
+    x = torch.from_numpy(normal(N, D, 1)).cuda()
+    g = torch.from_numpy(normal(N, O_, 2)).cuda()
+    grads = []
+    for flag in (True, False):
+        reset_config(2, 0.125, seed=9, fused_rp=True)
+        config.grad_weight_in_projected_space = flag
+        torch.manual_seed(0)
+        lin = QLinear(D, O_).cuda().train()
+        xg = x.clone().requires_grad_()
+        lin(xg).backward(g)
+        grads.append((lin.weight.grad.clone(), xg.grad.clone(), lin.bias.grad.clone()))
+    config.grad_weight_in_projected_space = True
+    assert relfro(grads[0][0], grads[1][0]) < 1e-5
+    assert torch.equal(grads[0][1], grads[1][1]) and torch.equal(grads[0][2], grads[1][2])
+
+
 def test_eval_mode_bypasses_compression_and_state_dict_prefix():
     reset_config()
     net = QModule(models.GCN(16, 8, 4, 2, dropout=0.5, batch_norm=True)).cuda()
