@@ -45,6 +45,10 @@ def test_fused_projection_pack(N, D, k, bits):
     assert np.array_equal(sb.view(torch.int16).cpu().numpy().view(np.uint16), osb)      # (ii)
     assert np.array_equal(mb.view(torch.int16).cpu().numpy().view(np.uint16), omb)
     assert np.array_equal(packed.cpu().numpy().view(np.uint8)[:-1], op)
+    # without the debugging copy of the projection the epilogue takes its conversion-free path on full
+    # tiles: same bytes
+    packed2, sb2, mb2 = Q.rp_quantize_pack(xt, Rt, bits, seed=seed, offset=off_n, row_offset=0)
+    assert torch.equal(packed2[:-1], packed[:-1]) and torch.equal(sb2, sb) and torch.equal(mb2, mb)
     config.check_device_status = False
 
 
