@@ -39,6 +39,8 @@ SIGNATURES = {
     "exact_rp_workspace_bytes": (c_i64, [c_i64, c_i64]),
     "exact_rp_quantize_pack": (c_int, [c_ptr, c_i64, c_i64, c_ptr, c_i64, c_int, c_u64, c_u64, c_i64, c_ptr, c_ptr,
                                        c_ptr, c_ptr, c_ptr, c_ptr]),
+    "exact_unpack_rp_workspace_bytes": (c_i64, [c_i64, c_i64]),
+    "exact_unpack_dequant_rp": (c_int, [c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_i64, c_ptr, c_ptr, c_ptr]),
     "exact_rademacher": (c_int, [c_u64, c_u64, c_i64, c_i64, c_ptr, c_ptr]),
     "exact_spmm": (c_int, [c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_int, c_ptr, c_ptr]),
 }

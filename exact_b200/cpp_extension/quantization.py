@@ -101,6 +101,38 @@ def rp_quantize_pack(data, R, bits, seed=None, offset=None, row_offset=None, wan
     return (packed, scale, mn, y) if want_projection else (packed, scale, mn)
 
 
+def unpack_rp_supported(D, k):
+    """Shapes the fused unpack+transpose-projection kernel takes."""
+    Dpad, kpan = (D + 15) // 16 * 16, (k + 31) // 32
+    return Dpad <= 256 and Dpad * kpan * 128 + 2 * 128 * kpan * 128 + 2048 <= 200 * 1024
+
+
+def unpack_dequant_rp(packed, bits, scale, mn, N, R):
+    """Fused dequantise(packed [N, k]) @ R^T -> fp32 [N, D]; R is [D, k] = +-1/sqrt(k)."""
+    if not packed.is_cuda or packed.dtype != torch.int8 or packed.dim() != 1:
+        raise RuntimeError("The type of data is not correct!")
+    _check_cuda_float(scale, "scale", 1, (torch.bfloat16,))
+    _check_cuda_float(mn, "min", 1, (torch.bfloat16,))
+    _check_cuda_float(R, "R", 2)
+    D, k = R.shape
+    if not unpack_rp_supported(D, k):
+        raise _lib.ExactB200Error("unpack_dequant_rp: unsupported shape")
+    lib = _lib.load()
+    need = int(lib.exact_packed_bytes(N, k, bits))
+    if packed.numel() < need or scale.numel() < N or mn.numel() < N:
+        raise RuntimeError("packed stream or statistics shorter than N x k requires")
+    ws = torch.empty(int(lib.exact_unpack_rp_workspace_bytes(D, k)), dtype=torch.uint8, device=packed.device)
+    out = torch.empty((N, D), dtype=torch.float32, device=packed.device)
+    nbytes = need + 4 * N + D * k * 4 + N * D * 4
+    _lib.invoke("exact_unpack_dequant_rp", nbytes, _lib.ptr(packed), bits, _lib.ptr(scale), _lib.ptr(mn), N, k,
+                _lib.ptr(R), D, _lib.ptr(ws), _lib.ptr(out), _lib.stream_ptr())
+    if config.check_device_status:
+        status = int(ws[:4].view(torch.int32).item())
+        if status != 0:
+            raise _lib.ExactB200Error(f"unpack_dequant_rp: device status {status} (a bounded on-chip wait expired)")
+    return out
+
+
 def pack_single_precision(data, min, max, scale, bits, stochastic, noise=None, seed=None, offset=None,
                           row_offset=None):
     """quantization.cc:37-48.  `max` is accepted and ignored, as in the reference kernel; `stochastic`

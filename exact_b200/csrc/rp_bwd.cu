@@ -1,0 +1,297 @@
+// Fused unpack + dequantise + transpose projection:  X_hat = dequantise(packed) @ R^T  in one kernel.
+//
+// Replaces the backward chain dequantize_activation -> rp2input of exact/exact/ops.py:164-166 (and
+// :298-300, :356-358): unpack_single_precision (quantization_cuda_kernel.cu:158-185) writes the [N, k]
+// fp32 dequantised projection to HBM, torch.matmul(., rand_matrix.t()) (ops.py:124) reads it back.
+// Here the dequantised tile is produced straight into shared memory as the A operand of a tcgen05
+// GEMM; only the packed stream is read and only the [N, D] reconstruction is written.
+//
+// One CTA per SM, persistent over 128-row tiles, 9 warps:
+//   warp 0     loads sign(R) (the B operand, [D x k], K-major, 128-byte swizzle) once by TMA and keeps
+//              it resident; then issues tcgen05.mma.kind::tf32 (M = 128, N = D padded to 16, K = 8)
+//              per tile into one of two TMEM accumulator buffers.
+//   warps 1-4  A producers, thread = row: read the row's packed bytes and bf16 statistics, dequantise
+//              (code / scale + min, IEEE), store 16-byte chunks into the 128-byte-swizzled K-major
+//              layout the MMA expects (chunk index XOR row % 8), fence.proxy.async, signal.
+//   warps 5-8  epilogue, thread = row: tcgen05.ld, * 1/sqrt(k), fp32 stores of the reconstruction.
+// Two A buffers and two accumulator buffers overlap producer, MMA and epilogue of consecutive tiles.
+// All mbarrier waits are bounded; on expiry the CTA aborts cleanly and leaves a non-zero status word.
+#include "exact_b200.h"
+#include "tc.cuh"
+
+namespace exb {
+
+constexpr int kBwdTileM = 128;
+constexpr int kBwdThreads = 288;  // 9 warps
+
+struct RpBwdParams {
+  const uint8_t* packed;
+  const uint16_t* scale_bf16;
+  const uint16_t* min_bf16;
+  float* out;
+  int* status;
+  long long N;
+  int D, k, Dpad, kpanels, kmma, bits;
+  int num_tiles;
+  unsigned a_bytes, b_bytes, panel_b_bytes, tmem_cols;
+  float inv_sqrt_k;
+};
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+rp_unpack_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ RpBwdParams p) {
+  constexpr int WPT = 8 / BITS;
+  constexpr uint32_t MASK = (1u << BITS) - 1u;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) unsigned long long s_bfull;
+  __shared__ __align__(8) unsigned long long s_afull[2];
+  __shared__ __align__(8) unsigned long long s_aempty[2];
+  __shared__ __align__(8) unsigned long long s_tfull[2];
+  __shared__ __align__(8) unsigned long long s_tempty[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t b_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_base = b_base + p.b_bytes;
+  volatile int* abort_flag = &s_abort;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(smem_u32(&s_bfull), 1);
+    for (int b = 0; b < 2; b++) {
+      mbar_init(smem_u32(&s_afull[b]), 4);   // one arrival per producer warp
+      mbar_init(smem_u32(&s_aempty[b]), 1);  // tcgen05.commit
+      mbar_init(smem_u32(&s_tfull[b]), 1);   // tcgen05.commit
+      mbar_init(smem_u32(&s_tempty[b]), 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(smem_u32(&s_tmem_base), p.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  const int first = blockIdx.x, step = gridDim.x;
+
+  if (warp == 0) {
+    // ---------------- B load (once) + MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = true;
+      const uint32_t bfull = smem_u32(&s_bfull);
+      mbar_arrive_expect_tx(bfull, p.b_bytes);
+      for (int pn = 0; pn < p.kpanels; pn++) tma_load_2d(b_base + (uint32_t)pn * p.panel_b_bytes, &tm_r, pn * 32, 0, bfull);
+      ok = mbar_wait(bfull, 0, abort_flag);
+      const uint32_t idesc = umma_idesc_tf32(kBwdTileM, p.Dpad);
+      int t = 0;
+      for (int tile = first; tile < p.num_tiles && ok; tile += step, t++) {
+        const int buf = t & 1;
+        const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&s_tempty[buf]), ph ^ 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&s_afull[buf]), ph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.Dpad);
+        for (int j = 0; j < p.kmma; j++) {
+          const int pn = j >> 2, k4 = j & 3;
+          const uint64_t a_desc = umma_desc_sw128(a_base + (uint32_t)buf * p.a_bytes + (uint32_t)pn * (kBwdTileM * 128));
+          const uint64_t b_desc = umma_desc_sw128(b_base + (uint32_t)pn * p.panel_b_bytes);
+          umma_tf32(d_tmem, a_desc + (uint64_t)(k4 * 2), b_desc + (uint64_t)(k4 * 2), idesc, j != 0);
+        }
+        umma_commit(smem_u32(&s_aempty[buf]));
+        umma_commit(smem_u32(&s_tfull[buf]));
+      }
+    }
+  } else if (warp <= 4) {
+    // ---------------- A producers: unpack + dequantise into swizzled shared memory ----------------
+    const int r = (warp - 1) * 32 + lane;  // row within the tile
+    const int chunks = p.kpanels * 8;      // 16-byte chunks per row
+    const bool vec = (p.k & 3) == 0;
+    int t = 0;
+    bool ok = true;
+    for (int tile = first; tile < p.num_tiles && ok; tile += step, t++) {
+      const int buf = t & 1;
+      const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+      if (!mbar_wait(smem_u32(&s_aempty[buf]), ph ^ 1u, abort_flag)) { ok = false; break; }
+      const long long n = (long long)tile * kBwdTileM + r;
+      const bool row_ok = n < p.N;
+      float s = 1.f, m = 0.f;
+      if (row_ok) {
+        s = bf16_bits_to_f32(__ldg(p.scale_bf16 + n));
+        m = bf16_bits_to_f32(__ldg(p.min_bf16 + n));
+      }
+      const uint8_t* __restrict__ src = p.packed + (n / WPT) * p.k;
+      const int sh = (int)(n % WPT) * BITS;
+      const uint32_t row_addr = a_base + (uint32_t)buf * p.a_bytes + (uint32_t)r * 128u;
+      for (int c4 = 0; c4 < chunks; c4++) {
+        const int c = c4 * 4;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (row_ok && c < p.k) {
+          uint32_t w;
+          if (vec) {
+            w = __ldg(reinterpret_cast<const uint32_t*>(src + c));
+          } else {
+            w = 0;
+#pragma unroll
+            for (int b = 0; b < 4; b++)
+              if (c + b < p.k) w |= (uint32_t)__ldg(src + c + b) << (8 * b);
+          }
+#pragma unroll
+          for (int b = 0; b < 4; b++) {
+            if (c + b < p.k) {
+              const uint32_t code = ((w >> (8 * b)) >> sh) & MASK;
+              v[b] = __fadd_rn(__fdiv_rn((float)code, s), m);  // quantization_cuda_kernel.cu:182
+            }
+          }
+        }
+        const uint32_t pn = (uint32_t)c4 >> 3, ci = (uint32_t)c4 & 7u;
+        const uint32_t addr = row_addr + pn * (kBwdTileM * 128) + ((ci ^ ((uint32_t)r & 7u)) << 4);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3])
+                     : "memory");
+      }
+      fence_proxy_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_afull[buf]));
+    }
+  } else {
+    // ---------------- epilogue: warps 5..8, thread = row ----------------
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const bool vec = (p.D & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+    int t = 0;
+    bool ok = true;
+    for (int tile = first; tile < p.num_tiles && ok; tile += step, t++) {
+      const int buf = t & 1;
+      const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+      if (!mbar_wait(smem_u32(&s_tfull[buf]), ph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * p.Dpad);
+      const long long n = (long long)tile * kBwdTileM + r;
+      float* __restrict__ dst = p.out + n * p.D;
+      for (int c0 = 0; c0 < p.Dpad; c0 += 16) {
+        float v[16];
+        tmem_ld16(taddr + (uint32_t)c0, v);
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) {
+            const int c = c0 + j;
+            if (vec && c + 4 <= p.D) {
+              __stcs(reinterpret_cast<float4*>(dst + c),
+                     make_float4(__fmul_rn(v[j], p.inv_sqrt_k), __fmul_rn(v[j + 1], p.inv_sqrt_k),
+                                 __fmul_rn(v[j + 2], p.inv_sqrt_k), __fmul_rn(v[j + 3], p.inv_sqrt_k)));
+            } else {
+#pragma unroll
+              for (int b = 0; b < 4; b++)
+                if (c + b < p.D) dst[c + b] = __fmul_rn(v[j + b], p.inv_sqrt_k);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_tempty[buf]));
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+  if (threadIdx.x == 0 && s_abort) atomicExch(p.status, 1);
+}
+
+// sign(R), zero padded to [Dpad, kpad32]; also clears the status word.
+__global__ void rp_bwd_prepare_kernel(const float* __restrict__ R, int D, int k, int Dpad, int kpad32,
+                                      float* __restrict__ rs, int* status) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0) *status = 0;
+  if (i >= Dpad * kpad32) return;
+  const int d = i / kpad32, j = i - d * kpad32;
+  float v = 0.f;
+  if (d < D && j < k) v = R[(long long)d * k + j] > 0.f ? 1.f : -1.f;
+  rs[i] = v;
+}
+
+static void bwd_dims(long long D, long long k, int* Dpad, int* kpad32) {
+  *Dpad = (int)((D + 15) / 16 * 16);
+  *kpad32 = (int)((k + 31) / 32 * 32);
+}
+
+}  // namespace exb
+
+using namespace exb;
+
+extern "C" {
+
+int64_t exact_unpack_rp_workspace_bytes(int64_t D, int64_t k) {
+  if (D <= 0 || k <= 0) return 256;
+  int Dpad, kpad32;
+  bwd_dims(D, k, &Dpad, &kpad32);
+  return 256 + (int64_t)Dpad * kpad32 * 4;
+}
+
+int exact_unpack_dequant_rp(const uint8_t* packed, int bits, const uint16_t* scale_bf16, const uint16_t* min_bf16,
+                            int64_t N, int64_t k, const float* R, int64_t D, void* workspace, float* out,
+                            void* stream) {
+  EXB_REQUIRE(bits == 1 || bits == 2 || bits == 4 || bits == 8, "bits must be 1, 2, 4 or 8 (got %d)", bits);
+  EXB_REQUIRE(N >= 0 && D > 0 && k > 0, "unpack_dequant_rp: bad shape");
+  if (N == 0) return EXB_OK;
+  EXB_REQUIRE(packed && scale_bf16 && min_bf16 && R && workspace && out, "unpack_dequant_rp: null pointer");
+  EXB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "unpack_dequant_rp: workspace must be 256-byte aligned");
+  int Dpad, kpad32;
+  bwd_dims(D, k, &Dpad, &kpad32);
+  const int kpanels = kpad32 / 32;
+  const long long a_bytes = (long long)kBwdTileM * kpanels * 128;
+  const long long b_bytes = (long long)Dpad * kpanels * 128;
+  if (Dpad > 256 || b_bytes + 2 * a_bytes + 2048 > 200 * 1024)
+    return fail(EXB_ERR_UNSUPPORTED, "unpack_dequant_rp: D = %lld, k = %lld exceed one resident B tile (D <= 256, small k)",
+                (long long)D, (long long)k);
+  EXB_REQUIRE((N + kBwdTileM - 1) / kBwdTileM < 2147483647LL / kBwdTileM, "unpack_dequant_rp: too many rows");
+  if ((k & 3) == 0) EXB_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 3) == 0, "unpack_dequant_rp: packed must be 4-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  int* status = reinterpret_cast<int*>(workspace);
+  float* rs = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 256);
+  rp_bwd_prepare_kernel<<<(Dpad * kpad32 + 255) / 256, 256, 0, st>>>(R, (int)D, (int)k, Dpad, kpad32, rs, status);
+  EXB_CUDA_OK(cudaGetLastError());
+
+  CUtensorMap tm_r;
+  int rc = make_tensor_map_2d_f32(&tm_r, rs, (unsigned long long)kpad32, (unsigned long long)Dpad,
+                                  (unsigned long long)kpad32 * 4, 32, (unsigned)Dpad);
+  if (rc) return rc;
+
+  RpBwdParams p{};
+  p.packed = packed; p.scale_bf16 = scale_bf16; p.min_bf16 = min_bf16; p.out = out; p.status = status;
+  p.N = N; p.D = (int)D; p.k = (int)k; p.Dpad = Dpad; p.kpanels = kpanels; p.kmma = (int)((k + 7) / 8); p.bits = bits;
+  p.num_tiles = (int)((N + kBwdTileM - 1) / kBwdTileM);
+  p.a_bytes = (unsigned)a_bytes; p.b_bytes = (unsigned)b_bytes; p.panel_b_bytes = (unsigned)(Dpad * 128);
+  unsigned cols = 32;
+  while (cols < (unsigned)(2 * Dpad)) cols <<= 1;
+  p.tmem_cols = cols;
+  p.inv_sqrt_k = (float)(1.0 / sqrt((double)k));
+  const size_t dyn = (size_t)(b_bytes + 2 * a_bytes) + 1024;
+  int grid = sm_count();
+  if (grid > p.num_tiles) grid = p.num_tiles;
+
+#define EXB_BWD_LAUNCH(BITS_)                                                                                   \
+  {                                                                                                             \
+    EXB_CUDA_OK(cudaFuncSetAttribute(rp_unpack_kernel<BITS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn)); \
+    rp_unpack_kernel<BITS_><<<grid, kBwdThreads, dyn, st>>>(tm_r, p);                                           \
+  }
+  switch (bits) {
+    case 1: EXB_BWD_LAUNCH(1) break;
+    case 2: EXB_BWD_LAUNCH(2) break;
+    case 4: EXB_BWD_LAUNCH(4) break;
+    default: EXB_BWD_LAUNCH(8) break;
+  }
+#undef EXB_BWD_LAUNCH
+  EXB_CUDA_OK(cudaGetLastError());
+  return EXB_OK;
+}
+
+}  // extern "C"

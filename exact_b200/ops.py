@@ -181,8 +181,17 @@ class qlinear(Function):
         quantized, weight, bias, randmat = ctx.saved
         ori_input_shape, q_input_shape, rp = ctx.other_args
         grad_output = grad_output.contiguous()
-        input = dequantize_activation(quantized, q_input_shape)
         projected = config.kept_frac < 1.0 and rp and randmat is not None
+        input = None
+        if (projected and not config.grad_weight_in_projected_space and config.fused_rp and config.compress_activation
+                and not config.simulate and not config.swap and len(ori_input_shape) == 2
+                and ext_quantization.unpack_rp_supported(ori_input_shape[1], q_input_shape[1])):
+            # dequantise + transpose projection in one kernel (reference order: g^T (Xq R^T))
+            q_input, q_bits, q_scale, q_min = quantized
+            input = ext_quantization.unpack_dequant_rp(q_input, q_bits, q_scale, q_min, q_input_shape[0], randmat)
+            projected = False
+        if input is None:
+            input = dequantize_activation(quantized, q_input_shape)
         del quantized, ctx.saved
         empty_cache(config.empty_cache_threshold)
         if projected and config.grad_weight_in_projected_space:

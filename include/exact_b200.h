@@ -161,6 +161,20 @@ EXACT_API int exact_rp_quantize_pack(const float* x, int64_t N, int64_t D, const
                                      uint8_t* packed, uint16_t* scale_bf16, uint16_t* min_bf16, float* y_out,
                                      void* stream);
 
+/* Fused unpack + dequantise + transpose projection: the backward chain dequantize_activation ->
+ * rp2input of exact/exact/ops.py:164-166 (unpack_single_precision, quantization.cc:50-62, then
+ * torch.matmul(., rand_matrix.t()), ops.py:124) as one tcgen05 (tf32) GEMM whose A operand is
+ * dequantised straight into shared memory, so the [N, k] dequantised projection never reaches HBM.
+ *   packed / scale_bf16 / min_bf16: a packed [N, k] activation as exact_quantize_pack or
+ *   exact_rp_quantize_pack produce it;  R [D, k] fp32 (+-1/sqrt(k));  out [N, D] fp32.
+ *   D <= 256 and k small enough for sign(R) to stay resident in shared memory; other shapes return
+ *   code 3 and the caller uses the unfused chain.  workspace: exact_unpack_rp_workspace_bytes(D, k)
+ *   bytes, 256-byte aligned; its first int32 is the status word (see exact_rp_quantize_pack). */
+EXACT_API int64_t exact_unpack_rp_workspace_bytes(int64_t D, int64_t k);
+EXACT_API int exact_unpack_dequant_rp(const uint8_t* packed, int bits, const uint16_t* scale_bf16,
+                                      const uint16_t* min_bf16, int64_t N, int64_t k, const float* R, int64_t D,
+                                      void* workspace, float* out, void* stream);
+
 /* The random matrix of input2rp (exact/exact/ops.py:107-118, gen_rad_mat at ops.py:112-114):
  * out [D, k] row-major fp32, entries +-1/sqrt(k).  Sign i (row-major index) is bit i % 128 of the
  * Philox4x32-10 block with counter (i / 128, offset) and key `seed`, instead of a draw from torch's

@@ -58,3 +58,27 @@ def test_unsupported_shapes_are_refused():
     with pytest.raises(RuntimeError):
         Q.rp_quantize_pack(x, R, 2)
     assert not Q.rp_supported(602, 76) and not Q.rp_supported(602, 301) and Q.rp_supported(256, 32)
+
+
+BWD_CASES = [(256, 128, 32, 2), (1000, 256, 32, 2), (1000, 100, 13, 2), (4096, 128, 16, 4), (513, 64, 8, 8),
+             (50000, 256, 32, 2), (130, 256, 64, 1), (9, 36, 5, 2), (3000, 200, 25, 2)]
+
+
+@pytest.mark.parametrize("N,D,k,bits", BWD_CASES)
+def test_fused_unpack_transpose_projection(N, D, k, bits):
+    """dequantise(packed) @ R^T in one kernel against the oracle's dequantise -> rp2input
+    (ops.py:164-166): 1e-2 relative Frobenius (tf32 rounding of the dequantised values)."""
+    config.check_device_status = True
+    y = normal(N, k, 5)
+    noise = oracle.noise_b200(1, 2, N, k)
+    op, osb, omb, _, _ = oracle.quantize_activation(y, noise, bits)
+    R = oracle.rademacher(7, 1, D, k)
+    ref = oracle.rp2input(oracle.dequantize_activation(op, osb, omb, N, k, bits), R)
+    pk = torch.from_numpy(np.concatenate([op, np.zeros(3, np.uint8)]).view(np.int8)).cuda()
+    sb = torch.from_numpy(osb.view(np.int16)).cuda().view(torch.bfloat16)
+    mb = torch.from_numpy(omb.view(np.int16)).cuda().view(torch.bfloat16)
+    out = Q.unpack_dequant_rp(pk, bits, sb, mb, N, torch.from_numpy(R).cuda()).cpu().numpy()
+    assert out.shape == (N, D)
+    assert rel_fro(out, ref) < 1e-2
+    assert rel_fro(out, ref) < 3e-3
+    config.check_device_status = False
