@@ -104,7 +104,7 @@ def rp_quantize_pack(data, R, bits, seed=None, offset=None, row_offset=None, wan
 def unpack_rp_supported(D, k):
     """Shapes the fused unpack+transpose-projection kernel takes."""
     Dpad, kpan = (D + 15) // 16 * 16, (k + 31) // 32
-    return Dpad <= 256 and Dpad * kpan * 128 + 2 * 128 * kpan * 128 + 2048 <= 200 * 1024
+    return Dpad <= 256 and Dpad * kpan * 128 + 2 * 128 * kpan * 128 + 4 * 4096 + 2048 <= 200 * 1024
 
 
 def unpack_dequant_rp(packed, bits, scale, mn, N, R):

@@ -13,7 +13,8 @@
 //   warps 1-4  A producers, thread = row: read the row's packed bytes and bf16 statistics, dequantise
 //              (code / scale + min, IEEE), store 16-byte chunks into the 128-byte-swizzled K-major
 //              layout the MMA expects (chunk index XOR row % 8), fence.proxy.async, signal.
-//   warps 5-8  epilogue, thread = row: tcgen05.ld, * 1/sqrt(k), fp32 stores of the reconstruction.
+//   warps 5-8  epilogue: tcgen05.ld (thread = row), * 1/sqrt(k), transposed through a warp-private
+//              swizzled staging tile so that the fp32 reconstruction leaves in full 128-byte lines.
 // Two A buffers and two accumulator buffers overlap producer, MMA and epilogue of consecutive tiles.
 // All mbarrier waits are bounded; on expiry the CTA aborts cleanly and leaves a non-zero status word.
 #include "exact_b200.h"
@@ -33,6 +34,7 @@ struct RpBwdParams {
   long long N;
   int D, k, Dpad, kpanels, kmma, bits;
   int num_tiles;
+  int nbuf;  // TMEM accumulator buffers per CTA: 2, or 1 when two CTAs share the SM's 512 columns at D > 128
   unsigned a_bytes, b_bytes, panel_b_bytes, tmem_cols;
   float inv_sqrt_k;
 };
@@ -42,7 +44,7 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 }
 
 template <int BITS>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 2)
 rp_unpack_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ RpBwdParams p) {
   constexpr int WPT = 8 / BITS;
   constexpr uint32_t MASK = (1u << BITS) - 1u;
@@ -89,12 +91,14 @@ rp_unpack_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       const uint32_t idesc = umma_idesc_tf32(kBwdTileM, p.Dpad);
       int t = 0;
       for (int tile = first; tile < p.num_tiles && ok; tile += step, t++) {
-        const int buf = t & 1;
+        const int buf = t & 1;                              // A buffer
         const uint32_t ph = (uint32_t)(t >> 1) & 1u;
-        if (!mbar_wait(smem_u32(&s_tempty[buf]), ph ^ 1u, abort_flag)) { ok = false; break; }
+        const int tb = t % p.nbuf;                          // accumulator buffer
+        const uint32_t tph = (uint32_t)(t / p.nbuf) & 1u;
+        if (!mbar_wait(smem_u32(&s_tempty[tb]), tph ^ 1u, abort_flag)) { ok = false; break; }
         if (!mbar_wait(smem_u32(&s_afull[buf]), ph, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.Dpad);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(tb * p.Dpad);
         for (int j = 0; j < p.kmma; j++) {
           const int pn = j >> 2, k4 = j & 3;
           const uint64_t a_desc = umma_desc_sw128(a_base + (uint32_t)buf * p.a_bytes + (uint32_t)pn * (kBwdTileM * 128));
@@ -102,7 +106,7 @@ rp_unpack_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
           umma_tf32(d_tmem, a_desc + (uint64_t)(k4 * 2), b_desc + (uint64_t)(k4 * 2), idesc, j != 0);
         }
         umma_commit(smem_u32(&s_aempty[buf]));
-        umma_commit(smem_u32(&s_tfull[buf]));
+        umma_commit(smem_u32(&s_tfull[tb]));
       }
     }
   } else if (warp <= 4) {
@@ -123,6 +127,14 @@ rp_unpack_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
         s = bf16_bits_to_f32(__ldg(p.scale_bf16 + n));
         m = bf16_bits_to_f32(__ldg(p.min_bf16 + n));
       }
+      // code / s as q0 = c*r, rem = fma(-q0, s, c), q = fma(rem, r, q0) with r the correctly rounded
+      // reciprocal: equal to the IEEE quotient for codes 0..255 and 2^-100 <= |s| <= 2^100; other scales
+      // (inf of a constant row, NaN, denormal) take the division sequence.
+      const float rcp = __frcp_rn(s);
+      const uint32_t sexp = (__float_as_uint(s) >> 23) & 0xffu;
+      const bool tame = __all_sync(0xffffffffu, sexp >= 27u && sexp <= 227u);
+      const f32x2 r2 = f2_pack(rcp, rcp), ns2 = f2_pack(-s, -s), m2 = f2_pack(m, m);
+      const f32x2 neg_2p23 = f2_pack(-8388608.f, -8388608.f);
       const uint8_t* __restrict__ src = p.packed + (n / WPT) * p.k;
       const int sh = (int)(n % WPT) * BITS;
       const uint32_t row_addr = a_base + (uint32_t)buf * p.a_bytes + (uint32_t)r * 128u;
@@ -139,11 +151,25 @@ rp_unpack_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
             for (int b = 0; b < 4; b++)
               if (c + b < p.k) w |= (uint32_t)__ldg(src + c + b) << (8 * b);
           }
+          if (tame && c + 4 <= p.k) {
+            const uint32_t t4 = (w >> sh) & (0x01010101u * MASK);
+            float cf[4];
 #pragma unroll
-          for (int b = 0; b < 4; b++) {
-            if (c + b < p.k) {
-              const uint32_t code = ((w >> (8 * b)) >> sh) & MASK;
-              v[b] = __fadd_rn(__fdiv_rn((float)code, s), m);  // quantization_cuda_kernel.cu:182
+            for (int b = 0; b < 4; b++) cf[b] = __uint_as_float(__byte_perm(t4, 0x4b000000u, 0x7540 | b));  // 2^23 + code
+#pragma unroll
+            for (int b = 0; b < 4; b += 2) {
+              const f32x2 c2 = f2_add(f2_pack(cf[b], cf[b + 1]), neg_2p23);
+              const f32x2 q0 = f2_mul(c2, r2);
+              const f32x2 q = f2_fma(f2_fma(q0, ns2, c2), r2, q0);
+              f2_unpack(f2_add(q, m2), v[b], v[b + 1]);
+            }
+          } else {
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+              if (c + b < p.k) {
+                const uint32_t code = ((w >> (8 * b)) >> sh) & MASK;
+                v[b] = __fadd_rn(__fdiv_rn((float)code, s), m);  // quantization_cuda_kernel.cu:182
+              }
             }
           }
         }
@@ -159,36 +185,57 @@ rp_unpack_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
   } else {
     // ---------------- epilogue: warps 5..8, thread = row ----------------
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;
     const bool vec = (p.D & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+    const uint32_t stage_addr = a_base + 2u * p.a_bytes + (uint32_t)quad * 4096u;  // 32 rows x 128 bytes per warp
     int t = 0;
     bool ok = true;
     for (int tile = first; tile < p.num_tiles && ok; tile += step, t++) {
-      const int buf = t & 1;
-      const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+      const int buf = t % p.nbuf;
+      const uint32_t ph = (uint32_t)(t / p.nbuf) & 1u;
       if (!mbar_wait(smem_u32(&s_tfull[buf]), ph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * p.Dpad);
-      const long long n = (long long)tile * kBwdTileM + r;
-      float* __restrict__ dst = p.out + n * p.D;
-      for (int c0 = 0; c0 < p.Dpad; c0 += 16) {
-        float v[16];
-        tmem_ld16(taddr + (uint32_t)c0, v);
-        if (n < p.N) {
+      // 32 columns at a time: accumulators -> this warp's private staging tile in shared memory
+      // (16-byte chunks XOR-swizzled by row) -> coalesced global stores, 4 rows x 128 bytes per instruction.
+      const long long row_base = (long long)tile * kBwdTileM + quad * 32;
+      for (int c0 = 0; c0 < p.Dpad; c0 += 32) {
+        const int cols = (p.Dpad - c0) < 32 ? (p.Dpad - c0) : 32;   // 16 or 32 (Dpad is a multiple of 16)
+        for (int h = 0; h * 16 < cols; h++) {
+          float v[16];
+          tmem_ld16(taddr + (uint32_t)(c0 + h * 16), v);
 #pragma unroll
-          for (int j = 0; j < 16; j += 4) {
-            const int c = c0 + j;
+          for (int j = 0; j < 4; j++) {
+            const uint32_t ci = (uint32_t)(h * 4 + j);
+            const uint32_t addr = stage_addr + (uint32_t)lane * 128u + ((ci ^ ((uint32_t)lane & 7u)) << 4);
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(__fmul_rn(v[4 * j], p.inv_sqrt_k)),
+                         "f"(__fmul_rn(v[4 * j + 1], p.inv_sqrt_k)), "f"(__fmul_rn(v[4 * j + 2], p.inv_sqrt_k)),
+                         "f"(__fmul_rn(v[4 * j + 3], p.inv_sqrt_k))
+                         : "memory");
+          }
+        }
+        __syncwarp();
+        const uint32_t ci = (uint32_t)lane & 7u;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const int rr = 4 * i + (lane >> 3);
+          const long long nn = row_base + rr;
+          const int c = c0 + (int)ci * 4;
+          float4 o;
+          const uint32_t addr = stage_addr + (uint32_t)rr * 128u + ((ci ^ ((uint32_t)rr & 7u)) << 4);
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(o.x), "=f"(o.y), "=f"(o.z), "=f"(o.w) : "r"(addr));
+          if (nn < p.N && (int)ci * 4 < cols) {
+            float* __restrict__ d = p.out + nn * p.D + c;
             if (vec && c + 4 <= p.D) {
-              __stcs(reinterpret_cast<float4*>(dst + c),
-                     make_float4(__fmul_rn(v[j], p.inv_sqrt_k), __fmul_rn(v[j + 1], p.inv_sqrt_k),
-                                 __fmul_rn(v[j + 2], p.inv_sqrt_k), __fmul_rn(v[j + 3], p.inv_sqrt_k)));
+              __stcs(reinterpret_cast<float4*>(d), o);
             } else {
+              const float ov[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-              for (int b = 0; b < 4; b++)
-                if (c + b < p.D) dst[c + b] = __fmul_rn(v[j + b], p.inv_sqrt_k);
+              for (int bb = 0; bb < 4; bb++)
+                if (c + bb < p.D) d[bb] = ov[bb];
             }
           }
         }
+        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
@@ -249,7 +296,7 @@ int exact_unpack_dequant_rp(const uint8_t* packed, int bits, const uint16_t* sca
   const int kpanels = kpad32 / 32;
   const long long a_bytes = (long long)kBwdTileM * kpanels * 128;
   const long long b_bytes = (long long)Dpad * kpanels * 128;
-  if (Dpad > 256 || b_bytes + 2 * a_bytes + 2048 > 200 * 1024)
+  if (Dpad > 256 || b_bytes + 2 * a_bytes + 4 * 4096 + 2048 > 200 * 1024)
     return fail(EXB_ERR_UNSUPPORTED, "unpack_dequant_rp: D = %lld, k = %lld exceed one resident B tile (D <= 256, small k)",
                 (long long)D, (long long)k);
   EXB_REQUIRE((N + kBwdTileM - 1) / kBwdTileM < 2147483647LL / kBwdTileM, "unpack_dequant_rp: too many rows");
@@ -270,12 +317,23 @@ int exact_unpack_dequant_rp(const uint8_t* packed, int bits, const uint16_t* sca
   p.N = N; p.D = (int)D; p.k = (int)k; p.Dpad = Dpad; p.kpanels = kpanels; p.kmma = (int)((k + 7) / 8); p.bits = bits;
   p.num_tiles = (int)((N + kBwdTileM - 1) / kBwdTileM);
   p.a_bytes = (unsigned)a_bytes; p.b_bytes = (unsigned)b_bytes; p.panel_b_bytes = (unsigned)(Dpad * 128);
+  const size_t dyn = (size_t)(b_bytes + 2 * a_bytes) + 4 * 4096 + 1024;  // + epilogue staging tiles
+  // CTAs per SM: bounded by shared memory (about 200 KB) and by the 512 TMEM columns of the SM.
+  int ctas = (int)((200 * 1024) / (dyn + 1024));
+  if (ctas > 4) ctas = 4;
+  if (ctas < 1) ctas = 1;
+  p.nbuf = 2;
   unsigned cols = 32;
   while (cols < (unsigned)(2 * Dpad)) cols <<= 1;
+  if (ctas >= 2 && cols * 2 > 512) {  // D > 128: one accumulator buffer per CTA, two CTAs overlap each other
+    p.nbuf = 1;
+    cols = 32;
+    while (cols < (unsigned)Dpad) cols <<= 1;
+  }
+  while (ctas > 1 && (unsigned)ctas * cols > 512) ctas--;
   p.tmem_cols = cols;
   p.inv_sqrt_k = (float)(1.0 / sqrt((double)k));
-  const size_t dyn = (size_t)(b_bytes + 2 * a_bytes) + 1024;
-  int grid = sm_count();
+  int grid = sm_count() * ctas;
   if (grid > p.num_tiles) grid = p.num_tiles;
 
 #define EXB_BWD_LAUNCH(BITS_)                                                                                   \

@@ -91,6 +91,28 @@ def run_rp(N, D, kept_frac, bits, reps):
             "peak_kind": kind}
 
 
+def run_unpack_rp(N, D, kept_frac, bits, reps):
+    """Fused unpack + dequantise + transpose projection (tcgen05): GB/s on the algorithmic bytes."""
+    dev = torch.device("cuda")
+    k = int(kept_frac * D + 0.999)
+    if not Q.unpack_rp_supported(D, k):
+        return {"op": "unpack_rp", "N": N, "D": D, "k": k, "bits": bits, "skipped": "shape not taken by the fused kernel"}
+    g = torch.Generator(device=dev).manual_seed(0)
+    y = torch.randn(N, k, device=dev, generator=g)
+    pk, sb, mb = Q.quantize_pack(y, bits, seed=1, offset=0)
+    from .ops import _rademacher
+    R = _rademacher(D, k, dev, torch.float32, seed=1, offset=0)
+    flush = torch.empty(64 * 1024 * 1024, device=dev) if N * D * 4 < 256e6 else None
+    call = lambda: Q.unpack_dequant_rp(pk, bits, sb, mb, N, R)
+    ms = _time(call, reps, flush)
+    nbytes = (pk.numel() - 1) + 4 * N + D * k * 4 + N * D * 4
+    peak, kind = _peak()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"op": "unpack_rp", "N": N, "D": D, "k": k, "bits": bits, "ms": round(ms, 4), "GB/s": round(gbs, 1),
+            "frac": round(gbs / peak, 4), "TFLOP/s": round(2.0 * N * D * k / (ms * 1e-3) / 1e12, 2), "peak": peak,
+            "peak_kind": kind}
+
+
 def run_spmm(nodes, avg_deg, K, reps, reduce):
     from . import graphs
     dev = torch.device("cuda")
@@ -111,7 +133,7 @@ def run_spmm(nodes, avg_deg, K, reps, reduce):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack"])
+    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp"])
     ap.add_argument("--kept-frac", type=float, nargs="*", default=[0.5, 0.125])
     ap.add_argument("--N", type=int, nargs="*", default=[100_000, 1_000_000, 10_000_000])
     ap.add_argument("--D", type=int, nargs="*", default=[64, 128, 256, 602])
@@ -128,6 +150,16 @@ def main():
     if a.op == "spmm":
         for K in a.K:
             print(json.dumps(run_spmm(a.nodes, a.avg_deg, K, a.reps, "mean")), flush=True)
+        return
+    if a.op == "unpack_rp":
+        for N in a.N:
+            for D in a.D:
+                if N * D * 4 > a.max_bytes:
+                    continue
+                for kf in a.kept_frac:
+                    for bits in a.bits:
+                        print(json.dumps(run_unpack_rp(N, D, kf, bits, a.reps)), flush=True)
+                torch.cuda.empty_cache()
         return
     if a.op == "rp_pack":
         for N in a.N:
