@@ -55,7 +55,8 @@ class ExactB200Error(RuntimeError):
 
 
 def lib_path():
-    return _build.LIB
+    """The in-tree library, or the file EXACT_B200_LIBRARY names."""
+    return os.environ.get("EXACT_B200_LIBRARY") or _build.LIB
 
 
 def load():

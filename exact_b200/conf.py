@@ -43,6 +43,11 @@ class QuantizationConfig:
         # Do not produce compressed copies that no backward formula reads (the SpMM's dense operand
         # when edge values need no gradient).  Outputs and gradients are unaffected.
         self.skip_dead_saves = True
+        # Aggregation followed by a linear layer with fewer outputs than inputs (the last GraphSAGE layer):
+        # back-propagate as (A^T g) W instead of A^T (g W), so the transposed aggregation and the
+        # gradient all-gather of a row-sharded run work on out_features columns.  Same result up to fp32
+        # reassociation.
+        self.aggregate_gradient_first = True
 
     def manual_seed(self, seed):
         self.seed = int(seed)

@@ -4,9 +4,9 @@ kept as library calls exactly as the reference keeps them."""
 import torch
 
 
-def linear_backward(grad_output, input, weight, bias=None):
-    """backward_func.cc:83-93."""
-    grad_input = grad_output.mm(weight)
+def linear_backward(grad_output, input, weight, bias=None, need_grad_input=True):
+    """backward_func.cc:83-93.  The input gradient is left out (None) when the caller has no use for it."""
+    grad_input = grad_output.mm(weight) if need_grad_input else None
     grad_weight = grad_output.t().mm(input)
     grad_bias = grad_output.sum(0) if bias is not None else None
     return grad_input, grad_weight, grad_bias

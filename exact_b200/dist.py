@@ -78,20 +78,23 @@ class sharded_spmm(torch.autograd.Function):
     transposed weights of spmm.cc:70-77 / 128-137."""
 
     @staticmethod
+    def gathered_operand(adj, x):
+        """All rows of the dense operand in local HBM."""
+        if x.requires_grad:
+            return adj.gather(x.contiguous(), "fw")
+        # a leaf that needs no gradient is the model's input features: in full-batch training the same
+        # tensor comes back every epoch, so its gathered copy is kept until the tensor is modified
+        c = adj._const_gather
+        if c is not None and c[0] is x and c[1] == x._version:
+            return c[2]
+        x_full = adj.gather(x.contiguous(), "fw_const").clone() if adj.world > 1 else x
+        adj._const_gather = (x, x._version, x_full)
+        return x_full
+
+    @staticmethod
     def forward(ctx, adj, x, reduce):
         ctx.adj = adj
-        if not x.requires_grad:
-            # a leaf that needs no gradient is the model's input features: in full-batch training the same
-            # tensor comes back every epoch, so its gathered copy is kept until the tensor is modified
-            c = adj._const_gather
-            if c is not None and c[0] is x and c[1] == x._version:
-                x_full = c[2]
-            else:
-                x_full = adj.gather(x.contiguous(), "fw_const").clone() if adj.world > 1 else x
-                adj._const_gather = (x, x._version, x_full)
-        else:
-            x_full = adj.gather(x.contiguous(), "fw")
-        return ext_spmm._spmm(adj.rowptr, adj.col, adj.value, x_full, reduce)
+        return ext_spmm._spmm(adj.rowptr, adj.col, adj.value, sharded_spmm.gathered_operand(adj, x), reduce)
 
     @staticmethod
     def backward(ctx, grad_out):

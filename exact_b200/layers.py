@@ -14,7 +14,7 @@ from .cpp_extension import quantization as ext_quantization
 from .ops import project_and_quantize, qbatch_norm, qlinear
 from .qscheme import QScheme
 from .sparse import SparseTensor, gcn_norm
-from .spmm import QMatmul, qmatmul
+from .spmm import QMatmul, aggregate_linear_applies, qaggregate_linear, qmatmul
 
 
 def _glorot(t):
@@ -242,8 +242,12 @@ class QSAGEConv(SAGEConv):
             quantized, randmat, _ = project_and_quantize(x[0], self.scheme, True)
         else:
             quantized, randmat = None, None
-        out = self.message_and_aggregate(edge_index, x, quantized=quantized, randmat=randmat)
-        out = self.lin_l(out)
+        if self.training and l_eq_r and aggregate_linear_applies(edge_index, x[0], self.lin_l.weight):
+            out = qaggregate_linear.apply(edge_index, x[0], self.lin_l.weight, self.lin_l.bias,
+                                          self.msg_and_aggr_func.reduce, self.lin_l.scheme)
+        else:
+            out = self.message_and_aggregate(edge_index, x, quantized=quantized, randmat=randmat)
+            out = self.lin_l(out)
         x_r = x[1]
         if self.root_weight and x_r is not None:
             out = out + self.lin_r(x_r, quantized, randmat)

@@ -180,35 +180,43 @@ class qlinear(Function):
     def backward(ctx, grad_output):
         quantized, weight, bias, randmat = ctx.saved
         ori_input_shape, q_input_shape, rp = ctx.other_args
-        grad_output = grad_output.contiguous()
-        projected = config.kept_frac < 1.0 and rp and randmat is not None
-        input = None
-        if (projected and not config.grad_weight_in_projected_space and config.fused_rp and config.compress_activation
-                and not config.simulate and not config.swap and len(ori_input_shape) == 2
-                and ext_quantization.unpack_rp_supported(ori_input_shape[1], q_input_shape[1])):
-            # dequantise + transpose projection in one kernel (reference order: g^T (Xq R^T))
-            q_input, q_bits, q_scale, q_min = quantized
-            input = ext_quantization.unpack_dequant_rp(q_input, q_bits, q_scale, q_min, q_input_shape[0], randmat)
-            projected = False
-        if input is None:
-            input = dequantize_activation(quantized, q_input_shape)
-        del quantized, ctx.saved
-        empty_cache(config.empty_cache_threshold)
-        if projected and config.grad_weight_in_projected_space:
-            # grad_W = g^T (Xq R^T) = (g^T Xq) R^T: the [N, D] reconstruction of ops.py:165-166 is never
-            # materialised and the large GEMM shrinks from 2*N*out*D to 2*N*out*k flops.
-            grad_weight = grad_output.t().mm(input).mm(randmat.t())
-            grad_input = grad_output.mm(weight) if ctx.needs_input_grad[0] else None
-            grad_bias = grad_output.sum(0) if bias is not None else None
-        else:
-            if projected:
-                input = rp2input(input, ori_input_shape, randmat)
-            grad_input, grad_weight, grad_bias = ext_backward_func.linear_backward(grad_output, input, weight, bias)
-            if not ctx.needs_input_grad[0]:
-                grad_input = None
-        del input, grad_output
-        empty_cache(config.empty_cache_threshold)
+        del ctx.saved
+        grad_input, grad_weight, grad_bias = linear_backward_from_compressed(
+            quantized, weight, bias, randmat, ori_input_shape, q_input_shape, rp, grad_output.contiguous(),
+            ctx.needs_input_grad[0])
         return grad_input, grad_weight, grad_bias, None, None, None, None
+
+
+def linear_backward_from_compressed(quantized, weight, bias, randmat, ori_input_shape, q_input_shape, rp,
+                                    grad_output, need_grad_input):
+    """ops.py:152-178: (grad_input, grad_weight, grad_bias) of y = x W^T + b from the compressed x."""
+    projected = config.kept_frac < 1.0 and rp and randmat is not None
+    input = None
+    if (projected and not config.grad_weight_in_projected_space and config.fused_rp and config.compress_activation
+            and not config.simulate and not config.swap and len(ori_input_shape) == 2
+            and ext_quantization.unpack_rp_supported(ori_input_shape[1], q_input_shape[1])):
+        # dequantise + transpose projection in one kernel (reference order: g^T (Xq R^T))
+        q_input, q_bits, q_scale, q_min = quantized
+        input = ext_quantization.unpack_dequant_rp(q_input, q_bits, q_scale, q_min, q_input_shape[0], randmat)
+        projected = False
+    if input is None:
+        input = dequantize_activation(quantized, q_input_shape)
+    del quantized
+    empty_cache(config.empty_cache_threshold)
+    if projected and config.grad_weight_in_projected_space:
+        # grad_W = g^T (Xq R^T) = (g^T Xq) R^T: the [N, D] reconstruction of ops.py:165-166 is never
+        # materialised and the large GEMM shrinks from 2*N*out*D to 2*N*out*k flops.
+        grad_weight = grad_output.t().mm(input).mm(randmat.t())
+        grad_input = grad_output.mm(weight) if need_grad_input else None
+        grad_bias = grad_output.sum(0) if bias is not None else None
+    else:
+        if projected:
+            input = rp2input(input, ori_input_shape, randmat)
+        grad_input, grad_weight, grad_bias = ext_backward_func.linear_backward(grad_output, input, weight, bias,
+                                                                               need_grad_input)
+    del input, grad_output
+    empty_cache(config.empty_cache_threshold)
+    return grad_input, grad_weight, grad_bias
 
 
 class qbatch_norm(Function):

@@ -144,6 +144,23 @@ def test_grad_weight_in_projected_space_equals_reference_order():
         assert torch.equal(grads[0][1], gset[1]) and torch.equal(grads[0][2], gset[2])
 
 
+@pytest.mark.parametrize("cfg_name,nodes", [("cfg3", 2000), ("cfg4", 3000)])
+def test_aggregate_gradient_first_is_a_reassociation(cfg_name, nodes):
+    """The last GraphSAGE layer (hidden -> classes) back-propagates (A^T g) W instead of A^T (g W): same
+    forward bits, same compressed tensors, gradients equal up to fp32 summation order."""
+    runs = []
+    for flag in (True, False):
+        config.aggregate_gradient_first = flag
+        try:
+            loss, out, grads, _, _, _ = run_model(cfg_name, nodes, seed=6, fused_rp=True)
+        finally:
+            config.aggregate_gradient_first = True
+        runs.append((loss, out, grads))
+    assert runs[0][0] == runs[1][0] and torch.equal(runs[0][1], runs[1][1])
+    for k, g in runs[0][2].items():
+        assert relfro(g, runs[1][2][k]) < 2e-5, k
+
+
 def test_eval_mode_bypasses_compression_and_state_dict_prefix():
     reset_config()
     net = QModule(models.GCN(16, 8, 4, 2, dropout=0.5, batch_norm=True)).cuda()
