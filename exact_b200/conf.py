@@ -43,10 +43,15 @@ class QuantizationConfig:
         # Do not produce compressed copies that no backward formula reads (the SpMM's dense operand
         # when edge values need no gradient).  Outputs and gradients are unaffected.
         self.skip_dead_saves = True
-        # Aggregation followed by a linear layer with fewer outputs than inputs (the last GraphSAGE layer):
-        # back-propagate as (A^T g) W instead of A^T (g W), so the transposed aggregation and the
-        # gradient all-gather of a row-sharded run work on out_features columns.  Same result up to fp32
-        # reassociation.
+        # Dense-layer GEMMs over node rows on the tensor cores with operands split into tf32 head and tail
+        # (fp32-equivalent accuracy); False: the library's fp32 GEMM.
+        self.linear_tensor_core = True
+        # QSAGEConv as one autograd node: same compressed tensors, one GEMM for lin_l + lin_r, the two
+        # input-gradient products accumulated in the GEMM epilogue.  Same result up to fp32 reassociation.
+        self.fuse_sage_layer = True
+        # Inside that node, when lin_l has fewer outputs than inputs (the last GraphSAGE layer),
+        # back-propagate (A^T g) W_l instead of A^T (g W_l): the transposed aggregation and the gradient
+        # all-gather of a row-sharded run work on out_features columns.
         self.aggregate_gradient_first = True
 
     def manual_seed(self, seed):

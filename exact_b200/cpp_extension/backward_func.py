@@ -1,12 +1,74 @@
 """Stand-in for the reference's `exact.cpp_extension.backward_func` module
-(exact/exact/cpp_extension/backward_func.cc:83-107): library GEMMs and ATen batch-norm pass-throughs,
-kept as library calls exactly as the reference keeps them."""
+(exact/exact/cpp_extension/backward_func.cc:83-107): the dense-layer GEMMs and ATen batch-norm
+pass-throughs.  The tall GEMMs (rows = nodes) go to the tensor-core kernel with fp32-equivalent accuracy
+(exact_linear_forward); the weight-gradient reductions and unsupported shapes stay library GEMMs."""
 import torch
+
+from .. import _lib
+from ..conf import config
+
+
+def _tc_ok(a):
+    return (config.linear_tensor_core and a.is_cuda and a.dtype == torch.float32 and a.dim() == 2
+            and a.size(0) >= 1024)
+
+
+def _rows16(a):
+    """`a` with 16-byte aligned rows: itself when its pitch already is, else a zero-padded copy."""
+    if a.stride(1) == 1 and a.stride(0) % 4 == 0 and a.stride(0) >= a.size(1) and a.data_ptr() % 16 == 0:
+        return a
+    K = a.size(1)
+    out = a.new_zeros((a.size(0), (K + 3) // 4 * 4))
+    out[:, :K].copy_(a)
+    return out[:, :K]
+
+
+def linear_forward(a, weight, bias=None, a2=None, weight2=None, out=None, accumulate=False):
+    """a @ weight.T (+ a2 @ weight2.T) (+ bias), optionally added to `out`: F.linear of ops.py:150 and the
+    g W product of backward_func.cc:86 (pass weight.t()).  fp32 in and out."""
+    if not _tc_ok(a) or (a2 is not None and not _tc_ok(a2)):
+        r = torch.nn.functional.linear(a, weight, bias)
+        if a2 is not None:
+            r = r.addmm_(a2, weight2.t())
+        if out is not None:
+            return out.add_(r) if accumulate else out.copy_(r)
+        return r
+    lib = _lib.load()
+    M, K = a.shape
+    N = weight.size(0)
+    a = _rows16(a)
+    w = weight if weight.stride(1) == 1 else weight.contiguous()
+    K2 = 0
+    if a2 is not None:
+        K2 = a2.size(1)
+        a2 = _rows16(a2)
+        w2 = weight2 if weight2.stride(1) == 1 else weight2.contiguous()
+    if bias is not None:
+        bias = bias.contiguous()
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        accumulate = False
+    assert out.shape == (M, N) and out.stride(1) == 1
+    for n0 in range(0, N, 256):
+        n1 = min(N, n0 + 256)
+        ws = torch.empty(int(lib.exact_linear_workspace_bytes(n1 - n0, K, K2)), dtype=torch.uint8, device=a.device)
+        wb, cb = w[n0:n1], out[:, n0:n1]
+        nbytes = 4 * (M * (K + K2) + (n1 - n0) * (K + K2) + M * (n1 - n0) * (2 if accumulate else 1))
+        _lib.invoke("exact_linear_forward", nbytes, _lib.ptr(a), M, K, a.stride(0), _lib.ptr(wb), wb.stride(0),
+                    _lib.ptr(a2) if K2 else None, K2, a2.stride(0) if K2 else 0,
+                    _lib.ptr(w2[n0:n1]) if K2 else None, w2.stride(0) if K2 else 0, n1 - n0,
+                    _lib.ptr(bias[n0:n1]) if bias is not None else None, 1 if accumulate else 0, _lib.ptr(ws),
+                    _lib.ptr(cb), out.stride(0), _lib.stream_ptr())
+        if config.check_device_status:
+            status = int(ws[:4].view(torch.int32).item())
+            if status != 0:
+                raise _lib.ExactB200Error(f"linear_forward: device status {status} (a bounded on-chip wait expired)")
+    return out
 
 
 def linear_backward(grad_output, input, weight, bias=None, need_grad_input=True):
     """backward_func.cc:83-93.  The input gradient is left out (None) when the caller has no use for it."""
-    grad_input = grad_output.mm(weight) if need_grad_input else None
+    grad_input = linear_forward(grad_output, weight.t()) if need_grad_input else None
     grad_weight = grad_output.t().mm(input)
     grad_bias = grad_output.sum(0) if bias is not None else None
     return grad_input, grad_weight, grad_bias

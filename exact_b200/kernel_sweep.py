@@ -113,6 +113,30 @@ def run_unpack_rp(N, D, kept_frac, bits, reps):
             "peak_kind": kind}
 
 
+def run_linear(M, K, N, reps):
+    """Dense-layer GEMM (tf32 head/tail split, tcgen05) against the library fp32 GEMM: ms, TFLOP/s, error vs fp64."""
+    from .cpp_extension import backward_func as B
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    a = torch.randn(M, K, device=dev, generator=g)
+    w = torch.randn(N, K, device=dev, generator=g)
+    b = torch.randn(N, device=dev, generator=g)
+    flush = torch.empty(64 * 1024 * 1024, device=dev) if M * (K + N) * 4 < 256e6 else None
+    ms = _time(lambda: B.linear_forward(a, w, b), reps, flush)
+    ms_lib = _time(lambda: torch.nn.functional.linear(a, w, b), reps, flush)
+    rows = min(M, 20000)
+    ref = a[:rows].double() @ w.double().t() + b.double()
+    err = float((B.linear_forward(a, w, b)[:rows].double() - ref).norm() / ref.norm())
+    err_lib = float((torch.nn.functional.linear(a, w, b)[:rows].double() - ref).norm() / ref.norm())
+    nbytes = 4 * (M * K + N * K + M * N)
+    peak, kind = _peak()
+    return {"op": "linear", "M": M, "K": K, "N": N, "ms": round(ms, 4), "library_fp32_ms": round(ms_lib, 4),
+            "TFLOP/s": round(2.0 * M * K * N / (ms * 1e-3) / 1e12, 1),
+            "tensor_TFLOP/s": round(6.0 * M * K * N / (ms * 1e-3) / 1e12, 1),
+            "GB/s": round(nbytes / (ms * 1e-3) / 1e9, 1), "frac_hbm": round(nbytes / (ms * 1e-3) / 1e9 / peak, 4),
+            "rel_err_vs_fp64": err, "library_rel_err_vs_fp64": err_lib, "peak_kind": kind}
+
+
 def run_spmm(nodes, avg_deg, K, reps, reduce):
     from . import graphs
     dev = torch.device("cuda")
@@ -133,7 +157,7 @@ def run_spmm(nodes, avg_deg, K, reps, reduce):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp"])
+    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp", "linear"])
     ap.add_argument("--kept-frac", type=float, nargs="*", default=[0.5, 0.125])
     ap.add_argument("--N", type=int, nargs="*", default=[100_000, 1_000_000, 10_000_000])
     ap.add_argument("--D", type=int, nargs="*", default=[64, 128, 256, 602])
@@ -150,6 +174,12 @@ def main():
     if a.op == "spmm":
         for K in a.K:
             print(json.dumps(run_spmm(a.nodes, a.avg_deg, K, a.reps, "mean")), flush=True)
+        return
+    if a.op == "linear":
+        for M in a.N:
+            for K in a.D:
+                for N in a.K:
+                    print(json.dumps(run_linear(M, K, N, a.reps)), flush=True)
         return
     if a.op == "unpack_rp":
         for N in a.N:

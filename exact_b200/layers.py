@@ -14,7 +14,7 @@ from .cpp_extension import quantization as ext_quantization
 from .ops import project_and_quantize, qbatch_norm, qlinear
 from .qscheme import QScheme
 from .sparse import SparseTensor, gcn_norm
-from .spmm import QMatmul, aggregate_linear_applies, qaggregate_linear, qmatmul
+from .spmm import QMatmul, qmatmul, qsage_layer, sage_layer_applies
 
 
 def _glorot(t):
@@ -238,16 +238,16 @@ class QSAGEConv(SAGEConv):
             l_eq_r = True
         else:
             l_eq_r = False
+        if l_eq_r and self.training and not self.normalize and sage_layer_applies(edge_index):
+            return qsage_layer.apply(edge_index, x[0], self.lin_l.weight, self.lin_l.bias,
+                                     self.lin_r.weight if self.root_weight else None,
+                                     self.msg_and_aggr_func.reduce, self.scheme, self.lin_l.scheme)
         if l_eq_r and self.training:
             quantized, randmat, _ = project_and_quantize(x[0], self.scheme, True)
         else:
             quantized, randmat = None, None
-        if self.training and l_eq_r and aggregate_linear_applies(edge_index, x[0], self.lin_l.weight):
-            out = qaggregate_linear.apply(edge_index, x[0], self.lin_l.weight, self.lin_l.bias,
-                                          self.msg_and_aggr_func.reduce, self.lin_l.scheme)
-        else:
-            out = self.message_and_aggregate(edge_index, x, quantized=quantized, randmat=randmat)
-            out = self.lin_l(out)
+        out = self.message_and_aggregate(edge_index, x, quantized=quantized, randmat=randmat)
+        out = self.lin_l(out)
         x_r = x[1]
         if self.root_weight and x_r is not None:
             out = out + self.lin_r(x_r, quantized, randmat)

@@ -174,6 +174,8 @@ class qlinear(Function):
         ctx.scheme = scheme
         ctx.saved = quantized, weight, bias, randmat
         ctx.other_args = ori_input_shape, proj_input_shape, rp
+        if input.dim() == 2:
+            return ext_backward_func.linear_forward(input, weight, bias)
         return F.linear(input, weight, bias)
 
     @staticmethod
@@ -207,7 +209,7 @@ def linear_backward_from_compressed(quantized, weight, bias, randmat, ori_input_
         # grad_W = g^T (Xq R^T) = (g^T Xq) R^T: the [N, D] reconstruction of ops.py:165-166 is never
         # materialised and the large GEMM shrinks from 2*N*out*D to 2*N*out*k flops.
         grad_weight = grad_output.t().mm(input).mm(randmat.t())
-        grad_input = grad_output.mm(weight) if need_grad_input else None
+        grad_input = ext_backward_func.linear_forward(grad_output, weight.t()) if need_grad_input else None
         grad_bias = grad_output.sum(0) if bias is not None else None
     else:
         if projected:

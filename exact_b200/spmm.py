@@ -5,6 +5,7 @@ import torch.nn.functional as F
 from torch.autograd.function import Function
 
 from .conf import config
+from .cpp_extension import backward_func as ext_backward_func
 from .cpp_extension import spmm as ext_spmm
 from .ops import linear_backward_from_compressed, project_and_quantize, qspmm_mean, qspmm_sum
 from .qscheme import QScheme
@@ -78,55 +79,70 @@ def _aggregate_transposed(src, grad, reduce):
     return ext_spmm._spmm(t_ptr, t_col, t_w, grad, "sum")
 
 
-class qaggregate_linear(Function):
-    """y = reduce(A, x) W^T + b, the aggregation + lin_l pair of QSAGEConv (layers.py:163-166), as one
-    autograd node.  Forward and the saved compressed tensors are those of QMatmul followed by QLinear.
-    Backward uses A^T (g W) = (A^T g) W: the transposed aggregation (and, row-sharded, the gradient
-    all-gather before it) runs on the out_features columns of g instead of the in_features columns of
-    g W.  It is taken when out_features < in_features; the result differs from the two-node order by
-    fp32 reassociation only."""
+class qsage_layer(Function):
+    """y = reduce(A, x) W_l^T + b (+ x W_r^T): the aggregation, lin_l and lin_r of QSAGEConv
+    (layers.py:153-170) as one autograd node.  The compressed tensors saved are those of the separate
+    nodes (x once, shared by the aggregation and lin_r; reduce(A, x) for lin_l) and are drawn in the same
+    order.  What changes is the dense arithmetic around them:
+      forward   one GEMM over the concatenated operands [reduce(A, x) | x] [W_l | W_r]^T + b;
+      backward  grad_x = A^T (g W_l) + g W_r, with the transposed aggregation applied to g first when
+                out_features < in_features ((A^T g) W_l: the SpMM, and the gradient all-gather of a
+                row-sharded run, then work on out_features columns), and the second product accumulated
+                into the first by the GEMM's epilogue.
+    Results differ from the separate nodes by fp32 reassociation only."""
 
     @staticmethod
-    def forward(ctx, src, x, weight, bias, reduce, lin_scheme):
+    def forward(ctx, src, x, w_l, b_l, w_r, reduce, scheme_x, scheme_l):
+        # the input, compressed once (layers.py:153-159)
+        q_x, randmat_x, proj_x = project_and_quantize(x, scheme_x, True)
+        if w_r is None:
+            q_x = randmat_x = None   # drawn (the noise stream stays that of the separate nodes), read by nothing
         agg = _aggregate(src, x, reduce)
-        quantized, randmat, proj_shape = project_and_quantize(agg, lin_scheme, True)
+        q_agg, randmat_agg, proj_agg = project_and_quantize(agg, scheme_l, True)
         empty_cache(config.empty_cache_threshold)
         ctx.src, ctx.reduce = src, reduce
-        ctx.saved = quantized, weight, bias, randmat
-        ctx.other_args = agg.shape, proj_shape
-        return F.linear(agg, weight, bias)
+        ctx.saved = q_x, randmat_x, q_agg, randmat_agg, w_l, b_l, w_r
+        ctx.other_args = x.shape, proj_x, proj_agg
+        return ext_backward_func.linear_forward(agg, w_l, b_l, a2=x if w_r is not None else None, weight2=w_r)
 
     @staticmethod
     def backward(ctx, grad_output):
-        quantized, weight, bias, randmat = ctx.saved
-        ori_shape, proj_shape = ctx.other_args
+        q_x, randmat_x, q_agg, randmat_agg, w_l, b_l, w_r = ctx.saved
+        x_shape, proj_x, proj_agg = ctx.other_args
         del ctx.saved
-        grad_output = grad_output.contiguous()
-        _, grad_weight, grad_bias = linear_backward_from_compressed(
-            quantized, weight, bias, randmat, ori_shape, proj_shape, True, grad_output, False)
+        g = grad_output.contiguous()
+        _, grad_w_l, grad_b = linear_backward_from_compressed(q_agg, w_l, b_l, randmat_agg, x_shape, proj_agg, True,
+                                                              g, False)
+        grad_w_r = None
+        if w_r is not None:
+            _, grad_w_r, _ = linear_backward_from_compressed(q_x, w_r, None, randmat_x, x_shape, proj_x, True, g,
+                                                             False)
         grad_x = None
         if ctx.needs_input_grad[1]:
-            out_f = grad_output.size(1)
-            pad = (-out_f) % 4   # whole 128-bit column groups for the gather
-            if pad:
-                g = grad_output.new_zeros((grad_output.size(0), out_f + pad))
-                g[:, :out_f].copy_(grad_output)
-                w = weight.new_zeros((out_f + pad, weight.size(1)))
-                w[:out_f].copy_(weight)
+            out_f, in_f = w_l.shape
+            if out_f < in_f and config.aggregate_gradient_first:
+                pad = (-out_f) % 4   # whole 128-bit column groups for the gather
+                gp, wp = g, w_l
+                if pad:
+                    gp = g.new_zeros((g.size(0), out_f + pad))
+                    gp[:, :out_f].copy_(g)
+                    wp = w_l.new_zeros((out_f + pad, in_f))
+                    wp[:out_f].copy_(w_l)
+                t = _aggregate_transposed(ctx.src, gp, ctx.reduce)
+                grad_x = ext_backward_func.linear_forward(t, wp.t(), None, a2=g if w_r is not None else None,
+                                                          weight2=w_r.t() if w_r is not None else None)
             else:
-                g, w = grad_output, weight
-            grad_x = _aggregate_transposed(ctx.src, g, ctx.reduce).mm(w)
-        return None, grad_x, grad_weight, grad_bias, None, None
+                grad_x = _aggregate_transposed(ctx.src, ext_backward_func.linear_forward(g, w_l.t()), ctx.reduce)
+                if w_r is not None:
+                    grad_x = ext_backward_func.linear_forward(g, w_r.t(), None, out=grad_x, accumulate=True)
+        return None, grad_x, grad_w_l, grad_b, grad_w_r, None, None, None
 
 
-def aggregate_linear_applies(src, x, weight):
-    """Whether the one-node aggregation + linear is taken: dense-operand gradient wanted, fewer output
-    than input features, no edge-value gradient, and the aggregation's own compressed copy (which only
-    the edge-value gradient reads) not being kept."""
+def sage_layer_applies(src):
+    """Whether QSAGEConv runs as the one-node layer: no edge-value gradient, and the aggregation's own
+    compressed copy (read only by the edge-value gradient) not being kept."""
     from .dist import ShardedSparseTensor
-    if not (config.aggregate_gradient_first and config.skip_dead_saves and x.requires_grad):
-        return False
-    if weight.size(0) >= weight.size(1):
+    if not (config.fuse_sage_layer and config.skip_dead_saves):
         return False
     if isinstance(src, ShardedSparseTensor):
         return True

@@ -175,6 +175,25 @@ EXACT_API int exact_unpack_dequant_rp(const uint8_t* packed, int bits, const uin
                                       const uint16_t* min_bf16, int64_t N, int64_t k, const float* R, int64_t D,
                                       void* workspace, float* out, void* stream);
 
+/* Dense layer GEMM with fp32-equivalent accuracy on the tensor cores (each operand split into a tf32
+ * head and tail, three tcgen05 MMAs per tile, fp32 accumulation):
+ *     C[M, N] (+)= A[M, K] B[N, K]^T  (+ A2[M, K2] B2[N, K2]^T)  (+ bias[N])
+ * Replaces the fp32 cuBLAS GEMMs of the quantised linear layer: F.linear(input, weight, bias) in
+ * qlinear.forward (exact/exact/ops.py:150) with A = input, B = weight [out, in]; and
+ * grad_input = grad_output.mm(weight) of linear_backward (exact/exact/cpp_extension/backward_func.cc:86)
+ * with A = grad_output, B = weight^T.  The optional second pair sums two layers that share their output,
+ * W_l mean_j(x_j) + W_r x of the GraphSAGE layer (exact/exact/layers.py:163-170), in one pass.
+ *   lda / ldb / lda2 / ldb2 / ldc: row pitches in elements.  A (and A2) must be 16-byte aligned with
+ *   lda % 4 == 0; N <= 256 per call (wider outputs: one call per 256-column block of B / C); other
+ *   shapes return code 3 and the caller uses a library GEMM.  accumulate != 0 adds to C.
+ *   workspace: exact_linear_workspace_bytes(N, K, K2) bytes, 256-byte aligned; its first int32 is the
+ *   status word (see exact_rp_quantize_pack). */
+EXACT_API int64_t exact_linear_workspace_bytes(int64_t N, int64_t K, int64_t K2);
+EXACT_API int exact_linear_forward(const float* A, int64_t M, int64_t K, int64_t lda, const float* B, int64_t ldb,
+                                   const float* A2, int64_t K2, int64_t lda2, const float* B2, int64_t ldb2,
+                                   int64_t N, const float* bias, int accumulate, void* workspace, float* C,
+                                   int64_t ldc, void* stream);
+
 /* The random matrix of input2rp (exact/exact/ops.py:107-118, gen_rad_mat at ops.py:112-114):
  * out [D, k] row-major fp32, entries +-1/sqrt(k).  Sign i (row-major index) is bit i % 128 of the
  * Philox4x32-10 block with counter (i / 128, offset) and key `seed`, instead of a draw from torch's

@@ -145,20 +145,27 @@ def test_grad_weight_in_projected_space_equals_reference_order():
 
 
 @pytest.mark.parametrize("cfg_name,nodes", [("cfg3", 2000), ("cfg4", 3000)])
-def test_aggregate_gradient_first_is_a_reassociation(cfg_name, nodes):
-    """The last GraphSAGE layer (hidden -> classes) back-propagates (A^T g) W instead of A^T (g W): same
-    forward bits, same compressed tensors, gradients equal up to fp32 summation order."""
+def test_one_node_sage_layer_is_a_reassociation(cfg_name, nodes):
+    """QSAGEConv as one autograd node (one GEMM for lin_l + lin_r; (A^T g) W_l in the last layer) against
+    the separate QMatmul / QLinear nodes: the same compressed tensors drawn in the same order, results
+    equal up to fp32 summation order.  One stochastic-rounding code of a saved INT2 tensor that lands on
+    the other side of its threshold moves a weight gradient of this 2000-row problem by about 0.5 %,
+    hence the looser bound on the gradients."""
     runs = []
-    for flag in (True, False):
-        config.aggregate_gradient_first = flag
+    for fuse, first in ((True, True), (True, False), (False, True)):
+        config.fuse_sage_layer, config.aggregate_gradient_first = fuse, first
         try:
             loss, out, grads, _, _, _ = run_model(cfg_name, nodes, seed=6, fused_rp=True)
         finally:
-            config.aggregate_gradient_first = True
+            config.fuse_sage_layer, config.aggregate_gradient_first = True, True
         runs.append((loss, out, grads))
+    # inside the node the order of the backward products does not touch the forward pass
     assert runs[0][0] == runs[1][0] and torch.equal(runs[0][1], runs[1][1])
     for k, g in runs[0][2].items():
-        assert relfro(g, runs[1][2][k]) < 2e-5, k
+        assert relfro(g, runs[1][2][k]) < 5e-5, (k, relfro(g, runs[1][2][k]))
+    assert abs(runs[0][0] - runs[2][0]) < 1e-5 * abs(runs[2][0]) and relfro(runs[0][1], runs[2][1]) < 1e-5
+    for k, g in runs[0][2].items():
+        assert relfro(g, runs[2][2][k]) < 3e-2, (k, relfro(g, runs[2][2][k]))
 
 
 def test_eval_mode_bypasses_compression_and_state_dict_prefix():
