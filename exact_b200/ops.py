@@ -208,7 +208,7 @@ def linear_backward_from_compressed(quantized, weight, bias, randmat, ori_input_
     if projected and config.grad_weight_in_projected_space:
         # grad_W = g^T (Xq R^T) = (g^T Xq) R^T: the [N, D] reconstruction of ops.py:165-166 is never
         # materialised and the large GEMM shrinks from 2*N*out*D to 2*N*out*k flops.
-        grad_weight = grad_output.t().mm(input).mm(randmat.t())
+        grad_weight = ext_backward_func.rows_reduce_mm(grad_output, input).mm(randmat.t())
         grad_input = ext_backward_func.linear_forward(grad_output, weight.t()) if need_grad_input else None
         grad_bias = grad_output.sum(0) if bias is not None else None
     else:

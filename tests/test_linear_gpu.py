@@ -100,3 +100,12 @@ def test_small_or_disabled_uses_library():
         assert torch.equal(B.linear_forward(a, w), torch.nn.functional.linear(a, w))
     finally:
         config.linear_tensor_core = True
+
+
+@pytest.mark.parametrize("M,out,k", [(40037, 64, 32), (70000, 47, 13), (1000, 64, 32)])
+def test_rows_reduce_mm(M, out, k):
+    """The weight-gradient reduction g^T x (backward_func.cc:87) as a batched product + sum."""
+    g, x = t(normal(M, out, 1)), t(normal(M, k, 2))
+    ref = g.double().t() @ x.double()
+    got = B.rows_reduce_mm(g, x)
+    assert got.shape == (out, k) and relfro(got, ref) < 1e-6
