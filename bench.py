@@ -147,6 +147,7 @@ def run_b200(args):
     config.activation_compression_bits = [c["bits"]]
     config.kept_frac = c["kept_frac"]
     config.manual_seed(0)
+    config.compact_gather = not args.dense_gather
     net = QModule(cls(c["feats"], c["hidden"], c["classes"], c["layers"], dropout=c["dropout"],
                       batch_norm=c["batch_norm"])).to(dev).train()
     opt = torch.optim.Adam(net.parameters(), lr=0.002)
@@ -210,6 +211,9 @@ def run_b200(args):
     if rank == 0 and not args.no_kernels:
         kern = kernel_bandwidths(torch, Q, _lib, dev, hbm_peak)
 
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
     # dominant kernel of the epoch by device time
@@ -236,6 +240,7 @@ def run_b200(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(c, n), "nodes": n, "directed_edges": nnz, "parallelism": f"rows/{world}",
+                   "exchange": "none" if world == 1 else ("dense rows" if args.dense_gather else "zero-compacted rows"),
                    "l2": "inputs larger than L2" if n * c["hidden"] * 4 > 126e6 else "working set fits L2",
                    "setup_s": round(setup_s, 1)},
         "e2e": {"value": round(args.steps / (ms_e2e * 1e-3), 4), "unit": "epoch/s",
@@ -378,6 +383,7 @@ def main():
     ap.add_argument("--cpu-nodes", type=int, default=200000, help="nodes of the bounded sample the CPU baseline runs")
     ap.add_argument("--no-kernels", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--dense-gather", action="store_true", help="N > 1: exchange dense rows (no zero compaction)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

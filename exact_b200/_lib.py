@@ -42,6 +42,9 @@ SIGNATURES = {
     "exact_unpack_rp_workspace_bytes": (c_i64, [c_i64, c_i64]),
     "exact_unpack_dequant_rp": (c_int, [c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_i64, c_ptr, c_ptr, c_ptr]),
     "exact_rademacher": (c_int, [c_u64, c_u64, c_i64, c_i64, c_ptr, c_ptr]),
+    "exact_rows_mask_count": (c_int, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr]),
+    "exact_rows_compact_write": (c_int, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr]),
+    "exact_rows_expand": (c_int, [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_i64, c_i64, c_ptr, c_i64, c_ptr]),
     "exact_linear_workspace_bytes": (c_i64, [c_i64, c_i64, c_i64]),
     "exact_linear_forward": (c_int, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_i64, c_ptr, c_i64, c_i64, c_ptr, c_i64,
                                      c_i64, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_ptr]),

@@ -46,6 +46,10 @@ class QuantizationConfig:
         # Dense-layer GEMMs over node rows on the tensor cores with operands split into tf32 head and tail
         # (fp32-equivalent accuracy); False: the library's fp32 GEMM.
         self.linear_tensor_core = True
+        # Row-sharded aggregation: send operands that are mostly exact zeros (ReLU + dropout outputs and
+        # gradients that passed their masks) zero-compacted; shards denser than the bound go as they are.
+        self.compact_gather = True
+        self.compact_gather_max_density = 0.6
         # QSAGEConv as one autograd node: same compressed tensors, one GEMM for lin_l + lin_r, the two
         # input-gradient products accumulated in the GEMM epilogue.  Same result up to fp32 reassociation.
         self.fuse_sage_layer = True

@@ -12,6 +12,7 @@ import torch
 import torch.distributed as dist
 
 from .conf import config
+from .cpp_extension import rows as ext_rows
 from .cpp_extension import spmm as ext_spmm
 from .sparse import SparseTensor
 
@@ -45,6 +46,7 @@ class ShardedSparseTensor:
         self.t_col = t_col[f0:f1].to(index_dtype).contiguous()
         self.t_w = None if t_w is None else t_w[f0:f1].contiguous()
         self._gather_buf = {}
+        self._dense_streak = {}     # tag -> calls left before compaction is tried again after a dense operand
         self._const_gather = None   # (tensor, version, gathered): input features do not change between epochs
 
     @property
@@ -54,16 +56,34 @@ class ShardedSparseTensor:
     def size(self, dim):
         return self.local_rows if dim == 0 else self.n_global
 
-    def gather(self, x_local, tag):
-        """All-gather of the row shards of an [local_rows, K] matrix -> [n_global, K] in local HBM."""
-        K = x_local.size(1)
-        key = (tag, K, x_local.dtype)
+    def _buffer(self, key, shape, dtype, device):
         buf = self._gather_buf.get(key)
-        if buf is None:
-            buf = torch.empty((self.world * self.shard, K), dtype=x_local.dtype, device=x_local.device)
+        if buf is None or buf.shape != torch.Size(shape):
+            buf = torch.empty(shape, dtype=dtype, device=device)
             self._gather_buf[key] = buf
+        return buf
+
+    def gather(self, x_local, tag):
+        """All rows of an [local_rows, K] matrix in local HBM: [n_global, K].  Operands that are mostly
+        exact zeros (ReLU + dropout outputs, gradients that passed their masks) cross NVLink
+        zero-compacted and are expanded on arrival; others go as they are."""
         if self.world == 1:
             return x_local
+        K = x_local.size(1)
+        if (config.compact_gather and x_local.dtype == torch.float32 and K % 32 == 0 and K >= 64):
+            left = self._dense_streak.get(tag, 0)
+            if left > 0:
+                self._dense_streak[tag] = left - 1
+            else:
+                out = self._gather_compacted(x_local, tag)
+                if out is not None:
+                    return out
+                self._dense_streak[tag] = 16
+        return self._gather_dense(x_local, tag)
+
+    def _gather_dense(self, x_local, tag):
+        K = x_local.size(1)
+        buf = self._buffer((tag, K, x_local.dtype), (self.world * self.shard, K), x_local.dtype, x_local.device)
         if x_local.size(0) != self.shard:   # the last shard is shorter: pad to the common size
             pad = buf[self.rank * self.shard:(self.rank + 1) * self.shard]
             pad[:x_local.size(0)].copy_(x_local)
@@ -71,6 +91,39 @@ class ShardedSparseTensor:
             x_local = pad
         dist.all_gather_into_tensor(buf, x_local.contiguous(), group=self.group)
         return buf[:self.n_global]
+
+    def _gather_compacted(self, x_local, tag):
+        """mask + row offsets + kept values of every shard, then one expansion into dense rows.  Returns
+        None (nothing sent yet beyond the counts) when some shard is too dense for this to pay."""
+        dev, K, W, S, R = x_local.device, x_local.size(1), x_local.size(1) // 32, self.shard, self.world
+        n_loc = x_local.size(0)
+        x_local = x_local.contiguous()
+        mask = self._buffer((tag, "mask_loc"), (S, W), torch.int32, dev)
+        rowcnt = self._buffer((tag, "rowcnt"), (S,), torch.int32, dev)
+        if n_loc < S:
+            mask[n_loc:].zero_()
+            rowcnt[n_loc:].zero_()
+        ext_rows.mask_count(x_local, mask[:n_loc], rowcnt[:n_loc])
+        rowoff = self._buffer((tag, "rowoff_loc"), (S + 1,), torch.int64, dev)
+        rowoff[:1].zero_()
+        torch.cumsum(rowcnt, 0, out=rowoff[1:])
+        counts = self._buffer((tag, "counts"), (R,), torch.int64, dev)
+        dist.all_gather_into_tensor(counts, rowoff[S:S + 1], group=self.group)
+        cap = int(counts.max().item())          # the one host synchronisation of the exchange
+        if cap > config.compact_gather_max_density * S * K:
+            return None
+        cap = max((cap + 255) // 256 * 256, 256)
+        vals = torch.empty(cap, dtype=torch.float32, device=dev)
+        ext_rows.compact_write(x_local, rowoff, vals)
+        vals_all = torch.empty(R * cap, dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(vals_all, vals, group=self.group)
+        rowoff_all = self._buffer((tag, "rowoff_all"), (R * (S + 1),), torch.int64, dev)
+        dist.all_gather_into_tensor(rowoff_all, rowoff, group=self.group)
+        mask_all = self._buffer((tag, "mask_all"), (R * S, W), torch.int32, dev)
+        dist.all_gather_into_tensor(mask_all, mask, group=self.group)
+        out = self._buffer((tag, K, x_local.dtype), (R * S, K), torch.float32, dev)
+        ext_rows.expand(mask_all, rowoff_all, vals_all, R * S, K, S, S + 1, cap, out)
+        return out[:self.n_global]
 
 
 class sharded_spmm(torch.autograd.Function):

@@ -194,6 +194,24 @@ EXACT_API int exact_linear_forward(const float* A, int64_t M, int64_t K, int64_t
                                    int64_t N, const float* bias, int accumulate, void* workspace, float* C,
                                    int64_t ldc, void* stream);
 
+/* Zero-compacted rows, the exchange format of the row-sharded aggregation.  No counterpart in the
+ * reference (it is single-GPU).  A shard x [n, K] fp32 (row pitch ldx, K % 32 == 0) whose entries are
+ * mostly exact zeros (outputs of ReLU + dropout, gradients that passed their masks) is sent as
+ *   mask   uint32 [n, K/32]  bit c % 32 of word c / 32: element (row, c) is kept (any of its 32 bits set,
+ *                            so only +0.0 is dropped and the round trip is bit-exact);
+ *   rowoff int64  [n + 1]    exclusive prefix sum of the rows' kept counts (the caller scans rowcnt);
+ *   vals   fp32   [rowoff[n]] the kept elements, row-major.
+ * exact_rows_mask_count writes mask and rowcnt [n]; exact_rows_compact_write writes vals;
+ * exact_rows_expand writes dense rows out [n, K] (row pitch ldo) from the concatenation of several shards:
+ * rows [b * block_rows, (b + 1) * block_rows) use rowoff + b * rowoff_stride and vals + b * vals_stride. */
+EXACT_API int exact_rows_mask_count(const float* x, int64_t n, int64_t K, int64_t ldx, uint32_t* mask,
+                                    int32_t* rowcnt, void* stream);
+EXACT_API int exact_rows_compact_write(const float* x, int64_t n, int64_t K, int64_t ldx, const int64_t* rowoff,
+                                       float* vals, void* stream);
+EXACT_API int exact_rows_expand(const uint32_t* mask, const int64_t* rowoff, const float* vals, int64_t n, int64_t K,
+                                int64_t block_rows, int64_t rowoff_stride, int64_t vals_stride, float* out,
+                                int64_t ldo, void* stream);
+
 /* The random matrix of input2rp (exact/exact/ops.py:107-118, gen_rad_mat at ops.py:112-114):
  * out [D, k] row-major fp32, entries +-1/sqrt(k).  Sign i (row-major index) is bit i % 128 of the
  * Philox4x32-10 block with counter (i / 128, offset) and key `seed`, instead of a draw from torch's

@@ -246,3 +246,26 @@ def spmm_bw_mat(rowptr, col, val, grad_out, n_cols, reduce="sum"):
         w = None if val is None else _f32(val)[perm]
     assert nnz == perm.size
     return spmm(colptr, row_t, w, grad_out, "sum")
+
+
+def rows_compact(x):
+    """Zero-compacted rows of x [n, K] fp32, K % 32 == 0 (the exchange format of the row-sharded
+    aggregation; no counterpart in the reference): mask uint32 [n, K/32] (bit c % 32 of word c / 32 set
+    when any bit of element c is set), rowoff int64 [n + 1], vals fp32 (kept elements, row-major)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n, K = x.shape
+    keep = x.view(np.uint32) != 0
+    weights = (np.uint64(1) << np.arange(32, dtype=np.uint64))
+    mask = (keep.reshape(n, K // 32, 32).astype(np.uint64) * weights).sum(-1).astype(np.uint32)
+    rowoff = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(keep.sum(1), out=rowoff[1:])
+    return mask, rowoff, x[keep]
+
+
+def rows_expand(mask, rowoff, vals, K):
+    """Inverse of rows_compact."""
+    n = mask.shape[0]
+    keep = ((mask[:, :, None] >> np.arange(32, dtype=np.uint32)) & 1).astype(bool).reshape(n, K)
+    out = np.zeros((n, K), dtype=np.float32)
+    out[keep] = vals[:rowoff[n]]
+    return out

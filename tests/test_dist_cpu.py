@@ -88,3 +88,74 @@ def test_shard_rows_are_multiples_of_eight():
     for n, w in ((2449029, 8), (2449029, 2), (100, 4), (7, 2)):
         s = shard_rows(n, w)
         assert s % 8 == 0 and s * w >= n and s * (w - 1) < n + 8 * w
+
+
+# ---- zero-compacted exchange: the CUDA kernels are replaced by their numpy restatement -----------------
+def _stub_rows(xdist):
+    import oracle
+
+    def mask_count(x, mask, rowcnt):
+        m, ro, _ = oracle.rows_compact(x.numpy())
+        mask.copy_(torch.from_numpy(m.view(np.int32)))
+        rowcnt.copy_(torch.from_numpy(np.diff(ro).astype(np.int32)))
+
+    def compact_write(x, rowoff, vals):
+        _, ro, v = oracle.rows_compact(x.numpy())
+        assert np.array_equal(ro, rowoff.numpy()[:ro.size])
+        vals[:v.size] = torch.from_numpy(v)
+
+    def expand(mask, rowoff, vals, n, K, block_rows, rowoff_stride, vals_stride, out):
+        for b in range(n // block_rows):
+            ro = rowoff.numpy()[b * rowoff_stride:b * rowoff_stride + block_rows + 1]
+            v = vals.numpy()[b * vals_stride:(b + 1) * vals_stride]
+            m = mask.numpy()[b * block_rows:(b + 1) * block_rows].view(np.uint32)
+            out[b * block_rows:(b + 1) * block_rows] = torch.from_numpy(oracle.rows_expand(m, ro, v, K))
+
+    xdist.ext_rows.mask_count, xdist.ext_rows.compact_write, xdist.ext_rows.expand = mask_count, compact_write, expand
+
+
+def _gather_worker(rank, world, port, n, K, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from exact_b200 import SparseTensor, config
+    from exact_b200 import dist as xdist
+    _stub_rows(xdist)
+    rowptr, col, _ = random_csr(n, n, 4 * n, 3, False)
+    row = np.repeat(np.arange(n), np.diff(rowptr))
+    full = SparseTensor(row=torch.from_numpy(row), col=torch.from_numpy(col), value=None, sparse_sizes=(n, n),
+                        is_sorted=True)
+    adj = xdist.shard_graph(full, "mean", rank, world)
+    sparse = normal(n, K, 7)
+    sparse[np.random.default_rng(8).random((n, K)) < 0.75] = 0.0
+    dense = normal(n, K, 9)
+    res = {}
+    config.compact_gather = True
+    res["sparse"] = adj.gather(torch.from_numpy(sparse[adj.row_start:adj.row_end]), "fw").clone()
+    res["streak_after_sparse"] = adj._dense_streak.get("fw", 0)
+    res["dense"] = adj.gather(torch.from_numpy(dense[adj.row_start:adj.row_end]), "bw").clone()
+    res["streak_after_dense"] = adj._dense_streak.get("bw", 0)
+    # while the streak lasts the dense route is taken without trying
+    res["dense_again"] = adj.gather(torch.from_numpy(dense[adj.row_start:adj.row_end]), "bw").clone()
+    res["streak_after_second"] = adj._dense_streak.get("bw", 0)
+    config.compact_gather = False
+    res["off"] = adj.gather(torch.from_numpy(sparse[adj.row_start:adj.row_end]), "fw").clone()
+    config.compact_gather = True
+    torch.save(res, os.path.join(result_dir, f"g{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_compacted_gather_equals_dense_gather(tmp_path):
+    n, K, world = 203, 64, 2        # 203 rows: the last shard is shorter than the first
+    port = _free_port()
+    mp.spawn(_gather_worker, args=(world, port, n, K, str(tmp_path)), nprocs=world, join=True)
+    sparse = normal(n, K, 7)
+    sparse[np.random.default_rng(8).random((n, K)) < 0.75] = 0.0
+    dense = normal(n, K, 9)
+    for r in range(world):
+        p = torch.load(os.path.join(tmp_path, f"g{r}.pt"))
+        assert np.array_equal(p["sparse"].numpy().view(np.uint32), sparse.view(np.uint32))
+        assert np.array_equal(p["off"].numpy(), sparse)
+        assert np.array_equal(p["dense"].numpy(), dense) and np.array_equal(p["dense_again"].numpy(), dense)
+        assert p["streak_after_sparse"] == 0 and p["streak_after_dense"] == 16 and p["streak_after_second"] == 15
