@@ -53,9 +53,9 @@ class QuantizationConfig:
         # QSAGEConv as one autograd node: same compressed tensors, one GEMM for lin_l + lin_r, the two
         # input-gradient products accumulated in the GEMM epilogue.  Same result up to fp32 reassociation.
         self.fuse_sage_layer = True
-        # Inside that node, when lin_l has fewer outputs than inputs (the last GraphSAGE layer),
-        # back-propagate (A^T g) W_l instead of A^T (g W_l): the transposed aggregation and the gradient
-        # all-gather of a row-sharded run work on out_features columns.
+        # Inside that node, when lin_l has no more outputs than inputs, back-propagate (A^T g) W_l instead
+        # of A^T (g W_l): the transposed aggregation (and the gradient exchange of a row-sharded run)
+        # works on g, which is narrower or sparser than g W_l.
         self.aggregate_gradient_first = True
 
     def manual_seed(self, seed):

@@ -16,16 +16,18 @@
 // element can turn its output row into NaN where an fp32 GEMM gives +-inf (inf times a tail of the
 // other sign).
 //
-// Structure (one CTA per SM, persistent over 128-row tiles of A, 10 warps):
+// Structure (one CTA per SM, persistent over 128-row tiles of A, 14 warps):
 //   warp 0     TMA producer.  Shared memory is a ring of six 32 KB slots; a 32-column K tile uses three
 //              consecutive slots: A (raw fp32 [128 x 32], 16 KB, the tail tile goes into the slot's other
 //              half), B_hi [Npad x 32] and B_lo [Npad x 32].  128-byte swizzle, no multicast.
-//   warps 2-5  converter: rewrite the raw A tile in place as a_hi and write a_lo beside it (same swizzled
+//              The A tile of four K tiles ahead is requested into L2 (tensor prefetch): A is read from
+//              HBM exactly once and the ring is only two K tiles deep.
+//   warps 2-9  converter: rewrite the raw A tile in place as a_hi and write a_lo beside it (same swizzled
 //              offsets), fence.proxy.async, signal.
 //   warp 1     MMA issuer: tcgen05.mma.cta_group::1.kind::tf32, M = 128, N = Npad, K = 8; per K tile
 //              8 MMAs (hi*hi, lo*hi) then release B_hi, 4 MMAs (hi*lo) then release A and B_lo.
 //              Accumulators are double-buffered in TMEM.
-//   warps 6-9  epilogue: tcgen05.ld -> per-warp staging tile in shared memory -> (+ bias, + old C)
+//   warps 10-13 epilogue: tcgen05.ld -> per-warp staging tile in shared memory -> (+ bias, + old C)
 //              -> coalesced global stores.
 // B_hi / B_lo are produced once per call from the (small) weight matrix by a preparation kernel.
 //
@@ -40,10 +42,12 @@ namespace exb {
 
 constexpr int kLinTileM = 128;
 constexpr int kLinTileK = 32;
-constexpr int kLinThreads = 320;
+constexpr int kLinConvWarps = 8;
+constexpr int kLinThreads = (2 + kLinConvWarps + 4) * 32;   // TMA, MMA, converters, epilogue
 constexpr int kLinSlots = 6;
 constexpr uint32_t kLinSlotBytes = 32 * 1024;
 constexpr uint32_t kLinHalf = 16 * 1024;        // raw / tail halves of an A slot
+constexpr int kLinPrefetch = 4;                 // K tiles of A requested into L2 ahead of their TMA load
 
 struct LinParams {
   float* C;
@@ -95,7 +99,7 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     for (int s = 0; s < kLinSlots; s++) {
       mbar_init(smem_u32(&s_full[s]), 1);
       mbar_init(smem_u32(&s_empty[s]), 1);
-      mbar_init(smem_u32(&s_conv[s]), 4);   // one arrival per converter warp
+      mbar_init(smem_u32(&s_conv[s]), kLinConvWarps);   // one arrival per converter warp
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(smem_u32(&s_tfull[b]), 1);
@@ -129,6 +133,14 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
               mbar_arrive_expect_tx(full, kLinHalf);
               if (kb < p.kblocks1) tma_load_2d(dst, &tm_a, kb * kLinTileK, tile * kLinTileM, full);
               else tma_load_2d(dst, &tm_a2, (kb - p.kblocks1) * kLinTileK, tile * kLinTileM, full);
+              // A comes from HBM exactly once: pull the tile that will be loaded kLinPrefetch K tiles from
+              // now into L2, so that its TMA load later pays L2 latency only (the ring holds two K tiles)
+              int pk = kb + kLinPrefetch, pt = tile;
+              if (pk >= p.kblocks) { pk -= p.kblocks; pt += step; }
+              if (pt < p.num_tiles && pk < p.kblocks) {
+                if (pk < p.kblocks1) tma_prefetch_2d(&tm_a, pk * kLinTileK, pt * kLinTileM);
+                else tma_prefetch_2d(&tm_a2, (pk - p.kblocks1) * kLinTileK, pt * kLinTileM);
+              }
             } else {
               mbar_arrive_expect_tx(full, b_bytes);
               tma_load_2d(dst, u == 1 ? &tm_bh : &tm_bl, kb * kLinTileK, 0, full);
@@ -192,9 +204,10 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         if (ok) umma_commit(smem_u32(&s_tfull[buf]));
       }
     }
-  } else if (warp < 6) {
-    // ---------------- converter: warps 2..5 ----------------
-    const int ct = threadIdx.x - 64;   // 0..127
+  } else if (warp < 2 + kLinConvWarps) {
+    // ---------------- converter: warps 2 .. 2 + kLinConvWarps - 1 ----------------
+    const int ct = threadIdx.x - 64;   // 0 .. 32 * kLinConvWarps - 1
+    constexpr int kPer = (int)(kLinHalf / 16) / (32 * kLinConvWarps);   // 16-byte chunks per thread
     int it = 0;
     bool ok = true;
     for (int tile = first; tile < p.num_tiles && ok; tile += step) {
@@ -204,8 +217,8 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         if (!mbar_wait(smem_u32(&s_full[s]), ph, abort_flag)) { ok = false; break; }
         const uint32_t base = ring + (uint32_t)s * kLinSlotBytes + (uint32_t)ct * 16u;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const uint32_t addr = base + (uint32_t)i * 2048u;
+        for (int i = 0; i < kPer; i++) {
+          const uint32_t addr = base + (uint32_t)i * (32u * kLinConvWarps * 16u);
           float a[4], h[4], l[4];
           asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a[0]), "=f"(a[1]), "=f"(a[2]), "=f"(a[3]) : "r"(addr));
 #pragma unroll
@@ -219,7 +232,7 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
       }
     }
   } else {
-    // ---------------- epilogue: warps 6..9 ----------------
+    // ---------------- epilogue: the last four warps ----------------
     const int quad = warp & 3;   // TMEM lanes 32*quad .. 32*quad+31
     const bool vec = (p.N & 3) == 0 && (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
     const uint32_t stage_addr = stage_base + (uint32_t)quad * 4096u;

@@ -120,12 +120,11 @@ class qsage_layer(Function):
         grad_x = None
         if ctx.needs_input_grad[1]:
             out_f, in_f = w_l.shape
-            from .dist import ShardedSparseTensor
-            sharded = isinstance(ctx.src, ShardedSparseTensor) and ctx.src.world > 1
-            # g has passed the ReLU / dropout masks (mostly zeros) while g W_l is dense: a row-sharded run
-            # that compacts what it exchanges gathers g also when the widths are equal
-            if config.aggregate_gradient_first and (out_f < in_f or (sharded and config.compact_gather
-                                                                       and out_f == in_f)):
+            # With out_features <= in_features the transposed aggregation runs on g itself: fewer (or as
+            # many) columns for the SpMM, one GEMM over [A^T g | g] instead of two, and, row-sharded, a
+            # gathered operand that has passed the ReLU / dropout masks (mostly zeros, sent compacted)
+            # instead of the dense g W_l.
+            if config.aggregate_gradient_first and out_f <= in_f:
                 pad = (-out_f) % 4   # whole 128-bit column groups for the gather
                 gp, wp = g, w_l
                 if pad:
