@@ -45,8 +45,12 @@ def long_row_plan(rowptr, threshold):
     return plan
 
 
-def _spmm(rowptr, col, value, mat, reduce):
-    """spmm.cc:12-18 -> spmm_cuda.cu:106-170."""
+REGROUP = 0x100   # EXACT_SPMM_REGROUP
+
+
+def _spmm(rowptr, col, value, mat, reduce, regroup=False):
+    """spmm.cc:12-18 -> spmm_cuda.cu:106-170.  `regroup`: the caller accepts a regrouped per-row fp32 sum
+    (narrow operands then gather two edges per load instruction)."""
     if not rowptr.is_cuda or not col.is_cuda or not mat.is_cuda:
         raise RuntimeError("rowptr, col and mat must be CUDA tensors")
     if rowptr.dim() != 1 or col.dim() != 1:
@@ -73,13 +77,14 @@ def _spmm(rowptr, col, value, mat, reduce):
     nbytes = nnz * K * 4 + nnz * (ib + (4 if value is not None else 0)) + (M + 1) * ib + M * K * 4
     thr = int(config.spmm_long_row)
     plan = long_row_plan(rowptr, thr) if thr > 0 else None
+    red = _lib.REDUCE[reduce] | (REGROUP if regroup else 0)
     if plan is None:
         _lib.invoke("exact_spmm", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), _lib.ptr(mat), M, K,
-                    _lib.REDUCE[reduce], _lib.ptr(out), _lib.stream_ptr())
+                    red, _lib.ptr(out), _lib.stream_ptr())
     else:
         scratch = torch.empty((plan["n_items"], K), dtype=torch.float32, device=mat.device)
         _lib.invoke("exact_spmm_split", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), _lib.ptr(mat),
-                    M, K, _lib.REDUCE[reduce], thr, _lib.ptr(plan["item_row"]), _lib.ptr(plan["item_begin"]),
+                    M, K, red, thr, _lib.ptr(plan["item_row"]), _lib.ptr(plan["item_begin"]),
                     _lib.ptr(plan["item_end"]), plan["n_items"], _lib.ptr(plan["long_row"]),
                     _lib.ptr(plan["long_item_ptr"]), plan["n_long"], _lib.ptr(scratch), _lib.ptr(out),
                     _lib.stream_ptr())

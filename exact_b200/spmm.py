@@ -71,12 +71,13 @@ def _aggregate(src, other, reduce):
 
 
 def _aggregate_transposed(src, grad, reduce):
-    """Gradient of reduce(A, other) with respect to `other` (spmm.cc:70-77, 128-137)."""
+    """Gradient of reduce(A, other) with respect to `other` (spmm.cc:70-77, 128-137).  Inside the one-node
+    layer the result is an fp32 regrouping of the separate nodes' anyway, so the SpMM may regroup too."""
     from .dist import ShardedSparseTensor
     if isinstance(src, ShardedSparseTensor):
-        return ext_spmm._spmm(src.t_rowptr, src.t_col, src.t_w, src.gather(grad, "bw"), "sum")
+        return ext_spmm._spmm(src.t_rowptr, src.t_col, src.t_w, src.gather(grad, "bw"), "sum", regroup=True)
     t_ptr, t_col, t_w = src.storage.transposed(reduce)
-    return ext_spmm._spmm(t_ptr, t_col, t_w, grad, "sum")
+    return ext_spmm._spmm(t_ptr, t_col, t_w, grad, "sum", regroup=True)
 
 
 class qsage_layer(Function):

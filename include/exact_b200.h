@@ -33,6 +33,11 @@ extern "C" {
 
 enum { EXACT_DTYPE_F32 = 0, EXACT_DTYPE_BF16 = 1 };
 enum { EXACT_REDUCE_SUM = 0, EXACT_REDUCE_MEAN = 1 };
+/* OR-ed into `reduce`: the caller accepts a per-row sum that is regrouped (two interleaved partial sums
+ * instead of strict edge order; same terms, fp32 reassociation).  Lets operands of at most 64 columns use a
+ * kernel that gathers two edges per load instruction.  Without it every row up to the long-row threshold
+ * is summed in edge order, bit-identical to the reference kernel. */
+enum { EXACT_SPMM_REGROUP = 0x100 };
 
 /* Library version (major * 100 + minor) and the last error message of the calling thread. */
 EXACT_API int exact_version(void);

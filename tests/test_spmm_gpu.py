@@ -95,3 +95,34 @@ def test_qmatmul_forward_and_grad(reduce, with_values):
         dense = dense / torch.from_numpy(np.maximum(np.diff(rowptr), 1)).cuda().float()[:, None]
     torch.testing.assert_close(out.detach(), dense @ t(mat), rtol=1e-4, atol=1e-4)
     torch.testing.assert_close(x.grad, dense.t() @ t(g), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("reduce", ["sum", "mean"])
+@pytest.mark.parametrize("with_values", [True, False])
+@pytest.mark.parametrize("K", [48, 64, 40, 16, 4])
+def test_regrouped_sum_for_narrow_operands(K, with_values, reduce):
+    """EXACT_SPMM_REGROUP: operands of at most 64 columns gather two edges per load instruction and add
+    (even edges) + (odd edges); the result equals the edge-order sum up to fp32 reassociation, hub rows
+    (cut into pieces) and empty rows included.  Wider operands ignore the flag and stay bit-exact."""
+    n = 4000
+    rng = np.random.default_rng(11)
+    hub = np.stack([np.zeros(1500, np.int64), rng.choice(n, 1500, replace=False)])
+    rest = rng.integers(0, n, (2, 30000))
+    rest = rest[:, rest[0] > 50]                                # rows 1..50 empty
+    e = np.concatenate([hub, rest], 1)
+    key = np.unique(e[0] * n + e[1])
+    row, col = key // n, key % n
+    rowptr = np.zeros(n + 1, np.int64)
+    np.cumsum(np.bincount(row, minlength=n), out=rowptr[1:])
+    val = rng.standard_normal(col.size).astype(np.float32) if with_values else None
+    mat = normal(n, K, 12)
+    ref = oracle.spmm(rowptr, col, val, mat, reduce)
+    out = S._spmm(t(rowptr), t(col), None if val is None else t(val), t(mat), reduce, regroup=True).cpu().numpy()
+    absval = np.ones(col.size, np.float32) if val is None else np.abs(val)
+    scale = oracle.spmm(rowptr, col, absval, np.abs(mat), reduce) + 1e-30
+    assert np.all(np.abs(out - ref) <= 2e-6 * scale)
+    assert np.array_equal(out[1:51], np.zeros((50, K), np.float32))
+    wide = normal(n, 128, 13)
+    strict = S._spmm(t(rowptr), t(col), None if val is None else t(val), t(wide), reduce).cpu().numpy()
+    flagged = S._spmm(t(rowptr), t(col), None if val is None else t(val), t(wide), reduce, regroup=True).cpu().numpy()
+    assert np.array_equal(strict, flagged)
