@@ -9,6 +9,8 @@
 // element 128*c + 4*l + j.  The layout is private: the reference's mask never leaves its extension
 // either (quantization.cc:71,92,119), only outputs and gradients are observable.
 #include "common.cuh"
+#include <cmath>
+
 #include "exact_b200.h"
 
 namespace exb {
@@ -24,6 +26,7 @@ struct MaskParams {
   float p;              // dropout probability
   float pinv;           // float(1 / (1 - p))
   float p1m;            // float(1 - p)
+  float p1m_inv_exact;  // 1 / p1m when p1m is a power of two (then g / p1m == g * that, bit for bit), else 0
   uint32_t off_lo, off_hi;
   unsigned long long q0;  // Philox block index of element 0 (global element index / 4)
   PhiloxKey key;
@@ -112,7 +115,10 @@ __global__ void __launch_bounds__(256) mask_backward_kernel(const __grid_constan
       if (OP == OP_RELU) {
         o[j] = keep ? g[j] : 0.f;                      // quantization_cuda_kernel.cu:303-308
       } else {
-        o[j] = keep ? __fdiv_rn(g[j], p.p1m) : 0.f;    // quantization_cuda_kernel.cu:565-569
+        // quantization_cuda_kernel.cu:565-569: g / float(1 - p); a power-of-two divisor (p = 0.5, 0.75, ...)
+        // is an exact scaling, done as one multiply
+        const float q = p.p1m_inv_exact != 0.f ? __fmul_rn(g[j], p.p1m_inv_exact) : __fdiv_rn(g[j], p.p1m);
+        o[j] = keep ? q : 0.f;
       }
     }
     store4<ALIGNED>(p.out, i, p.n, o);
@@ -189,6 +195,11 @@ int exact_act_quantized_dropout_backward(const float* grad_out, const uint32_t* 
   p.x = grad_out; p.out = grad_in; p.mask = const_cast<uint32_t*>(mask); p.n = n;
   p.p = prob;
   p.p1m = (float)(1.0 - (double)prob);  // quantization.cc:120
+  {
+    int ex = 0;
+    const float mant = frexpf(p.p1m, &ex);   // p1m = mant * 2^ex, mant in [0.5, 1)
+    p.p1m_inv_exact = (p.p1m > 0.f && mant == 0.5f && ex > -120 && ex < 120) ? ldexpf(1.f, 1 - ex) : 0.f;
+  }
   return launch_mask<OP_DROPOUT>(false, p, (cudaStream_t)stream);
 }
 

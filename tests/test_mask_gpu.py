@@ -34,7 +34,7 @@ def test_relu_unaligned_view():
     assert torch.equal(y, F.relu(x.detach())) and torch.equal(x.grad, (x.detach() > 0).float())
 
 
-@pytest.mark.parametrize("p", [0.5, 0.2])
+@pytest.mark.parametrize("p", [0.5, 0.2, 0.75])
 @pytest.mark.parametrize("shape", [(2330, 602), (1001, 7), (5,)])
 def test_dropout_supplied_uniforms(shape, p):
     x = np.random.default_rng(3).standard_normal(shape).astype(np.float32)
