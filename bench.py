@@ -92,6 +92,11 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per exact_spmm_split call, averaged over the five calls of
+# a step: profiles/spmm_dram_traffic_bench_sage_2449029n.md
+SPMM_DRAM_BYTES_PER_CALL = {("cfg4", 2449029): 36.04e9}
+
+
 def workload_name(c, nodes):
     return (f"{c['model']}{c['layers']}_{nodes}n_{c['feats']}f_{c['hidden']}h_{c['classes']}c_int{c['bits']}"
             f"_kf{c['kept_frac']}")
@@ -246,14 +251,20 @@ def run_b200(args):
         name, r = top
         per_ms = r["ms"] / r["launches"]
         achieved = r["bytes"] / r["launches"] / (per_ms * 1e-3) / 1e9
+        # DRAM bytes per call of this kernel, from the one-pass ncu capture of this very command (summary and
+        # command under profiles/); only the full single-GPU workload was captured
+        traffic = SPMM_DRAM_BYTES_PER_CALL.get((args.workload, n)) if (world == 1 and name == "exact_spmm_split") else None
         roofline = {"kernel": name, "bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak,
                     "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
-                    "traffic": None, "launches_per_step": r["launches"] / args.steps,
+                    "traffic": traffic,
+                    "traffic_GB/s": None if traffic is None else round(traffic / (per_ms * 1e-3) / 1e9, 1),
+                    "traffic_frac_of_peak": None if traffic is None else round(traffic / (per_ms * 1e-3) / 1e9 / hbm_peak, 4),
+                    "launches_per_step": r["launches"] / args.steps,
                     "ms_per_launch": round(per_ms, 4),
                     "share_of_step": round(r["ms"] / ms, 4),
-                    "bytes_model": "no-reuse bound: nnz*K*4 gather + indices + output; the 126 MB L2 serves most "
-                                   "gathers, so achieved can exceed the HBM copy peak (the kernel is bound by "
-                                   "L2->SM gather bandwidth)"}
+                    "bytes_model": "achieved: no-reuse bound nnz*K*4 gather + indices + output per call (L2 serves "
+                                   "about 60 % of the gathers, so it can exceed the HBM copy peak); traffic: "
+                                   "measured DRAM bytes per call (ncu), the figure the kernel is bound by"}
     cpu = None
     if args.gpus == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(c, args.cpu_nodes)
