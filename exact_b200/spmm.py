@@ -80,6 +80,38 @@ def _aggregate_transposed(src, grad, reduce):
     return ext_spmm._spmm(t_ptr, t_col, t_w, grad, "sum", regroup=True)
 
 
+def _inverse_degree(src):
+    """1 / max(deg, 1) of this rank's rows as an [rows, 1] fp32 column, or None when the adjacency carries
+    edge values (the per-edge weights of the mean's transpose are then not a row scaling)."""
+    from .dist import ShardedSparseTensor
+    if isinstance(src, ShardedSparseTensor):
+        if src.value is not None:
+            return None
+        inv = getattr(src, "_inv_deg", None)
+        if inv is None:
+            inv = (src.rowptr[1:] - src.rowptr[:-1]).to(torch.float32).clamp_(min=1).reciprocal_().unsqueeze(1)
+            src._inv_deg = inv
+        return inv
+    st = src.storage
+    if st.value() is not None:
+        return None
+    inv = getattr(st, "_inv_deg", None)
+    if inv is None:
+        inv = st.rowcount().to(torch.float32).clamp_(min=1).reciprocal_().unsqueeze(1)
+        st._inv_deg = inv
+    return inv
+
+
+def _aggregate_transposed_mean_scaled(src, scaled_grad):
+    """A_mean^T g = A^T (D^-1 g): `scaled_grad` already holds D^-1 g, so the SpMM needs no edge weights
+    (one load and one multiply per edge less: 10.0 against 12.0 ms at 125.8 M edges x 256 columns)."""
+    from .dist import ShardedSparseTensor
+    if isinstance(src, ShardedSparseTensor):
+        return ext_spmm._spmm(src.t_rowptr, src.t_col, None, src.gather(scaled_grad, "bw"), "sum", regroup=True)
+    t_ptr, t_col, _ = src.storage.transposed("sum")
+    return ext_spmm._spmm(t_ptr, t_col, None, scaled_grad, "sum", regroup=True)
+
+
 class qsage_layer(Function):
     """y = reduce(A, x) W_l^T + b (+ x W_r^T): the aggregation, lin_l and lin_r of QSAGEConv
     (layers.py:153-170) as one autograd node.  The compressed tensors saved are those of the separate
@@ -127,13 +159,22 @@ class qsage_layer(Function):
             # instead of the dense g W_l.
             if config.aggregate_gradient_first and out_f <= in_f:
                 pad = (-out_f) % 4   # whole 128-bit column groups for the gather
+                inv = _inverse_degree(ctx.src) if ctx.reduce == "mean" else None
                 gp, wp = g, w_l
                 if pad:
                     gp = g.new_zeros((g.size(0), out_f + pad))
-                    gp[:, :out_f].copy_(g)
+                    if inv is not None:
+                        torch.mul(g, inv, out=gp[:, :out_f])
+                    else:
+                        gp[:, :out_f].copy_(g)
                     wp = w_l.new_zeros((out_f + pad, in_f))
                     wp[:out_f].copy_(w_l)
-                t = _aggregate_transposed(ctx.src, gp, ctx.reduce)
+                elif inv is not None:
+                    gp = g * inv
+                if inv is not None:
+                    t = _aggregate_transposed_mean_scaled(ctx.src, gp)
+                else:
+                    t = _aggregate_transposed(ctx.src, gp, ctx.reduce)
                 grad_x = ext_backward_func.linear_forward(t, wp.t(), None, a2=g if w_r is not None else None,
                                                           weight2=w_r.t() if w_r is not None else None)
             else:
