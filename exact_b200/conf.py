@@ -49,6 +49,9 @@ class QuantizationConfig:
         # Row-sharded aggregation: send operands that are mostly exact zeros (ReLU + dropout outputs and
         # gradients that passed their masks) zero-compacted; shards denser than the bound go as they are.
         self.compact_gather = True
+        # Row-sharded aggregation of the model's input features (a leaf that needs no gradient): keep the
+        # gathered copy while the same unmodified tensor keeps coming back, as it does in full-batch training.
+        self.cache_constant_gather = True
         self.compact_gather_max_density = 0.6
         # QSAGEConv as one autograd node: same compressed tensors, one GEMM for lin_l + lin_r, the two
         # input-gradient products accumulated in the GEMM epilogue.  Same result up to fp32 reassociation.

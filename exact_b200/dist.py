@@ -137,6 +137,8 @@ class sharded_spmm(torch.autograd.Function):
             return adj.gather(x.contiguous(), "fw")
         # a leaf that needs no gradient is the model's input features: in full-batch training the same
         # tensor comes back every epoch, so its gathered copy is kept until the tensor is modified
+        if not config.cache_constant_gather:
+            return adj.gather(x.contiguous(), "fw_const")
         c = adj._const_gather
         if c is not None and c[0] is x and c[1] == x._version:
             return c[2]
