@@ -171,13 +171,6 @@ rp_pack_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * p.kpad);
       const long long n = (long long)tile * kRpTileM + row_in_tile;
       const bool row_ok = n < p.N;
-#ifdef EXB_RP_SKIP_EPILOGUE  // timing experiment only: how fast the load + MMA pipeline runs alone
-      if (row_ok && p.k < 0) p.scale_bf16[n] = 0;
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_tempty[buf]));
-      continue;
-#endif
 
       // pass 1: row min / max of y = acc / sqrt(k) over the k real columns
       float lo = __int_as_float(0x7f800000), hi = __int_as_float(0xff800000);
