@@ -52,3 +52,47 @@ def test_bad_arguments_are_rejected_before_any_launch():
     assert rc == 1 and b"idx_bytes" in lib.exact_last_error()
     # empty inputs are a no-op, as torch.empty-shaped calls are in the reference
     assert lib.exact_quantize_pack(None, 0, 0, 128, 2, None, 0, 0, 0, None, None, None, None, None, None) == 0
+
+
+def test_new_entry_points_reject_bad_arguments_without_a_gpu():
+    lib = _lib.load()
+    assert lib.exact_linear_workspace_bytes(256, 256, 0) == 256 + 2 * 256 * 256 * 4
+    assert lib.exact_linear_workspace_bytes(47, 100, 256) == 256 + 2 * 48 * (128 + 256) * 4
+    # N wider than one MMA tile and rows of A that are not 16-byte aligned are "unsupported" (code 3): the caller
+    # keeps its library GEMM; a second operand pair needs all three of A2, B2, K2
+    one = ctypes.c_void_p(16)
+    rc = lib.exact_linear_forward(one, 8, 8, 8, one, 8, None, 0, 0, None, 0, 300, None, 0, one, one, 300, None)
+    assert rc == 3 and b"256" in lib.exact_last_error()
+    rc = lib.exact_linear_forward(one, 8, 6, 6, one, 6, None, 0, 0, None, 0, 8, None, 0, one, one, 8, None)
+    assert rc == 3 and b"aligned" in lib.exact_last_error()
+    rc = lib.exact_linear_forward(one, 8, 8, 8, one, 8, one, 0, 0, None, 0, 8, None, 0, one, one, 8, None)
+    assert rc == 1
+    assert lib.exact_linear_forward(None, 0, 8, 8, None, 8, None, 0, 0, None, 0, 8, None, 0, None, None, 8, None) == 0
+    rc = lib.exact_rows_mask_count(one, 4, 48, 48, one, one, None)
+    assert rc == 1 and b"multiple of 32" in lib.exact_last_error()
+    rc = lib.exact_rows_expand(one, one, one, 4, 64, 0, 5, 64, one, 64, None)
+    assert rc == 1
+    assert lib.exact_rows_compact_write(None, 0, 64, 64, None, None, None) == 0
+
+
+def test_dense_layer_host_logic_on_cpu():
+    """Off the GPU (or below the row threshold, or with the switch off) the wrappers are the library ops."""
+    import torch
+    from exact_b200.cpp_extension import backward_func as B
+    g = torch.Generator().manual_seed(0)
+    a, w, b = torch.randn(50, 12, generator=g), torch.randn(7, 12, generator=g), torch.randn(7, generator=g)
+    a2, w2 = torch.randn(50, 5, generator=g), torch.randn(7, 5, generator=g)
+    assert torch.equal(B.linear_forward(a, w, b), torch.nn.functional.linear(a, w, b))
+    ref = torch.nn.functional.linear(a, w, b) + a2 @ w2.t()
+    assert torch.allclose(B.linear_forward(a, w, b, a2=a2, weight2=w2), ref, atol=1e-6)
+    out = torch.ones(50, 7)
+    assert torch.allclose(B.linear_forward(a, w, None, out=out, accumulate=True), 1 + a @ w.t(), atol=1e-6)
+    gi, gw, gb = B.linear_backward(torch.randn(50, 7, generator=g), a, w, b, need_grad_input=False)
+    assert gi is None and gw.shape == (7, 12) and gb.shape == (7,)
+    # rows whose pitch is not a multiple of 16 bytes are copied into padded rows, values unchanged
+    v = torch.randn(9, 47, generator=g)
+    p = B._rows16(v)
+    assert p.shape == v.shape and torch.equal(p, v) and p.stride(0) == 48
+    big = torch.randn(70000, 6, generator=g)
+    x = torch.randn(70000, 3, generator=g)
+    assert torch.allclose(B.rows_reduce_mm(big, x), big.t() @ x, rtol=1e-4, atol=1e-3)
