@@ -33,9 +33,9 @@ SIGNATURES = {
                                                     c_ptr]),
     "exact_act_quantized_dropout_backward": (c_int, [c_ptr, c_ptr, c_i64, c_f32, c_ptr, c_ptr]),
     "exact_spmm_split": (c_int, [c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_int, c_i64, c_ptr, c_ptr, c_ptr,
-                                 c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr]),
+                                 c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr]),
     "exact_spmm_split_static": (c_int, [c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_int, c_i64, c_ptr, c_ptr,
-                                        c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr]),
+                                        c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr]),
     "exact_rp_workspace_bytes": (c_i64, [c_i64, c_i64]),
     "exact_rp_quantize_pack": (c_int, [c_ptr, c_i64, c_i64, c_ptr, c_i64, c_int, c_u64, c_u64, c_i64, c_ptr, c_ptr,
                                        c_ptr, c_ptr, c_ptr, c_ptr]),

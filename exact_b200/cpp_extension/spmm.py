@@ -20,12 +20,15 @@ def _plans_of(rowptr):
     return per
 
 
-def long_row_plan(rowptr, threshold):
+def long_row_plan(rowptr, threshold, col=None):
     """Pieces of the rows with more than `threshold` edges (see exact_spmm_split in the header), built
-    once per row-pointer tensor with torch ops and cached.  None when there is no such row."""
+    once per row-pointer tensor with torch ops and cached.  None when there is no such row.  With `col`
+    the pieces are listed by the column of their first edge (item_slot keeps their place in the row):
+    pieces of different hub rows that gather the same source rows then run together."""
     per = _plans_of(rowptr)
-    if threshold in per:
-        return per[threshold]
+    key = (threshold, col is not None)
+    if key in per:
+        return per[key]
     rp = rowptr.to(torch.int64)
     deg = rp[1:] - rp[:-1]
     long_row = torch.nonzero(deg > threshold).flatten()
@@ -38,14 +41,17 @@ def long_row_plan(rowptr, threshold):
         within = torch.arange(item_row.numel(), device=rowptr.device) - torch.repeat_interleave(ptr[:-1], pieces)
         begin = rp[item_row] + within * threshold
         end = torch.minimum(begin + threshold, rp[item_row + 1])
+        slot = None
+        if col is not None:
+            order = torch.argsort(col[begin].to(torch.int64), stable=True)
+            item_row, begin, end = item_row[order], begin[order], end[order]
+            slot = order.to(torch.int32).contiguous()
         plan = {"long_row": long_row.to(torch.int32), "long_item_ptr": ptr.to(torch.int32),
-                "item_row": item_row.to(torch.int32), "item_begin": begin.contiguous(), "item_end": end.contiguous(),
+                "item_row": item_row.to(torch.int32).contiguous(), "item_begin": begin.contiguous(),
+                "item_end": end.contiguous(), "item_slot": slot,
                 "n_items": int(item_row.numel()), "n_long": int(long_row.numel())}
-    per[threshold] = plan
+    per[key] = plan
     return plan
-
-
-REGROUP = 0x100   # EXACT_SPMM_REGROUP
 
 
 def _spmm(rowptr, col, value, mat, reduce, regroup=False):
@@ -76,7 +82,7 @@ def _spmm(rowptr, col, value, mat, reduce, regroup=False):
     # no-reuse bound: every edge gathers a full K-row; plus indices, values, row pointers and the output
     nbytes = nnz * K * 4 + nnz * (ib + (4 if value is not None else 0)) + (M + 1) * ib + M * K * 4
     thr = int(config.spmm_long_row)
-    plan = long_row_plan(rowptr, thr) if thr > 0 else None
+    plan = long_row_plan(rowptr, thr, col) if thr > 0 else None
     red = _lib.REDUCE[reduce] | (REGROUP if regroup else 0)
     if plan is None:
         _lib.invoke("exact_spmm", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), _lib.ptr(mat), M, K,
@@ -85,7 +91,7 @@ def _spmm(rowptr, col, value, mat, reduce, regroup=False):
         scratch = torch.empty((plan["n_items"], K), dtype=torch.float32, device=mat.device)
         _lib.invoke("exact_spmm_split", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), _lib.ptr(mat),
                     M, K, red, thr, _lib.ptr(plan["item_row"]), _lib.ptr(plan["item_begin"]),
-                    _lib.ptr(plan["item_end"]), plan["n_items"], _lib.ptr(plan["long_row"]),
+                    _lib.ptr(plan["item_end"]), _lib.ptr(plan["item_slot"]), plan["n_items"], _lib.ptr(plan["long_row"]),
                     _lib.ptr(plan["long_item_ptr"]), plan["n_long"], _lib.ptr(scratch), _lib.ptr(out),
                     _lib.stream_ptr())
     return out

@@ -39,6 +39,7 @@ struct SpmmParams {
   const int* item_row;
   const long long* item_begin;
   const long long* item_end;
+  const int* item_slot;      // scratch slot of each listed piece, or null (slot = position)
   long long n_items;
   const int* long_row;
   const int* long_item_ptr;
@@ -183,7 +184,7 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_csr_kernel(const __grid_
     if (unit >= p.n_items) return;
     begin = p.item_begin[unit];
     end = p.item_end[unit];
-    dst = p.scratch + unit * K;
+    dst = p.scratch + (long long)(p.item_slot ? p.item_slot[unit] : (int)unit) * K;
   }
   accumulate_edges<IdxT, VEC, KVT, HAS_VAL, FULL>(p, begin, end, coff, cvalid, s_idx[warp], s_val[warp], lane, acc);
 
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_csr_pair_kernel(const __
     if (unit >= p.n_items) return;
     begin = p.item_begin[unit];
     end = p.item_end[unit];
-    dst = p.scratch + unit * K;
+    dst = p.scratch + (long long)(p.item_slot ? p.item_slot[unit] : (int)unit) * K;
   }
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   const unsigned long long row_bytes = (unsigned long long)K * 4ull;
@@ -401,9 +402,9 @@ int exact_spmm(const void* rowptr, const void* col, int idx_bytes, const float* 
 
 int exact_spmm_split(const void* rowptr, const void* col, int idx_bytes, const float* value, const float* mat,
                      int64_t M, int64_t K, int reduce, int64_t long_threshold, const int32_t* item_row,
-                     const int64_t* item_begin, const int64_t* item_end, int64_t n_items,
-                     const int32_t* long_row, const int32_t* long_item_ptr, int64_t n_long, float* scratch,
-                     float* out, void* stream) {
+                     const int64_t* item_begin, const int64_t* item_end, const int32_t* item_slot,
+                     int64_t n_items, const int32_t* long_row, const int32_t* long_item_ptr, int64_t n_long,
+                     float* scratch, float* out, void* stream) {
   EXB_REQUIRE(long_threshold > 0, "spmm_split: long_threshold must be positive");
   EXB_REQUIRE(n_items >= 0 && n_long >= 0, "spmm_split: negative plan size");
   if (n_items > 0)
@@ -413,7 +414,7 @@ int exact_spmm_split(const void* rowptr, const void* col, int idx_bytes, const f
   p.rowptr = rowptr; p.col = col; p.val = value; p.mat = mat; p.out = out; p.M = M; p.K = K;
   p.long_threshold = long_threshold;
   p.item_row = item_row; p.item_begin = reinterpret_cast<const long long*>(item_begin);
-  p.item_end = reinterpret_cast<const long long*>(item_end); p.n_items = n_items;
+  p.item_end = reinterpret_cast<const long long*>(item_end); p.item_slot = item_slot; p.n_items = n_items;
   p.long_row = long_row; p.long_item_ptr = long_item_ptr; p.n_long = n_long; p.scratch = scratch;
   return spmm_common(p, idx_bytes, reduce, (cudaStream_t)stream);
 }
@@ -444,8 +445,8 @@ static int static_scratch_address(float** out) {
 int exact_spmm_split_static(const void* rowptr, const void* col, int idx_bytes, const float* value,
                             const float* mat, int64_t M, int64_t K, int reduce, int64_t long_threshold,
                             const int32_t* item_row, const int64_t* item_begin, const int64_t* item_end,
-                            int64_t n_items, const int32_t* long_row, const int32_t* long_item_ptr,
-                            int64_t n_long, float* out, void* stream) {
+                            const int32_t* item_slot, int64_t n_items, const int32_t* long_row,
+                            const int32_t* long_item_ptr, int64_t n_long, float* out, void* stream) {
   EXB_REQUIRE(n_items >= 0 && K >= 0, "spmm_split_static: negative size");
   EXB_REQUIRE(n_items * K <= (int64_t)EXACT_SPMM_STATIC_SCRATCH_FLOATS,
               "spmm_split_static: %lld pieces x %lld columns need %lld floats of scratch, the built-in array holds %lld; "
@@ -455,7 +456,7 @@ int exact_spmm_split_static(const void* rowptr, const void* col, int idx_bytes, 
   int rc = static_scratch_address(&scratch);
   if (rc) return rc;
   return exact_spmm_split(rowptr, col, idx_bytes, value, mat, M, K, reduce, long_threshold, item_row, item_begin,
-                          item_end, n_items, long_row, long_item_ptr, n_long, scratch, out, stream);
+                          item_end, item_slot, n_items, long_row, long_item_ptr, n_long, scratch, out, stream);
 }
 
 }  // extern "C"

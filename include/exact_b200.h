@@ -118,16 +118,24 @@ EXACT_API int exact_spmm(const void* rowptr, const void* col, int idx_bytes, con
  *   long_row      [n_long]      int32  indices of the long rows, ascending
  *   long_item_ptr [n_long + 1]  int32  pieces of long row i are items long_item_ptr[i] .. [i+1]
  *   item_row      [n_items]     int32  row of each piece
- *   item_begin / item_end [n_items] int64  edge range of each piece (at most long_threshold edges,
- *                                      consecutive pieces of a row tile its edge range in order)
+ *   item_begin / item_end [n_items] int64  edge range of each piece (at most long_threshold edges; the
+ *                                      pieces of a row tile its edge range)
+ *   item_slot     [n_items]     int32  or NULL: the slot of scratch each listed piece writes.  Slots
+ *                                      long_item_ptr[i] .. [i+1] hold the pieces of long row i in edge
+ *                                      order; the pieces themselves may be listed (= processed) in any
+ *                                      order.  Listing them by the column of their first edge lets pieces
+ *                                      of different hub rows that gather the same source rows run
+ *                                      together, so those rows are read from HBM once (10.1 -> 8.7 ms at
+ *                                      125.8 M edges x 256 columns).  NULL: piece j writes slot j.
  *   scratch       [n_items, K]  fp32   caller-owned; holds the partial sums of the pieces
  * Rows up to the threshold are summed exactly as exact_spmm sums them; a long row is the in-order sum
  * of its pieces' sums. */
 EXACT_API int exact_spmm_split(const void* rowptr, const void* col, int idx_bytes, const float* value,
                                const float* mat, int64_t M, int64_t K, int reduce, int64_t long_threshold,
                                const int32_t* item_row, const int64_t* item_begin, const int64_t* item_end,
-                               int64_t n_items, const int32_t* long_row, const int32_t* long_item_ptr,
-                               int64_t n_long, float* scratch, float* out, void* stream);
+                               const int32_t* item_slot, int64_t n_items, const int32_t* long_row,
+                               const int32_t* long_item_ptr, int64_t n_long, float* scratch, float* out,
+                               void* stream);
 
 /* exact_spmm_split without the scratch argument (no counterpart in the reference).  Meant for hosts
  * that must not allocate device memory around the call -- a serving loop with a frozen memory plan, a
@@ -144,9 +152,9 @@ EXACT_API int exact_spmm_split(const void* rowptr, const void* col, int idx_byte
 EXACT_API int exact_spmm_split_static(const void* rowptr, const void* col, int idx_bytes, const float* value,
                                       const float* mat, int64_t M, int64_t K, int reduce,
                                       int64_t long_threshold, const int32_t* item_row,
-                                      const int64_t* item_begin, const int64_t* item_end, int64_t n_items,
-                                      const int32_t* long_row, const int32_t* long_item_ptr, int64_t n_long,
-                                      float* out, void* stream);
+                                      const int64_t* item_begin, const int64_t* item_end,
+                                      const int32_t* item_slot, int64_t n_items, const int32_t* long_row,
+                                      const int32_t* long_item_ptr, int64_t n_long, float* out, void* stream);
 
 /* Fused random projection + quantise + pack: the chain input2rp -> quantize_activation of
  * exact/exact/ops.py:142-149 (torch.matmul(input, rand_matrix), ops.py:117, then ops.py:61-83) as one

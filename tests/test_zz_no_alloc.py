@@ -35,7 +35,8 @@ def _call(name, rowptr, col, val, mat, reduce, thr, plan, scratch, out):
     lib = _lib.load()
     args = [_lib.ptr(rowptr), _lib.ptr(col), 8, _lib.ptr(val), _lib.ptr(mat), rowptr.numel() - 1, mat.size(1),
             _lib.REDUCE[reduce], thr, _lib.ptr(plan["item_row"]), _lib.ptr(plan["item_begin"]),
-            _lib.ptr(plan["item_end"]), plan["n_items"], _lib.ptr(plan["long_row"]), _lib.ptr(plan["long_item_ptr"]),
+            _lib.ptr(plan["item_end"]), _lib.ptr(plan.get("item_slot")), plan["n_items"], _lib.ptr(plan["long_row"]),
+            _lib.ptr(plan["long_item_ptr"]),
             plan["n_long"]]
     if scratch is not None:
         args.append(_lib.ptr(scratch))
@@ -48,7 +49,7 @@ def test_static_scratch_matches_caller_scratch_twice(reduce):
     n, K, thr = 5000, 128, 512
     rowptr_np, col_np = _graph(n, 1)
     rowptr, col = torch.from_numpy(rowptr_np).cuda(), torch.from_numpy(col_np).cuda()
-    plan = S.long_row_plan(rowptr, thr)
+    plan = S.long_row_plan(rowptr, thr, col)   # pieces listed by first column, slots by place in the row
     assert plan is not None and plan["n_long"] == 3 and plan["n_items"] * K <= 4 * 1024 * 1024
     for rep in range(2):   # two calls in a row share the built-in array
         g = torch.Generator(device="cuda").manual_seed(10 + rep)
