@@ -39,7 +39,7 @@ class QuantizationConfig:
         # Read back (synchronising) the status word of kernels with bounded on-chip waits after each call.
         self.check_device_status = False
         # SpMM: rows with more edges than this are cut into pieces that separate warps sum (0: never).
-        self.spmm_long_row = 512
+        self.spmm_long_row = 256
         # Do not produce compressed copies that no backward formula reads (the SpMM's dense operand
         # when edge values need no gradient).  Outputs and gradients are unaffected.
         self.skip_dead_saves = True

@@ -54,6 +54,9 @@ def long_row_plan(rowptr, threshold, col=None):
     return plan
 
 
+REGROUP = 0x100   # EXACT_SPMM_REGROUP
+
+
 def _spmm(rowptr, col, value, mat, reduce, regroup=False):
     """spmm.cc:12-18 -> spmm_cuda.cu:106-170.  `regroup`: the caller accepts a regrouped per-row fp32 sum
     (narrow operands then gather two edges per load instruction)."""

@@ -66,7 +66,7 @@ def test_hub_rows_and_empty_rows(K, with_values):
                 # each (possibly cancelling) element
                 err = np.abs(out[long] - ref[long]).max(1)
                 assert np.all(err <= 1e-5 * np.abs(ref[long]).max(1))
-    config.spmm_long_row = 512
+    config.spmm_long_row = 256
 
 
 @pytest.mark.parametrize("reduce", ["sum", "mean"])
