@@ -94,7 +94,7 @@ class ClockSampler:
 
 # dram__bytes_read.sum + dram__bytes_write.sum per exact_spmm_split call, averaged over the five calls of
 # a step: profiles/spmm_dram_traffic_bench_sage_2449029n.md
-SPMM_DRAM_BYTES_PER_CALL = {("cfg4", 2449029): 36.04e9}
+SPMM_DRAM_BYTES_PER_CALL = {("cfg4", 2449029): 20.63e9}
 
 
 def workload_name(c, nodes):
@@ -264,8 +264,8 @@ def run_b200(args):
                     "ms_per_launch": round(per_ms, 4),
                     "share_of_step": round(r["ms"] / ms, 4),
                     "bytes_model": "achieved: no-reuse bound nnz*K*4 gather + indices + output per call (L2 serves "
-                                   "about 60 % of the gathers, so it can exceed the HBM copy peak); traffic: "
-                                   "measured DRAM bytes per call (ncu), the figure the kernel is bound by"}
+                                   "about 80 % of the gathers, so it exceeds the HBM copy peak: the kernel is bound "
+                                   "by gather latency and L2->SM throughput); traffic: measured DRAM bytes per call (ncu)"}
     cpu = None
     if args.gpus == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(c, args.cpu_nodes)
