@@ -17,9 +17,10 @@
 // other sign).
 //
 // Structure (one CTA per SM, persistent over 128-row tiles of A, 14 warps):
-//   warp 0     TMA producer.  Shared memory is a ring of six 32 KB slots; a 32-column K tile uses three
-//              consecutive slots: A (raw fp32 [128 x 32], 16 KB, the tail tile goes into the slot's other
-//              half), B_hi [Npad x 32] and B_lo [Npad x 32].  128-byte swizzle, no multicast.
+//   warp 0     TMA producer.  Shared memory is a 192 KB ring of K-tile stages; a 32-column K tile uses three
+//              parts: A (raw fp32 [128 x 32], 16 KB, the tail tile goes into the part's other half),
+//              B_hi [Npad x 32] and B_lo [Npad x 32]: two stages at Npad = 256, up to four for narrow
+//              outputs.  128-byte swizzle, no multicast.
 //              The A tile of four K tiles ahead is requested into L2 (tensor prefetch): A is read from
 //              HBM exactly once and the ring is only two K tiles deep.
 //   warps 2-9  converter: rewrite the raw A tile in place as a_hi and write a_lo beside it (same swizzled
@@ -44,7 +45,9 @@ constexpr int kLinTileM = 128;
 constexpr int kLinTileK = 32;
 constexpr int kLinConvWarps = 8;
 constexpr int kLinThreads = (2 + kLinConvWarps + 4) * 32;   // TMA, MMA, converters, epilogue
-constexpr int kLinSlots = 6;
+constexpr int kLinSlots = 6;                    // ring capacity in 32 KB units
+constexpr int kLinMaxStages = 4;
+constexpr int kLinBars = kLinMaxStages * 3;
 constexpr uint32_t kLinSlotBytes = 32 * 1024;
 constexpr uint32_t kLinHalf = 16 * 1024;        // raw / tail halves of an A slot
 constexpr int kLinPrefetch = 4;                 // K tiles of A requested into L2 ahead of their TMA load
@@ -58,6 +61,9 @@ struct LinParams {
   int kblocks1, kblocks;   // K tiles of the first operand pair, and of both pairs together
   int num_tiles;
   int accumulate;          // C += ... instead of C = ...
+  int stages;              // K tiles the ring holds (2 at Npad = 256, up to 4 for narrow outputs)
+  unsigned b_slot;         // bytes of a B_hi / B_lo slot = Npad * 128
+  unsigned stage_bytes;    // A slot (32 KB) + two B slots
   unsigned tmem_cols;
 };
 
@@ -76,14 +82,27 @@ __device__ __forceinline__ void fence_proxy_async_smem_lin() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Part `it` of the stream of ring parts (three per K tile: A, B_hi, B_lo): barrier index, phase, address.
+struct LinPart { int b; uint32_t ph; uint32_t addr; };
+__device__ __forceinline__ LinPart lin_part(int it, const LinParams& p, uint32_t ring) {
+  const int kt = it / 3, part = it - kt * 3;
+  const int stage = kt % p.stages;
+  LinPart r;
+  r.b = stage * 3 + part;
+  r.ph = (uint32_t)(kt / p.stages) & 1u;
+  r.addr = ring + (uint32_t)stage * p.stage_bytes +
+           (part == 0 ? 0u : (part == 1 ? kLinSlotBytes : kLinSlotBytes + p.b_slot));
+  return r;
+}
+
 __global__ void __launch_bounds__(kLinThreads, 1)
 linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a2,
                      const __grid_constant__ CUtensorMap tm_bh, const __grid_constant__ CUtensorMap tm_bl,
                      const __grid_constant__ LinParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) unsigned long long s_full[kLinSlots];
-  __shared__ __align__(8) unsigned long long s_empty[kLinSlots];
-  __shared__ __align__(8) unsigned long long s_conv[kLinSlots];
+  __shared__ __align__(8) unsigned long long s_full[kLinBars];
+  __shared__ __align__(8) unsigned long long s_empty[kLinBars];
+  __shared__ __align__(8) unsigned long long s_conv[kLinBars];
   __shared__ __align__(8) unsigned long long s_tfull[2];
   __shared__ __align__(8) unsigned long long s_tempty[2];
   __shared__ uint32_t s_tmem_base;
@@ -96,7 +115,7 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int s = 0; s < kLinSlots; s++) {
+    for (int s = 0; s < kLinBars; s++) {
       mbar_init(smem_u32(&s_full[s]), 1);
       mbar_init(smem_u32(&s_empty[s]), 1);
       mbar_init(smem_u32(&s_conv[s]), kLinConvWarps);   // one arrival per converter warp
@@ -124,11 +143,10 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
       for (int tile = first; tile < p.num_tiles && ok; tile += step) {
         for (int kb = 0; kb < p.kblocks && ok; kb++) {
           for (int u = 0; u < 3; u++, it++) {
-            const int s = it % kLinSlots;
-            const uint32_t ph = (uint32_t)(it / kLinSlots) & 1u;
-            if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
-            const uint32_t full = smem_u32(&s_full[s]);
-            const uint32_t dst = ring + (uint32_t)s * kLinSlotBytes;
+            const LinPart pt_ = lin_part(it, p, ring);
+            if (!mbar_wait(smem_u32(&s_empty[pt_.b]), pt_.ph ^ 1u, abort_flag)) { ok = false; break; }
+            const uint32_t full = smem_u32(&s_full[pt_.b]);
+            const uint32_t dst = pt_.addr;
             if (u == 0) {
               mbar_arrive_expect_tx(full, kLinHalf);
               if (kb < p.kblocks1) tma_load_2d(dst, &tm_a, kb * kLinTileK, tile * kLinTileM, full);
@@ -151,10 +169,10 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
       if (!ok) {
         // leave no bulk copy in flight: wait (bounded) for every slot that was armed last
         const long long t0 = clock64();
-        for (int j = 0; j < kLinSlots && j < it; j++) {
-          const int jt = it - 1 - j;
-          const uint32_t bar = smem_u32(&s_full[jt % kLinSlots]);
-          const uint32_t ph = (uint32_t)(jt / kLinSlots) & 1u;
+        for (int j = 0; j < p.stages * 3 && j < it; j++) {
+          const LinPart q = lin_part(it - 1 - j, p, ring);
+          const uint32_t bar = smem_u32(&s_full[q.b]);
+          const uint32_t ph = q.ph;
           while (!mbar_try_wait(bar, ph) && clock64() - t0 < kWaitLimitCycles) {}
         }
       }
@@ -172,18 +190,16 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.Npad);
         for (int kb = 0; kb < p.kblocks; kb++, it += 3) {
-          const int sa = it % kLinSlots, sh = (it + 1) % kLinSlots, sl = (it + 2) % kLinSlots;
-          const uint32_t pa = (uint32_t)(it / kLinSlots) & 1u;
-          const uint32_t phh = (uint32_t)((it + 1) / kLinSlots) & 1u;
-          const uint32_t pl = (uint32_t)((it + 2) / kLinSlots) & 1u;
-          if (!mbar_wait(smem_u32(&s_conv[sa]), pa, abort_flag)) { ok = false; break; }
-          if (!mbar_wait(smem_u32(&s_full[sh]), phh, abort_flag)) { ok = false; break; }
+          const LinPart qa = lin_part(it, p, ring), qh = lin_part(it + 1, p, ring), ql = lin_part(it + 2, p, ring);
+          const int sa = qa.b, sh = qh.b, sl = ql.b;
+          const uint32_t pl = ql.ph;
+          if (!mbar_wait(smem_u32(&s_conv[sa]), qa.ph, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&s_full[sh]), qh.ph, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = ring + (uint32_t)sa * kLinSlotBytes;
-          const uint64_t ahi = umma_desc_sw128(a_addr);
-          const uint64_t alo = umma_desc_sw128(a_addr + kLinHalf);
-          const uint64_t bhi = umma_desc_sw128(ring + (uint32_t)sh * kLinSlotBytes);
-          const uint64_t blo = umma_desc_sw128(ring + (uint32_t)sl * kLinSlotBytes);
+          const uint64_t ahi = umma_desc_sw128(qa.addr);
+          const uint64_t alo = umma_desc_sw128(qa.addr + kLinHalf);
+          const uint64_t bhi = umma_desc_sw128(qh.addr);
+          const uint64_t blo = umma_desc_sw128(ql.addr);
 #pragma unroll
           for (int k4 = 0; k4 < kLinTileK / 8; k4++) {
             const uint64_t o = (uint64_t)(k4 * 2);   // 8 tf32 = 32 bytes along K inside the swizzle atom
@@ -212,10 +228,10 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     bool ok = true;
     for (int tile = first; tile < p.num_tiles && ok; tile += step) {
       for (int kb = 0; kb < p.kblocks; kb++, it += 3) {
-        const int s = it % kLinSlots;
-        const uint32_t ph = (uint32_t)(it / kLinSlots) & 1u;
-        if (!mbar_wait(smem_u32(&s_full[s]), ph, abort_flag)) { ok = false; break; }
-        const uint32_t base = ring + (uint32_t)s * kLinSlotBytes + (uint32_t)ct * 16u;
+        const LinPart qa = lin_part(it, p, ring);
+        const int s = qa.b;
+        if (!mbar_wait(smem_u32(&s_full[s]), qa.ph, abort_flag)) { ok = false; break; }
+        const uint32_t base = qa.addr + (uint32_t)ct * 16u;
 #pragma unroll
         for (int i = 0; i < kPer; i++) {
           const uint32_t addr = base + (uint32_t)i * (32u * kLinConvWarps * 16u);
@@ -391,6 +407,10 @@ int exact_linear_forward(const float* A, int64_t M, int64_t K, int64_t lda, cons
   p.kblocks1 = Kpad1 / kLinTileK; p.kblocks = Kpad / kLinTileK;
   p.num_tiles = (int)((M + kLinTileM - 1) / kLinTileM);
   p.accumulate = accumulate ? 1 : 0;
+  p.b_slot = (unsigned)Npad * kLinTileK * 4;
+  p.stage_bytes = kLinSlotBytes + 2 * p.b_slot;
+  p.stages = (int)((kLinSlots * kLinSlotBytes) / p.stage_bytes);
+  if (p.stages > kLinMaxStages) p.stages = kLinMaxStages;
   unsigned cols = 32;
   while (cols < (unsigned)(2 * Npad)) cols <<= 1;
   p.tmem_cols = cols;
