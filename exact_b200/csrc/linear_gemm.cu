@@ -12,9 +12,9 @@
 // and the product is accumulated in fp32 as  a_hi b_hi + a_lo b_hi + a_hi b_lo.  The dropped terms
 // (a_lo b_lo and the rounding of the tails) are below 2^-21 |a b|, the size of the fp32 rounding of a
 // plain fp32 dot product, so the result is as accurate as an fp32 SIMT GEMM at three tensor-core MMAs
-// per tile instead of one fp32 FMA per product.  Non-finite inputs stay non-finite, but an infinite
-// element can turn its output row into NaN where an fp32 GEMM gives +-inf (inf times a tail of the
-// other sign).
+// per tile instead of one fp32 FMA per product.  Non-finite inputs stay non-finite and confined to their
+// rows, but an infinite element turns its output row into NaN where an fp32 GEMM gives +-inf (its tail is
+// inf - inf).
 //
 // Structure (one CTA per SM, persistent over 128-row tiles of A, 14 warps):
 //   warp 0     TMA producer.  Shared memory is a 192 KB ring of K-tile stages; a 32-column K tile uses three
@@ -50,6 +50,7 @@ constexpr int kLinMaxStages = 4;
 constexpr int kLinBars = kLinMaxStages * 3;
 constexpr uint32_t kLinSlotBytes = 32 * 1024;
 constexpr uint32_t kLinHalf = 16 * 1024;        // raw / tail halves of an A slot
+constexpr int kLinSleepNs = 200;                // back-off between polls of the roles that wait long (producer, epilogue)
 constexpr int kLinPrefetch = 4;                 // K tiles of A requested into L2 ahead of their TMA load
 
 struct LinParams {
@@ -72,11 +73,10 @@ __device__ __forceinline__ uint32_t rna_tf32(float x) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return r;
 }
-// (head, tail) of the split; the tail of a non-finite head is zero so that inf stays inf.
+// (head, tail) of the split.  A non-finite element has a NaN tail (inf - inf), so its output row is NaN.
 __device__ __forceinline__ void split_tf32(float a, float& hi, float& lo) {
   hi = __uint_as_float(rna_tf32(a));
-  const float d = __fsub_rn(a, hi);
-  lo = (fabsf(hi) <= 3.402823466e38f) ? __uint_as_float(rna_tf32(d)) : 0.f;
+  lo = __uint_as_float(rna_tf32(__fsub_rn(a, hi)));
 }
 __device__ __forceinline__ void fence_proxy_async_smem_lin() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -144,7 +144,7 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         for (int kb = 0; kb < p.kblocks && ok; kb++) {
           for (int u = 0; u < 3; u++, it++) {
             const LinPart pt_ = lin_part(it, p, ring);
-            if (!mbar_wait(smem_u32(&s_empty[pt_.b]), pt_.ph ^ 1u, abort_flag)) { ok = false; break; }
+            if (!mbar_wait<kLinSleepNs>(smem_u32(&s_empty[pt_.b]), pt_.ph ^ 1u, abort_flag)) { ok = false; break; }
             const uint32_t full = smem_u32(&s_full[pt_.b]);
             const uint32_t dst = pt_.addr;
             if (u == 0) {
@@ -238,7 +238,14 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
           float a[4], h[4], l[4];
           asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a[0]), "=f"(a[1]), "=f"(a[2]), "=f"(a[3]) : "r"(addr));
 #pragma unroll
-          for (int e = 0; e < 4; e++) split_tf32(a[e], h[e], l[e]);
+          for (int e = 0; e < 4; e++) h[e] = __uint_as_float(rna_tf32(a[e]));
+#pragma unroll
+          for (int e = 0; e < 4; e += 2) {   // tails: paired subtract, then round to tf32
+            float d0, d1;
+            f2_unpack(f2_sub(f2_pack(a[e], a[e + 1]), f2_pack(h[e], h[e + 1])), d0, d1);
+            l[e] = __uint_as_float(rna_tf32(d0));
+            l[e + 1] = __uint_as_float(rna_tf32(d1));
+          }
           asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(h[0]), "f"(h[1]), "f"(h[2]), "f"(h[3]) : "memory");
           asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr + kLinHalf), "f"(l[0]), "f"(l[1]), "f"(l[2]), "f"(l[3]) : "memory");
         }
@@ -257,7 +264,7 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     for (int tile = first; tile < p.num_tiles && ok; tile += step, t++) {
       const int buf = t & 1;
       const uint32_t ph = (uint32_t)(t >> 1) & 1u;
-      if (!mbar_wait(smem_u32(&s_tfull[buf]), ph, abort_flag)) { ok = false; break; }
+      if (!mbar_wait<kLinSleepNs>(smem_u32(&s_tfull[buf]), ph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * p.Npad);
       const long long row_base = (long long)tile * kLinTileM + quad * 32;

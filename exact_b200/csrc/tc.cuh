@@ -32,7 +32,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the abort flag is (or becomes) set.
+// Bounded wait: false when the abort flag is (or becomes) set.  SLEEP_NS > 0: a waiting warp sleeps that
+// long between polls instead of competing for issue slots with the warps that do the work.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   const long long t0 = clock64();
   while (true) {
@@ -42,6 +44,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       *abort_flag = 1;
       return false;
     }
+    if (SLEEP_NS > 0) asm volatile("nanosleep.u32 %0;" ::"r"(SLEEP_NS));
   }
 }
 

@@ -77,8 +77,8 @@ def test_strided_rows_and_column_block_of_c():
 
 
 def test_non_finite_inputs_stay_local():
-    """A row holding inf or NaN comes out non-finite (inf * tail may turn an fp32 inf into NaN); every
-    other row is unaffected."""
+    """A row holding inf or NaN comes out non-finite (the tail of inf is inf - inf = NaN); every other row
+    is unaffected."""
     M, K, N = 1536, 64, 48
     a, w = t(normal(M, K, 1)), t(normal(N, K, 2))
     a[5, 7] = float("inf")
