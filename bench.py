@@ -335,6 +335,27 @@ def kernel_bandwidths(torch, Q, _lib, dev, hbm_peak, N=1_000_000, D=128, reps=20
         sec = a.elapsed_time(b) * 1e-3 / reps
         out[name] = {"GB/s": round(nbytes / sec / 1e9, 1), "frac": round(nbytes / sec / 1e9 / hbm_peak, 4),
                      "TFLOP/s": round(2.0 * N2 * D2 * k2 / sec / 1e12, 1)}
+    del x2, pk
+    # the dense-layer GEMM (tf32 head/tail split, three MMAs per tile) against the library's fp32 GEMM
+    from exact_b200.cpp_extension import backward_func as B
+    M3, K3, N3 = 1_000_000, 256, 256
+    a3 = torch.randn(M3, K3, device=dev, generator=gen)
+    w3 = torch.randn(N3, K3, device=dev, generator=gen)
+    times = {}
+    for name, call in (("tc", lambda: B.linear_forward(a3, w3)), ("lib", lambda: torch.nn.functional.linear(a3, w3))):
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            call()
+        b.record()
+        torch.cuda.synchronize()
+        times[name] = a.elapsed_time(b) * 1e-3 / reps
+    out["linear_tf32x3_1Mx256x256"] = {"ms": round(times["tc"] * 1e3, 4), "library_fp32_ms": round(times["lib"] * 1e3, 4),
+                                       "fp32_equiv_TFLOP/s": round(2.0 * M3 * K3 * N3 / times["tc"] / 1e12, 1),
+                                       "tensor_TFLOP/s": round(6.0 * M3 * K3 * N3 / times["tc"] / 1e12, 1)}
     return out
 
 
