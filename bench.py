@@ -148,9 +148,9 @@ def run_b200(args):
     y = torch.randint(c["classes"], (n,), generator=g)[r0:r1].to(dev)
     torch.manual_seed(0)
     cls = models.GCN if c["model"] == "gcn" else models.SAGE
-    config.compress_activation = True
+    config.compress_activation = not args.no_compress
     config.activation_compression_bits = [c["bits"]]
-    config.kept_frac = c["kept_frac"]
+    config.kept_frac = 1.0 if args.no_compress else c["kept_frac"]
     config.manual_seed(0)
     config.compact_gather = not args.dense_gather
     config.cache_constant_gather = False   # every timed step exchanges its input features again
@@ -196,7 +196,9 @@ def run_b200(args):
         sampler.start()
     launches0 = _lib.LAUNCHES
     _lib.TIMER = _lib.KernelTimer()
+    torch.cuda.reset_peak_memory_stats(dev)
     ms = timed(lambda: step(x_dev), args.steps)
+    peak_mem = torch.cuda.max_memory_allocated(dev)
     ksum = _lib.TIMER.summary()
     _lib.TIMER = None
     launches = _lib.LAUNCHES - launches0
@@ -275,6 +277,7 @@ def run_b200(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(c, n), "nodes": n, "directed_edges": nnz, "parallelism": f"rows/{world}",
+                   "activations": "uncompressed (comparison run)" if args.no_compress else "compressed",
                    "exchange": "none" if world == 1 else (("dense rows" if args.dense_gather else "zero-compacted rows")
                                                          + ", input features exchanged every step"),
                    "l2": "inputs larger than L2" if n * c["hidden"] * 4 > 126e6 else "working set fits L2",
@@ -282,6 +285,7 @@ def run_b200(args):
         "e2e": {"value": round(args.steps / (ms_e2e * 1e-3), 4), "unit": "epoch/s",
                 "h2d_bytes_per_step": x_host.numel() * 4 * world, "d2h_bytes_per_step": 4 * world},
         "gpu_launches": launches,
+        "peak_device_memory_GB": round(peak_mem / 1e9, 2),   # rank 0, device-resident leg (graph, features, training state)
         "kernel_ms_per_step": {k: round(v["ms"] / args.steps, 3) for k, v in sorted(ksum.items())},
         "roofline": roofline, "kernels": kern, "cpu_baseline": cpu, "clocks": clocks,
     }
@@ -440,6 +444,8 @@ def main():
     ap.add_argument("--cpu-nodes", type=int, default=200000, help="nodes of the bounded sample the CPU baseline runs")
     ap.add_argument("--no-kernels", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-compress", action="store_true",
+                    help="comparison run: activations saved uncompressed (config.compress_activation = False)")
     ap.add_argument("--dense-gather", action="store_true", help="N > 1: exchange dense rows (no zero compaction)")
     args = ap.parse_args()
     if args.impl == "reference":
