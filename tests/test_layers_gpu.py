@@ -92,7 +92,7 @@ def run_model(cfg_name, nodes, seed, kept_frac=None, fused_rp=False):
 
 
 def test_config1_gcn_two_layers_forward_backward():
-    """BASELINE config 1, second half: 2-layer GCN 128->64->16 on a 4,096-node Erdos-Renyi graph."""
+    """Benchmark configuration 1, second half: 2-layer GCN 128->64->16 on a 4,096-node Erdos-Renyi graph."""
     loss, out, grads, oloss, oout, ograds = run_model("cfg1", None, seed=3)
     assert abs(loss - oloss) < 1e-4 * abs(oloss)
     assert relfro(out, oout) < 1e-5

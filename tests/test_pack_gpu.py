@@ -140,7 +140,7 @@ def test_no_upper_clamp_is_reproduced():
 
 
 def test_public_api_round_trip_config1():
-    """BASELINE config 1, first half: 4096 x 128, INT2, supplied noise, through the reference's API."""
+    """Benchmark configuration 1, first half: 4096 x 128, INT2, supplied noise, through the reference's API."""
     config.activation_compression_bits = [2]
     config.compress_activation = True
     x, u = relu_normal(4096, 128, 0), uniform01((4096, 128), 1)
