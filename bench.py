@@ -240,7 +240,7 @@ def run_b200(args):
     # ---- pack / unpack kernels against the HBM roofline (first half of the metric) -------------------
     kern = {}
     if rank == 0 and not args.no_kernels:
-        kern = kernel_bandwidths(torch, Q, _lib, dev, hbm_peak)
+        kern = kernel_bandwidths(torch, Q, _lib, dev, hbm_peak, workload_shape=(r1 - r0, c["hidden"]))
 
     if world > 1:
         dist.barrier()
@@ -292,9 +292,7 @@ def run_b200(args):
     print(json.dumps(line), flush=True)
 
 
-def kernel_bandwidths(torch, Q, _lib, dev, hbm_peak, N=1_000_000, D=128, reps=20):
-    """Achieved GB/s of the fused quantise+pack and of unpack+dequantise, INT{1,2,4,8}, fp32 in, on a
-    10^6 x 128 activation (512 MB: larger than L2), CUDA events on the launching stream."""
+def _pack_unpack_fractions(torch, Q, dev, hbm_peak, N, D, reps):
     out = {}
     gen = torch.Generator(device=dev).manual_seed(3)
     x = torch.randn(N, D, device=dev, generator=gen).relu_()
@@ -316,6 +314,18 @@ def kernel_bandwidths(torch, Q, _lib, dev, hbm_peak, N=1_000_000, D=128, reps=20
             gbs = nbytes * reps / (a.elapsed_time(b) * 1e-3) / 1e9
             out[f"{kind}_int{bits}"] = {"GB/s": round(gbs, 1), "frac": round(gbs / hbm_peak, 4)}
     out["shape"] = f"{N}x{D} fp32"
+    return out
+
+
+def kernel_bandwidths(torch, Q, _lib, dev, hbm_peak, N=1_000_000, D=128, reps=20, workload_shape=None):
+    """Achieved GB/s of the fused quantise+pack and of unpack+dequantise, INT{1,2,4,8}, fp32 in, on a
+    10^6 x 128 activation (512 MB: larger than L2) and on the workload's own hidden-activation shape, CUDA
+    events on the launching stream."""
+    out = _pack_unpack_fractions(torch, Q, dev, hbm_peak, N, D, reps)
+    if workload_shape is not None:
+        out["workload_shape"] = _pack_unpack_fractions(torch, Q, dev, hbm_peak, workload_shape[0], workload_shape[1],
+                                                       max(reps // 2, 5))
+    gen = torch.Generator(device=dev).manual_seed(4)
     # the two tensor-core kernels of the projection pair at 10^6 x 256 <-> k = 32, INT2
     from exact_b200.ops import _rademacher
     N2, D2, k2 = 1_000_000, 256, 32
