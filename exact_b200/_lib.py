@@ -32,6 +32,8 @@ SIGNATURES = {
     "exact_act_quantized_dropout_forward": (c_int, [c_ptr, c_i64, c_f32, c_ptr, c_u64, c_u64, c_i64, c_ptr, c_ptr,
                                                     c_ptr]),
     "exact_act_quantized_dropout_backward": (c_int, [c_ptr, c_ptr, c_i64, c_f32, c_ptr, c_ptr]),
+    "exact_act_quantized_relu_dropout_forward": (c_int, [c_ptr, c_i64, c_f32, c_ptr, c_u64, c_u64, c_i64, c_ptr, c_ptr,
+                                                         c_ptr]),
     "exact_spmm_split": (c_int, [c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_int, c_i64, c_ptr, c_ptr, c_ptr,
                                  c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr]),
     "exact_spmm_split_static": (c_int, [c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_int, c_i64, c_ptr, c_ptr,

@@ -53,6 +53,9 @@ class QuantizationConfig:
         # gathered copy while the same unmodified tensor keeps coming back, as it does in full-batch training.
         self.cache_constant_gather = True
         self.compact_gather_max_density = 0.6
+        # A model's ReLU + Dropout pair held in an ActDropout child becomes one QReLUDropout (one pass over
+        # the activation, one saved mask) instead of QReLU followed by QDropout; same outputs and gradients.
+        self.fuse_relu_dropout = True
         # QSAGEConv as one autograd node: same compressed tensors, one GEMM for lin_l + lin_r, the two
         # input-gradient products accumulated in the GEMM epilogue.  Same result up to fp32 reassociation.
         self.fuse_sage_layer = True

@@ -258,6 +258,40 @@ def act_quantized_dropout(input, p, train, uniforms=None):
     return _ActQuantizedDropout.apply(input, float(p), uniforms)
 
 
+class _ActQuantizedReLUDropout(_ActQuantizedDropout):
+    """ReLU then dropout in one pass, one mask; the backward is the dropout's with that mask."""
+
+    @staticmethod
+    def forward(ctx, input, p, uniforms):
+        lib = _lib.load()
+        n = input.numel()
+        out = torch.empty_like(input)
+        mask = torch.empty(int(lib.exact_mask_words(n)), dtype=torch.int32, device=input.device)
+        if uniforms is None:
+            seed, offset = config.seed, config.next_offset()
+        else:
+            seed = offset = 0
+        index_offset = config.row_offset * (n // input.shape[0]) if (input.dim() >= 2 and n) else 0
+        _lib.invoke("exact_act_quantized_relu_dropout_forward", 8 * n + n // 8, _lib.ptr(input), n, p,
+                    _lib.ptr(uniforms), seed, offset, index_offset, _lib.ptr(out), _lib.ptr(mask), _lib.stream_ptr())
+        ctx.save_for_backward(mask)
+        ctx.p = p
+        return out
+
+
+def act_quantized_relu_dropout(input, p, train, uniforms=None):
+    """dropout(relu(input)) as the two reference ops compute it (quantization.cc:66-84, 111-134), in one
+    pass and with one saved mask.  Eval mode: relu only."""
+    _check_cuda_float(input, "input")
+    if not train:
+        return torch.relu(input)
+    if uniforms is not None:
+        _check_cuda_float(uniforms, "uniforms")
+        if uniforms.numel() != input.numel():
+            raise RuntimeError("uniforms must have the shape of input")
+    return _ActQuantizedReLUDropout.apply(input.contiguous(), float(p), uniforms)
+
+
 def act_quantized_leaky_relu(input, slope):
     raise NotImplementedError("act_quantized_leaky_relu serves only the GAT layers, which are outside the "
                               "GCN/GraphSAGE path this library accelerates")

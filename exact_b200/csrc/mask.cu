@@ -15,7 +15,7 @@
 
 namespace exb {
 
-enum MaskOp { OP_RELU = 0, OP_DROPOUT = 1 };
+enum MaskOp { OP_RELU = 0, OP_DROPOUT = 1, OP_RELU_DROPOUT = 2 };
 
 struct MaskParams {
   const float* x;       // forward input or grad_out
@@ -71,6 +71,10 @@ __global__ void __launch_bounds__(256) mask_forward_kernel(const __grid_constant
         o[j] = keep[j] ? v[j] : 0.f;
       }
     } else {
+      if (OP == OP_RELU_DROPOUT) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = v[j] > 0.f ? v[j] : 0.f;   // the ReLU that precedes the dropout
+      }
       float u[4];
       if (p.u != nullptr) {
         load4<ALIGNED>(p.u, i, p.n, u);
@@ -86,6 +90,9 @@ __global__ void __launch_bounds__(256) mask_forward_kernel(const __grid_constant
         keep[j] = (u[j] > p.p) && (i + j < p.n);  // quantization_cuda_kernel.cu:466-469
         // quantization_cuda_kernel.cu:490: src * keep * pinv, two fp32 multiplies
         o[j] = __fmul_rn(__fmul_rn(v[j], keep[j] ? 1.f : 0.f), p.pinv);
+        // one mask serves both backward passes: the gradient survives where the ReLU passed and the
+        // dropout kept
+        if (OP == OP_RELU_DROPOUT) keep[j] = keep[j] && v[j] > 0.f;
       }
     }
     store4<ALIGNED>(p.out, i, p.n, o);
@@ -186,6 +193,23 @@ int exact_act_quantized_dropout_forward(const float* x, int64_t n, float prob, c
   p.q0 = (unsigned long long)index_offset >> 2;
   p.key = make_philox_key(seed);
   return launch_mask<OP_DROPOUT>(true, p, (cudaStream_t)stream);
+}
+
+int exact_act_quantized_relu_dropout_forward(const float* x, int64_t n, float prob, const float* uniforms,
+                                             uint64_t seed, uint64_t offset, int64_t index_offset, float* out,
+                                             uint32_t* mask, void* stream) {
+  EXB_REQUIRE(n >= 0, "relu_dropout: negative size");
+  EXB_REQUIRE(index_offset >= 0 && index_offset % 4 == 0, "relu_dropout: index_offset must be a non-negative multiple of 4");
+  EXB_REQUIRE(prob >= 0.f && prob <= 1.f, "relu_dropout: p must be in [0, 1] (got %f)", (double)prob);
+  MaskParams p{};
+  p.x = x; p.u = uniforms; p.out = out; p.mask = mask; p.n = n;
+  p.p = prob;
+  p.pinv = (float)(1.0 / (1.0 - (double)prob));  // quantization_cuda_kernel.cu:455
+  p.p1m = (float)(1.0 - (double)prob);
+  p.off_lo = (uint32_t)offset; p.off_hi = (uint32_t)(offset >> 32);
+  p.q0 = (unsigned long long)index_offset >> 2;
+  p.key = make_philox_key(seed);
+  return launch_mask<OP_RELU_DROPOUT>(true, p, (cudaStream_t)stream);
 }
 
 int exact_act_quantized_dropout_backward(const float* grad_out, const uint32_t* mask, int64_t n,

@@ -149,6 +149,33 @@ class QDropout(torch.nn.Module):
         return F.dropout(input, self.p, self.training)
 
 
+class ActDropout(torch.nn.Module):
+    """activation followed by dropout, as the GCN / GraphSAGE models apply them after every hidden layer
+    (mem_speed_bench/models/gcn.py:60-61, sage.py:72-73).  Kept as one child so that QModule can swap the
+    pair for the one-pass QReLUDropout; unconverted it just calls the two modules."""
+
+    def __init__(self, activation, dropout):
+        super().__init__()
+        self.activation, self.dropout = activation, dropout
+
+    def forward(self, input):
+        return self.dropout(self.activation(input))
+
+
+class QReLUDropout(torch.nn.Module):
+    """QReLU followed by QDropout (layers.py:284-292, 316-325) in one pass over the activation and with one
+    saved 1-bit mask; outputs and gradients are those of the two modules."""
+
+    def __init__(self, p):
+        super().__init__()
+        self.p = p
+
+    def forward(self, input):
+        if self.training:
+            return ext_quantization.act_quantized_relu_dropout(input, self.p, True)
+        return F.relu(input)
+
+
 class QDropout2(torch.nn.Module):
     """layers.py:328-337."""
 

@@ -4,7 +4,7 @@ layers of this package so that QModule can convert them."""
 import torch
 from torch.nn import BatchNorm1d, ModuleList
 
-from .layers import GCNConv, SAGEConv
+from .layers import ActDropout, GCNConv, SAGEConv
 
 
 class GCN(torch.nn.Module):
@@ -17,6 +17,7 @@ class GCN(torch.nn.Module):
         if drop_input:
             self.input_dropout = torch.nn.Dropout(p=dropout)
         self.activation = torch.nn.ReLU()
+        self.act_drop = ActDropout(self.activation, self.dropout)   # the pair applied after every hidden layer
         self.batch_norm, self.residual, self.num_layers = batch_norm, residual, num_layers
         self.convs = ModuleList()
         for i in range(num_layers):
@@ -42,8 +43,7 @@ class GCN(torch.nn.Module):
                 h = self.bns[idx](h)
             if self.residual and h.size(-1) == x.size(-1):
                 h = h + x[:h.size(0)]
-            x = self.activation(h)
-            x = self.dropout(x)
+            x = self.act_drop(h)
         return self.convs[-1](x, adj_t)
 
 
@@ -54,6 +54,7 @@ class SAGE(torch.nn.Module):
         self.in_channels, self.out_channels = in_channels, out_channels
         self.dropout = torch.nn.Dropout(p=dropout)
         self.activation = torch.nn.ReLU()
+        self.act_drop = ActDropout(self.activation, self.dropout)   # the pair applied after every hidden layer
         self.batch_norm, self.residual, self.num_layers = batch_norm, residual, num_layers
         self.use_linear = use_linear
         self.convs = ModuleList()
@@ -87,8 +88,7 @@ class SAGE(torch.nn.Module):
                 h = self.bns[idx](h)
             if self.residual and h.size(-1) == x.size(-1):
                 h = h + x[:h.size(0)]
-            x = self.activation(h)
-            x = self.dropout(x)
+            x = self.act_drop(h)
         h = self.convs[-1](x, adj_t)
         if self.use_linear:
             h = h + self.lins[-1](x)

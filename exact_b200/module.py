@@ -5,8 +5,8 @@ from collections import OrderedDict
 import torch.nn as nn
 
 from .conf import config
-from .layers import (GCNConv, QBatchNorm1d, QDropout, QDropout2, QGCNConv, QLinear, QReLU, QSAGEConv,
-                     SAGEConv)
+from .layers import (ActDropout, GCNConv, QBatchNorm1d, QDropout, QDropout2, QGCNConv, QLinear, QReLU,
+                     QReLUDropout, QSAGEConv, SAGEConv)
 
 
 class QModule(nn.Module):
@@ -19,7 +19,12 @@ class QModule(nn.Module):
     def convert_layers(module):
         """module.py:24-88."""
         for name, child in module.named_children():
-            if isinstance(child, (QBatchNorm1d, QLinear, QReLU, QGCNConv, QDropout, QDropout2, QSAGEConv)):
+            if isinstance(child, (QBatchNorm1d, QLinear, QReLU, QGCNConv, QDropout, QDropout2, QSAGEConv,
+                                  QReLUDropout)):
+                continue
+            if (isinstance(child, ActDropout) and isinstance(child.activation, nn.ReLU)
+                    and isinstance(child.dropout, nn.Dropout) and config.fuse_relu_dropout and not config.dropout2):
+                setattr(module, name, QReLUDropout(child.dropout.p))
                 continue
             if isinstance(child, nn.BatchNorm1d) and config.enable_quantized_bn:
                 setattr(module, name, QBatchNorm1d(child.num_features, child.eps, child.momentum, child.affine,

@@ -104,6 +104,15 @@ EXACT_API int exact_act_quantized_dropout_forward(const float* x, int64_t n, flo
 EXACT_API int exact_act_quantized_dropout_backward(const float* grad_out, const uint32_t* mask,
                                                    int64_t n, float p, float* grad_in, void* stream);
 
+/* ReLU followed by dropout in one pass over the activation (act_quantized_relu then
+ * act_quantized_dropout, quantization.cc:66-84 and 111-134, as models apply them back to back):
+ * out = dropout(max(x, 0)), bit-identical to the two calls with the same uniforms, and ONE 1-bit mask,
+ * set where the ReLU passed and the dropout kept.  Its backward is exact_act_quantized_dropout_backward
+ * with that mask (g / (1 - p) where set, else 0), which equals the two separate backward passes. */
+EXACT_API int exact_act_quantized_relu_dropout_forward(const float* x, int64_t n, float prob, const float* uniforms,
+                                                       uint64_t seed, uint64_t offset, int64_t index_offset,
+                                                       float* out, uint32_t* mask, void* stream);
+
 /* spmm.spmm_sum_fw / spmm_mean_fw (spmm.cc:31-55, 84-113 -> spmm_cuda.cu:27-170, reducer.cuh):
  * out[r, :] = reduce_{e in row r} value[e] * mat[col[e], :].  rowptr [M+1] and col [nnz] are int32
  * (idx_bytes = 4) or int64 (8); value [nnz] fp32 or NULL (all ones); mat [*, K]; out [M, K].

@@ -168,6 +168,23 @@ def test_one_node_sage_layer_is_a_reassociation(cfg_name, nodes):
         assert relfro(g, runs[2][2][k]) < 3e-2, (k, relfro(g, runs[2][2][k]))
 
 
+@pytest.mark.parametrize("cfg_name,nodes", [("cfg2", 3000), ("cfg4", 3000)])
+def test_relu_dropout_pair_as_one_module_changes_nothing(cfg_name, nodes):
+    """QModule turns a model's ReLU + Dropout pair (ActDropout) into QReLUDropout: one pass, one mask, the
+    same noise offset; outputs and gradients are bit-identical to QReLU followed by QDropout."""
+    runs = []
+    for fuse in (True, False):
+        config.fuse_relu_dropout = fuse
+        try:
+            loss, out, grads, _, _, _ = run_model(cfg_name, nodes, seed=8, fused_rp=True)
+        finally:
+            config.fuse_relu_dropout = True
+        runs.append((loss, out, grads))
+    assert runs[0][0] == runs[1][0] and torch.equal(runs[0][1], runs[1][1])
+    for k, g in runs[0][2].items():
+        assert torch.equal(g, runs[1][2][k]), k
+
+
 def test_eval_mode_bypasses_compression_and_state_dict_prefix():
     reset_config()
     net = QModule(models.GCN(16, 8, 4, 2, dropout=0.5, batch_norm=True)).cuda()

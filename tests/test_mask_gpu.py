@@ -68,3 +68,32 @@ def test_dropout_philox_and_reference_test():
 def test_dropout_eval_returns_input():
     x = torch.randn(10, 10, device="cuda")
     assert Q.act_quantized_dropout(x, 0.5, False) is x   # quantization.cc:115-117
+
+
+@pytest.mark.parametrize("p", [0.5, 0.2])
+@pytest.mark.parametrize("shape", [(2330, 602), (1001, 7), (5,)])
+def test_relu_dropout_in_one_pass_equals_the_two_ops(shape, p):
+    """exact_act_quantized_relu_dropout_forward: outputs and gradients bit-identical to act_quantized_relu
+    followed by act_quantized_dropout, with supplied uniforms and with the Philox draw of the same offset."""
+    from exact_b200 import config
+    x = np.random.default_rng(3).standard_normal(shape).astype(np.float32)
+    u = uniform01(shape, 4)
+    g = np.random.default_rng(5).standard_normal(shape).astype(np.float32)
+    for uniforms in (torch.from_numpy(u).cuda(), None):
+        outs = []
+        for fused in (True, False):
+            config.manual_seed(77)
+            xt = torch.from_numpy(x).cuda().requires_grad_()
+            if fused:
+                y = Q.act_quantized_relu_dropout(xt, p, True, uniforms=uniforms)
+            else:
+                y = Q.act_quantized_dropout(Q.act_quantized_relu(xt), p, True, uniforms=uniforms)
+            y.backward(torch.from_numpy(g).cuda())
+            outs.append((y.detach().clone(), xt.grad.clone()))
+        assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    # and against the oracle's two steps
+    out, keep = oracle.dropout_fw(oracle.relu_fw(x)[0], u, p)
+    xt = torch.from_numpy(x).cuda()
+    y = Q.act_quantized_relu_dropout(xt, p, True, uniforms=torch.from_numpy(u).cuda())
+    assert np.array_equal(y.cpu().numpy(), out)
+    assert torch.equal(Q.act_quantized_relu_dropout(xt, p, False), torch.relu(xt))
