@@ -137,6 +137,26 @@ def run_linear(M, K, N, reps):
             "rel_err_vs_fp64": err, "library_rel_err_vs_fp64": err_lib, "peak_kind": kind}
 
 
+def run_mask(N, D, p, reps):
+    """ReLU + dropout of a hidden layer in one pass (forward) and its backward: GB/s on 8 bytes + 1 bit per element."""
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(N, D, device=dev, generator=g).requires_grad_()
+    gout = torch.randn(N, D, device=dev, generator=g)
+    n = N * D
+    nbytes = 8 * n + n // 8
+    y = Q.act_quantized_relu_dropout(x, p, True)
+    ms_fw = _time(lambda: Q.act_quantized_relu_dropout(x, p, True), reps, None)
+    ms_bw = _time(lambda: torch.autograd.grad(y, x, gout, retain_graph=True), reps, None)
+    peak, kind = _peak()
+    out = []
+    for name, ms in (("relu_dropout_forward", ms_fw), ("relu_dropout_backward", ms_bw)):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out.append({"op": name, "N": N, "D": D, "p": p, "ms": round(ms, 4), "GB/s": round(gbs, 1),
+                    "frac": round(gbs / peak, 4), "peak": peak, "peak_kind": kind})
+    return out
+
+
 def run_spmm(nodes, avg_deg, K, reps, reduce):
     from . import graphs
     dev = torch.device("cuda")
@@ -157,7 +177,7 @@ def run_spmm(nodes, avg_deg, K, reps, reduce):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp", "linear"])
+    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp", "linear", "mask"])
     ap.add_argument("--kept-frac", type=float, nargs="*", default=[0.5, 0.125])
     ap.add_argument("--N", type=int, nargs="*", default=[100_000, 1_000_000, 10_000_000])
     ap.add_argument("--D", type=int, nargs="*", default=[64, 128, 256, 602])
@@ -174,6 +194,14 @@ def main():
     if a.op == "spmm":
         for K in a.K:
             print(json.dumps(run_spmm(a.nodes, a.avg_deg, K, a.reps, "mean")), flush=True)
+        return
+    if a.op == "mask":
+        for N in a.N:
+            for D in a.D:
+                if N * D * 4 > a.max_bytes:
+                    continue
+                for r in run_mask(N, D, 0.5, a.reps):
+                    print(json.dumps(r), flush=True)
         return
     if a.op == "linear":
         for M in a.N:
