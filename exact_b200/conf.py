@@ -36,8 +36,11 @@ class QuantizationConfig:
         # qlinear backward with a projected activation: form (g^T Xq) R^T instead of g^T (Xq R^T).  Same
         # result up to fp32 reassociation; the [N, D] reconstruction is never written.
         self.grad_weight_in_projected_space = True
-        # Read back (synchronising) the status word of kernels with bounded on-chip waits after each call.
+        # Read back (synchronising) the status word of kernels with bounded on-chip waits after each call
+        # (debugging).  Independently of it, QModule.forward polls the library-wide status word once per
+        # training step without synchronising (poll_device_status) and raises one step late.
         self.check_device_status = False
+        self.poll_device_status = True
         # SpMM: rows with more edges than this are cut into pieces that separate warps sum (0: never).
         self.spmm_long_row = 256
         # Do not produce compressed copies that no backward formula reads (the SpMM's dense operand
@@ -46,6 +49,15 @@ class QuantizationConfig:
         # Dense-layer GEMMs over node rows on the tensor cores with operands split into tf32 head and tail
         # (fp32-equivalent accuracy); False: the library's fp32 GEMM.
         self.linear_tensor_core = True
+        # Aggregation inside the one-node GraphSAGE layer: gather the dense operand as compact rows (kept
+        # columns + values per row) when at most this share of its entries is non-zero, as outputs of
+        # ReLU + dropout and gradients that passed their masks are.  Same sums bit for bit.
+        self.compact_operand = True
+        self.compact_operand_max_density = 0.5
+        # Row shards write their compact rows straight into every peer's buffer (plain stores over NVLink,
+        # buffers mapped with CUDA IPC) instead of going through a collective; off, or when the mapping
+        # fails, the collective-library exchange is used.
+        self.peer_exchange = True
         # Row-sharded aggregation: send operands that are mostly exact zeros (ReLU + dropout outputs and
         # gradients that passed their masks) zero-compacted; shards denser than the bound go as they are.
         self.compact_gather = True
@@ -63,6 +75,10 @@ class QuantizationConfig:
         # of A^T (g W_l): the transposed aggregation (and the gradient exchange of a row-sharded run)
         # works on g, which is narrower or sparser than g W_l.
         self.aggregate_gradient_first = True
+
+        # Called as hook(quantized, randmat) with every compressed activation the layers save (tests and the
+        # benchmark use it to hash the packed streams); None: no call.
+        self.quantized_hook = None
 
     def manual_seed(self, seed):
         self.seed = int(seed)

@@ -58,7 +58,7 @@ def linear_forward(a, weight, bias=None, a2=None, weight2=None, out=None, accumu
                     _lib.ptr(a2) if K2 else None, K2, a2.stride(0) if K2 else 0,
                     _lib.ptr(w2[n0:n1]) if K2 else None, w2.stride(0) if K2 else 0, n1 - n0,
                     _lib.ptr(bias[n0:n1]) if bias is not None else None, 1 if accumulate else 0, _lib.ptr(ws),
-                    _lib.ptr(cb), out.stride(0), _lib.stream_ptr())
+                    _lib.ptr(cb), out.stride(0), _lib.stream_ptr(), flops=6.0 * M * (K + K2) * (n1 - n0))
         if config.check_device_status:
             status = int(ws[:4].view(torch.int32).item())
             if status != 0:

@@ -1,8 +1,104 @@
-"""Zero-compacted rows (exact_rows_*): the exchange format of the row-sharded aggregation.  The
-reference is single-GPU and has no counterpart."""
+"""Sparse forms of dense operands that are mostly exact zeros.  The reference is single-GPU, gathers dense
+rows and has no counterpart.
+
+Compact rows (exact_crows_*): fixed-size slots holding each row's kept columns and values; what the SpMM
+gathers from and what row shards write into each other's memory.  Zero-compacted rows (exact_rows_*):
+mask + offsets + values, the wire format of the collective-library exchange."""
+import ctypes
+
 import torch
 
 from .. import _lib
+from ..conf import config
+
+
+class CompactRows:
+    """`rows` slots of an [rows, K] fp32 matrix in one uint8 buffer (see exact_crows_pack)."""
+
+    def __init__(self, buf, rows, K, density=0.25, address=None, device=None):
+        """`buf`: the uint8 tensor that holds the slots, or None with the device `address` of memory owned
+        elsewhere (a buffer the library allocated for peers to write into)."""
+        self.buf, self.rows, self.K = buf, rows, K
+        self.slot_bytes = slot_bytes(K)
+        self.density = density     # last measured share of kept entries (byte accounting only)
+        self._address = buf.data_ptr() if buf is not None else address
+        self._device = buf.device if buf is not None else device
+
+    @property
+    def device(self):
+        return self._device
+
+    def ptr(self):
+        return self._address
+
+
+class OperandForm:
+    """Remembers, per adjacency and call site, whether the dense operand of an aggregation is worth gathering
+    as compact rows.  The first call and every `reprobe`-th one measure the share of non-zero entries (one
+    host read of a device counter); the calls between reuse the decision, so the steady state has no
+    synchronisation.  Either form gives the same sums bit for bit."""
+
+    reprobe = 64
+
+    def __init__(self):
+        self.state = {}     # tag -> [mode, calls until the next probe, last density]
+
+    def mode(self, tag, K, dtype):
+        if not (config.compact_operand and dtype == torch.float32 and 64 <= K <= 256 and K % 4 == 0):
+            return "dense", 1.0
+        st = self.state.get(tag)
+        if st is None or st[1] <= 0:
+            return "probe", 0.25 if st is None else st[2]
+        st[1] -= 1
+        return st[0], st[2]
+
+    def decide(self, tag, density):
+        mode = "compact" if density <= config.compact_operand_max_density else "dense"
+        self.state[tag] = [mode, self.reprobe, density]
+        return mode
+
+
+def slot_bytes(K):
+    n = int(_lib.load().exact_crows_slot_bytes(K))
+    if n < 0:
+        raise RuntimeError(f"compact rows hold at most 256 columns (got {K})")
+    return n
+
+
+def crows_alloc(rows, K, device):
+    """An uninitialised buffer of `rows` slots."""
+    return CompactRows(torch.empty(rows * slot_bytes(K), dtype=torch.uint8, device=device), rows, K)
+
+
+def crows_pack(x, rowscale=None, out=None, row0=0, dst_ptrs=None, kept_total=None):
+    """Compact rows of x [n, K] (optionally x * rowscale[:, None]) into slots row0 .. row0 + n - 1 of `out`
+    (allocated when None) or of every buffer whose device address `dst_ptrs` lists (peers' buffers
+    included).  `kept_total`: a one-element int64 device tensor the number of kept entries is added to."""
+    if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1):
+        raise RuntimeError("crows_pack: expected a CUDA fp32 matrix with unit column stride")
+    n, K = x.shape
+    if out is None and dst_ptrs is None:
+        out = crows_alloc(row0 + n, K, x.device)
+    if dst_ptrs is None:
+        assert out.K == K and out.rows >= row0 + n
+        dst_ptrs = [out.ptr()]
+    if rowscale is not None:
+        rowscale = rowscale.reshape(-1)
+        assert rowscale.dtype == torch.float32 and rowscale.numel() == n and rowscale.is_contiguous()
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    nbytes = 4 * n * K + len(dst_ptrs) * n * (16 + K // 4 * 5)   # read once; ~25 % kept, written per destination
+    _lib.invoke("exact_crows_pack", nbytes, _lib.ptr(x), n, K, x.stride(0) if n else K, _lib.ptr(rowscale), row0, arr,
+                len(dst_ptrs), _lib.ptr(kept_total), _lib.stream_ptr(), device=x.device)
+    return out
+
+
+def crows_unpack(cr, n=None, row0=0):
+    """Dense [n, K] fp32 matrix of slots row0 .. row0 + n - 1."""
+    n = cr.rows - row0 if n is None else n
+    out = torch.empty((n, cr.K), dtype=torch.float32, device=cr.device)
+    _lib.invoke("exact_crows_unpack", 4 * n * cr.K, cr.ptr(), n, cr.K, row0, _lib.ptr(out), cr.K, _lib.stream_ptr(),
+                device=cr.device)
+    return out
 
 
 def _check(x):

@@ -46,6 +46,11 @@ inline int fail(int code, const char* fmt, ...) {
 
 int sm_count();  // cached multiProcessorCount of the current device (capi.cu)
 
+// Device address of the library-wide status word on the current device (capi.cu), or null without a device.
+// Kernels with bounded on-chip waits OR one of these codes into it when a wait expires; exact_status() reads it.
+int* status_word_ptr();
+enum DeviceStatusBits : int { EXB_STATUS_RP_PACK = 1, EXB_STATUS_UNPACK_RP = 2, EXB_STATUS_LINEAR = 4, EXB_STATUS_GRAD_WEIGHT = 8 };
+
 // Round keys of Philox4x32-10 for a 64-bit seed; lives in kernel parameters (constant bank) so the
 // per-round key XOR needs no register.
 struct PhiloxKey {

@@ -57,6 +57,7 @@ struct LinParams {
   float* C;
   const float* bias;
   int* status;
+  int* lib_status;    // library-wide status word of this device (capi.cu), or null
   long long M, ldc;
   int N, Npad;
   int kblocks1, kblocks;   // K tiles of the first operand pair, and of both pairs together
@@ -330,7 +331,10 @@ linear_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     tc_fence_after();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
-  if (threadIdx.x == 0 && s_abort) atomicExch(p.status, 1);
+  if (threadIdx.x == 0 && s_abort) {
+    atomicExch(p.status, 1);
+    if (p.lib_status) atomicOr(p.lib_status, EXB_STATUS_LINEAR);
+  }
 }
 
 // Heads and tails of [B | B2] (rows = output features), zero padded to [Npad, Kpad1 + Kpad2]; also
@@ -410,7 +414,7 @@ int exact_linear_forward(const float* A, int64_t M, int64_t K, int64_t lda, cons
   if (rc) return rc;
 
   LinParams p{};
-  p.C = C; p.bias = bias; p.status = status; p.M = M; p.ldc = ldc; p.N = (int)N; p.Npad = Npad;
+  p.C = C; p.bias = bias; p.status = status; p.lib_status = status_word_ptr(); p.M = M; p.ldc = ldc; p.N = (int)N; p.Npad = Npad;
   p.kblocks1 = Kpad1 / kLinTileK; p.kblocks = Kpad / kLinTileK;
   p.num_tiles = (int)((M + kLinTileM - 1) / kLinTileM);
   p.accumulate = accumulate ? 1 : 0;

@@ -31,6 +31,7 @@ struct RpBwdParams {
   const uint16_t* min_bf16;
   float* out;
   int* status;
+  int* lib_status;    // library-wide status word of this device (capi.cu), or null
   long long N;
   int D, k, Dpad, kpanels, kmma, bits;
   int num_tiles;
@@ -250,7 +251,10 @@ rp_unpack_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
     tc_fence_after();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
-  if (threadIdx.x == 0 && s_abort) atomicExch(p.status, 1);
+  if (threadIdx.x == 0 && s_abort) {
+    atomicExch(p.status, 1);
+    if (p.lib_status) atomicOr(p.lib_status, EXB_STATUS_UNPACK_RP);
+  }
 }
 
 // sign(R), zero padded to [Dpad, kpad32]; also clears the status word.
@@ -313,7 +317,7 @@ int exact_unpack_dequant_rp(const uint8_t* packed, int bits, const uint16_t* sca
   if (rc) return rc;
 
   RpBwdParams p{};
-  p.packed = packed; p.scale_bf16 = scale_bf16; p.min_bf16 = min_bf16; p.out = out; p.status = status;
+  p.packed = packed; p.scale_bf16 = scale_bf16; p.min_bf16 = min_bf16; p.out = out; p.status = status; p.lib_status = status_word_ptr();
   p.N = N; p.D = (int)D; p.k = (int)k; p.Dpad = Dpad; p.kpanels = kpanels; p.kmma = (int)((k + 7) / 8); p.bits = bits;
   p.num_tiles = (int)((N + kBwdTileM - 1) / kBwdTileM);
   p.a_bytes = (unsigned)a_bytes; p.b_bytes = (unsigned)b_bytes; p.panel_b_bytes = (unsigned)(Dpad * 128);

@@ -46,6 +46,7 @@ struct RpParams {
   uint16_t* min_bf16;
   float* y_out;       // optional [N, k] fp32 copy of the projection (tests)
   int* status;        // device word: 0 = ok
+  int* lib_status;    // library-wide status word of this device (capi.cu), or null
   long long N;
   long long row_offset;
   int D, k, kpad, bits;
@@ -280,7 +281,10 @@ rp_pack_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
-  if (threadIdx.x == 0 && s_abort) atomicExch(p.status, 1);
+  if (threadIdx.x == 0 && s_abort) {
+    atomicExch(p.status, 1);
+    if (p.lib_status) atomicOr(p.lib_status, EXB_STATUS_RP_PACK);
+  }
 }
 
 // sign(R)^T, zero padded to [kpad, Dpad]; also clears the status word.
@@ -358,6 +362,8 @@ int exact_rp_quantize_pack(const float* x, int64_t N, int64_t D, const float* R,
     return fail(EXB_ERR_UNSUPPORTED, "rp_quantize_pack: the TMA path needs 16-byte aligned rows (D %% 4 == 0); D = %lld", (long long)D);
   if (kpad > 256) return fail(EXB_ERR_UNSUPPORTED, "rp_quantize_pack: k = %lld exceeds one MMA tile (256)", (long long)k);
   EXB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "rp_quantize_pack: workspace must be 256-byte aligned");
+  // the epilogue stores 32-bit words of packed bytes when k % 4 == 0
+  EXB_REQUIRE(k % 4 != 0 || (reinterpret_cast<uintptr_t>(packed) & 3) == 0, "rp_quantize_pack: packed must be 4-byte aligned when k %% 4 == 0");
   EXB_REQUIRE((N + kRpTileM - 1) / kRpTileM < 2147483647LL / kRpTileM, "rp_quantize_pack: too many rows");
   cudaStream_t st = (cudaStream_t)stream;
   int* status = reinterpret_cast<int*>(workspace);
@@ -373,7 +379,7 @@ int exact_rp_quantize_pack(const float* x, int64_t N, int64_t D, const float* R,
   if (rc) return rc;
 
   RpParams p{};
-  p.packed = packed; p.scale_bf16 = scale_bf16; p.min_bf16 = min_bf16; p.y_out = y_out; p.status = status;
+  p.packed = packed; p.scale_bf16 = scale_bf16; p.min_bf16 = min_bf16; p.y_out = y_out; p.status = status; p.lib_status = status_word_ptr();
   p.N = N; p.row_offset = row_offset; p.D = (int)D; p.k = (int)k; p.kpad = kpad; p.bits = bits;
   p.num_tiles = (int)((N + kRpTileM - 1) / kRpTileM);
   p.kblocks = Dpad / kRpTileK;
@@ -386,10 +392,6 @@ int exact_rp_quantize_pack(const float* x, int64_t N, int64_t D, const float* R,
   int ctas_per_sm = 1;
   for (int c = 2; c <= 4; c++)
     if ((unsigned)c * cols <= 512 && (long long)c * 2 * p.stage_bytes + 4096 <= 200 * 1024) ctas_per_sm = c;
-  if (const char* e = getenv("EXACT_RP_CTAS")) {  // tuning knob
-    int v = atoi(e);
-    if (v >= 1 && v <= 4 && (unsigned)v * cols <= 512 && (long long)v * 2 * p.stage_bytes + 4096 <= 200 * 1024) ctas_per_sm = v;
-  }
   int stages = (int)((200 * 1024 / ctas_per_sm) / p.stage_bytes);
   if (stages > kRpMaxStages) stages = kRpMaxStages;
   if (stages < 2) stages = 2;

@@ -8,18 +8,87 @@ structure).  Weight gradients are summed with one small all-reduce per step.
 
 Every rank draws stochastic-rounding noise, dropout uniforms and projection signs keyed by global
 row / element indices (config.row_offset), so an N-rank run reproduces the 1-rank packed streams."""
+import ctypes
+import warnings
+
 import torch
 import torch.distributed as dist
 
+from . import _lib
 from .conf import config
 from .cpp_extension import rows as ext_rows
 from .cpp_extension import spmm as ext_spmm
 from .sparse import SparseTensor
 
 
+def _host_staged(t, group):
+    """CUDA tensors under the gloo backend (several ranks sharing one GPU in tests) go through the host."""
+    return t.is_cuda and dist.get_backend(group) == "gloo"
+
+
+def all_gather_into_tensor(out, inp, group=None):
+    if _host_staged(inp, group):
+        o = torch.empty(out.shape, dtype=out.dtype)
+        dist.all_gather_into_tensor(o, inp.cpu(), group=group)
+        out.copy_(o)
+    else:
+        dist.all_gather_into_tensor(out, inp, group=group)
+
+
+def all_reduce(t, op=dist.ReduceOp.SUM, group=None):
+    if _host_staged(t, group):
+        h = t.cpu()
+        dist.all_reduce(h, op=op, group=group)
+        t.copy_(h)
+    else:
+        dist.all_reduce(t, op=op, group=group)
+
+
 def shard_rows(n, world):
     """Rows per shard: ceil(n / world) rounded up to a multiple of 8."""
     return ((n + world - 1) // world + 7) // 8 * 8
+
+
+class PeerBuffers:
+    """One device buffer per rank that every rank of the node can write: allocated by the library on its
+    owner, exported as a CUDA IPC handle, opened by the other processes.  `ptrs[r]` is the address of rank
+    r's buffer as seen from this process (this rank's own allocation at ptrs[rank])."""
+
+    def __init__(self, nbytes, rank, world, group, device):
+        lib = _lib.load()
+        self.rank, self.world, self.group, self.device, self.nbytes = rank, world, group, device, nbytes
+        self.local = ctypes.c_void_p()
+        self.ptrs = [None] * world
+        self._imported = []
+        with torch.cuda.device(device):
+            _lib.check(lib.exact_peer_alloc(nbytes, ctypes.byref(self.local)), "exact_peer_alloc")
+            handle = ctypes.create_string_buffer(64)
+            _lib.check(lib.exact_peer_export(self.local, handle), "exact_peer_export")
+            handles = [None] * world
+            dist.all_gather_object(handles, (rank, handle.raw), group=group)
+            for r, raw in handles:
+                if r == rank:
+                    self.ptrs[r] = self.local.value
+                    continue
+                p = ctypes.c_void_p()
+                _lib.check(lib.exact_peer_import(ctypes.create_string_buffer(raw, 64), ctypes.byref(p)),
+                           "exact_peer_import")
+                self._imported.append(p)
+                self.ptrs[r] = p.value
+
+    def close(self):
+        """Unmap the peers' buffers, wait for every rank to have done so, free this rank's own."""
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for p in self._imported:
+                lib.exact_peer_close(p)
+            self._imported = []
+            if dist.is_initialized():
+                dist.barrier(group=self.group)
+            if self.local:
+                lib.exact_peer_free(self.local)
+                self.local = ctypes.c_void_p()
 
 
 class ShardedSparseTensor:
@@ -48,6 +117,75 @@ class ShardedSparseTensor:
         self._gather_buf = {}
         self._dense_streak = {}     # tag -> calls left before compaction is tried again after a dense operand
         self._const_gather = None   # (tensor, version, gathered): input features do not change between epochs
+        self._operand_form = ext_rows.OperandForm()
+        self._peers = {}            # K -> [PeerBuffers, PeerBuffers], used alternately
+        self._peer_turn = {}        # K -> exchanges done
+        self._peers_failed = False
+        self._sync = None           # the small tensor whose all-reduce orders the peers' writes before the reads
+
+    # ---- peer exchange ---------------------------------------------------------------------------------
+    def _peer_buffers(self, K, device):
+        """The two buffers of world * shard slots that compact rows of K columns alternate between, or None
+        when they cannot be set up on every rank (the collective exchange is used then).  Two, because a rank
+        may start writing the rows of the next exchange while a slower peer still reads those of this one;
+        the all-reduce of the exchange in between separates the reuse of a buffer from its last readers."""
+        if self._peers_failed or not (config.peer_exchange and device.type == "cuda" and dist.is_initialized()):
+            return None
+        pair = self._peers.get(K)
+        if pair is None:
+            ok, made = 1, []
+            try:
+                nbytes = self.world * self.shard * ext_rows.slot_bytes(K)
+                for _ in range(2):
+                    made.append(PeerBuffers(nbytes, self.rank, self.world, self.group, device))
+            except Exception as e:   # every rank must learn of it: agree below
+                ok = 0
+                warnings.warn(f"peer buffers unavailable ({e}); using the collective exchange")
+            flag = torch.tensor([ok], dtype=torch.int32, device=device)
+            all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            if int(flag.item()) == 0:
+                self._peers_failed = True
+                return None
+            pair = self._peers[K] = made
+            self._peer_turn[K] = 0
+        turn = self._peer_turn[K]
+        self._peer_turn[K] = turn + 1
+        return pair[turn & 1]
+
+    def exchange(self, x_local, tag, rowscale=None):
+        """Every row of the [local_rows, K] operand (times rowscale[:, None]) in local HBM: rows.CompactRows
+        with one slot per global row when the operand is mostly zeros and the ranks can write each other's
+        memory -- each rank compacts its rows once and stores them into all buffers, an all-reduce of one
+        word orders those stores before anyone's gathers, nothing is expanded -- else a dense [n_global, K]
+        matrix from the collective exchange."""
+        K = x_local.size(1)
+        dev = x_local.device
+        mode, density = self._operand_form.mode(tag, K, x_local.dtype)
+        if mode == "probe":
+            # share of non-zero entries over all ranks, from a local pack (one-off; every rank gets the same
+            # number, so every rank takes the same route)
+            kept = torch.zeros(1, dtype=torch.int64, device=dev)
+            ext_rows.crows_pack(x_local.contiguous(), rowscale, kept_total=kept)
+            all_reduce(kept, group=self.group)
+            density = float(kept.item()) / max(self.n_global * K, 1)
+            mode = self._operand_form.decide(tag, density)
+        if mode == "compact":
+            pb = self._peer_buffers(K, dev)
+            if pb is not None:
+                ext_rows.crows_pack(x_local.contiguous(), rowscale, row0=self.row_start, dst_ptrs=pb.ptrs)
+                if self._sync is None:
+                    self._sync = torch.zeros(1, dtype=torch.int32, device=dev)
+                all_reduce(self._sync, group=self.group)
+                return ext_rows.CompactRows(None, self.n_global, K, density, address=pb.ptrs[self.rank], device=dev)
+        if rowscale is not None:
+            x_local = x_local * rowscale.unsqueeze(1)
+        return self.gather(x_local.contiguous(), tag, try_compact=(mode == "compact"))
+
+    def close(self):
+        for pair in self._peers.values():
+            for pb in pair:
+                pb.close()
+        self._peers = {}
 
     @property
     def local_rows(self):
@@ -63,14 +201,15 @@ class ShardedSparseTensor:
             self._gather_buf[key] = buf
         return buf
 
-    def gather(self, x_local, tag):
-        """All rows of an [local_rows, K] matrix in local HBM: [n_global, K].  Operands that are mostly
-        exact zeros (ReLU + dropout outputs, gradients that passed their masks) cross NVLink
-        zero-compacted and are expanded on arrival; others go as they are."""
+    def gather(self, x_local, tag, try_compact=True):
+        """All rows of an [local_rows, K] matrix in local HBM: [n_global, K], through the collective library.
+        Operands that are mostly exact zeros (ReLU + dropout outputs, gradients that passed their masks)
+        cross NVLink zero-compacted and are expanded on arrival; others (and all with try_compact=False) go
+        as they are."""
         if self.world == 1:
             return x_local
         K = x_local.size(1)
-        if (config.compact_gather and x_local.dtype == torch.float32 and K % 32 == 0 and K >= 64):
+        if (try_compact and config.compact_gather and x_local.dtype == torch.float32 and K % 32 == 0 and K >= 64):
             left = self._dense_streak.get(tag, 0)
             if left > 0:
                 self._dense_streak[tag] = left - 1
@@ -89,7 +228,7 @@ class ShardedSparseTensor:
             pad[:x_local.size(0)].copy_(x_local)
             pad[x_local.size(0):].zero_()
             x_local = pad
-        dist.all_gather_into_tensor(buf, x_local.contiguous(), group=self.group)
+        all_gather_into_tensor(buf, x_local.contiguous(), group=self.group)
         return buf[:self.n_global]
 
     def _gather_compacted(self, x_local, tag):
@@ -108,7 +247,7 @@ class ShardedSparseTensor:
         rowoff[:1].zero_()
         torch.cumsum(rowcnt, 0, out=rowoff[1:])
         counts = self._buffer((tag, "counts"), (R,), torch.int64, dev)
-        dist.all_gather_into_tensor(counts, rowoff[S:S + 1], group=self.group)
+        all_gather_into_tensor(counts, rowoff[S:S + 1], group=self.group)
         cap = int(counts.max().item())          # the one host synchronisation of the exchange
         if cap > config.compact_gather_max_density * S * K:
             return None
@@ -116,11 +255,11 @@ class ShardedSparseTensor:
         vals = torch.empty(cap, dtype=torch.float32, device=dev)
         ext_rows.compact_write(x_local, rowoff, vals)
         vals_all = torch.empty(R * cap, dtype=torch.float32, device=dev)
-        dist.all_gather_into_tensor(vals_all, vals, group=self.group)
+        all_gather_into_tensor(vals_all, vals, group=self.group)
         rowoff_all = self._buffer((tag, "rowoff_all"), (R * (S + 1),), torch.int64, dev)
-        dist.all_gather_into_tensor(rowoff_all, rowoff, group=self.group)
+        all_gather_into_tensor(rowoff_all, rowoff, group=self.group)
         mask_all = self._buffer((tag, "mask_all"), (R * S, W), torch.int32, dev)
-        dist.all_gather_into_tensor(mask_all, mask, group=self.group)
+        all_gather_into_tensor(mask_all, mask, group=self.group)
         out = self._buffer((tag, K, x_local.dtype), (R * S, K), torch.float32, dev)
         ext_rows.expand(mask_all, rowoff_all, vals_all, R * S, K, S, S + 1, cap, out)
         return out[:self.n_global]
@@ -186,7 +325,7 @@ def allreduce_gradients(params, group=None):
     if not grads or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return
     flat = torch.cat([g.reshape(-1) for g in grads])
-    dist.all_reduce(flat, group=group)
+    all_reduce(flat, group=group)
     off = 0
     for g in grads:
         g.copy_(flat[off:off + g.numel()].view_as(g))

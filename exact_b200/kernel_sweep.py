@@ -157,22 +157,43 @@ def run_mask(N, D, p, reps):
     return out
 
 
-def run_spmm(nodes, avg_deg, K, reps, reduce):
+def run_spmm(nodes, avg_deg, K, reps, reduce, density=None):
+    """Mean / sum aggregation over an R-MAT graph.  `density`: the share of non-zero entries of the dense
+    operand; below 1 the operand is also packed into compact rows and the SpMM that gathers those is timed
+    beside the dense one (same output bit for bit), with the packing pass on its own line."""
     from . import graphs
+    from .cpp_extension import rows as RW
     dev = torch.device("cuda")
     adj = graphs.rmat(nodes, int(nodes * avg_deg / 2), 0, dev, self_loops=False)
     adj.to_int32_()
     rowptr, col, _ = adj.csr()
-    x = torch.randn(nodes, K, device=dev)
-    call = lambda: S._spmm(rowptr, col, None, x, reduce)
-    ms = _time(call, reps, None)
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(nodes, K, device=dev, generator=g)
+    if density is not None and density < 1.0:
+        x = x * (torch.rand(nodes, K, device=dev, generator=g) < density)
     nnz = col.numel()
-    nbytes = nnz * K * 4 + nnz * 4 + (nodes + 1) * 4 + nodes * K * 4
     peak, kind = _peak()
-    gbs = nbytes / (ms * 1e-3) / 1e9
-    return {"op": "spmm_" + reduce, "nodes": nodes, "nnz": nnz, "K": K, "ms": round(ms, 4), "GB/s": round(gbs, 1),
-            "frac": round(gbs / peak, 4), "peak": peak, "peak_kind": kind,
-            "perfect_reuse_GB/s": round((2 * nodes * K * 4 + nnz * 4) / (ms * 1e-3) / 1e9, 1)}
+    out = []
+    forms = [("dense", x)]
+    if density is not None and density < 1.0 and K <= 256 and K % 4 == 0:
+        cr = RW.crows_pack(x)
+        cr.density = density
+        ms_pack = _time(lambda: RW.crows_pack(x, out=cr), reps, None)
+        pack_bytes = nodes * K * 4 + nodes * (16 + int(density * K) * 5)
+        out.append({"op": "crows_pack", "nodes": nodes, "K": K, "density": density, "ms": round(ms_pack, 4),
+                    "GB/s": round(pack_bytes / (ms_pack * 1e-3) / 1e9, 1),
+                    "frac": round(pack_bytes / (ms_pack * 1e-3) / 1e9 / peak, 4), "peak": peak, "peak_kind": kind})
+        forms.append(("compact", cr))
+    for form, operand in forms:
+        ms = _time(lambda: S._spmm(rowptr, col, None, operand, reduce), reps, None)
+        row_bytes = K * 4 if form == "dense" else 16 + int(density * K) * 5
+        must = nodes * row_bytes + nnz * 4 + (nodes + 1) * 4 + nodes * K * 4
+        l2 = nnz * row_bytes + nnz * 4 + (nodes + 1) * 4 + nodes * K * 4
+        out.append({"op": "spmm_" + reduce, "operand": form, "nodes": nodes, "nnz": nnz, "K": K, "density": density,
+                    "ms": round(ms, 4), "GB/s": round(must / (ms * 1e-3) / 1e9, 1),
+                    "frac": round(must / (ms * 1e-3) / 1e9 / peak, 4), "l2_side_GB/s": round(l2 / (ms * 1e-3) / 1e9, 1),
+                    "peak": peak, "peak_kind": kind})
+    return out
 
 
 def main():
@@ -188,12 +209,15 @@ def main():
     ap.add_argument("--nodes", type=int, default=1_000_000)
     ap.add_argument("--avg-deg", type=float, default=50.0)
     ap.add_argument("--K", type=int, nargs="*", default=[256])
+    ap.add_argument("--density", type=float, default=None,
+                    help="--op spmm: share of non-zero operand entries; below 1 the compact-rows SpMM is timed too")
     ap.add_argument("--max-bytes", type=float, default=12e9, help="skip cases whose input exceeds this")
     a = ap.parse_args()
     _lib.load()
     if a.op == "spmm":
         for K in a.K:
-            print(json.dumps(run_spmm(a.nodes, a.avg_deg, K, a.reps, "mean")), flush=True)
+            for r in run_spmm(a.nodes, a.avg_deg, K, a.reps, "mean", a.density):
+                print(json.dumps(r), flush=True)
         return
     if a.op == "mask":
         for N in a.N:

@@ -4,6 +4,7 @@ from collections import OrderedDict
 
 import torch.nn as nn
 
+from . import _lib
 from .conf import config
 from .layers import (ActDropout, GCNConv, QBatchNorm1d, QDropout, QDropout2, QGCNConv, QLinear, QReLU,
                      QReLUDropout, QSAGEConv, SAGEConv)
@@ -46,6 +47,13 @@ class QModule(nn.Module):
                 QModule.convert_layers(child)
 
     def forward(self, *args, **kwargs):
+        if self.training and config.poll_device_status:
+            # one step late and without waiting for the GPU: raises if a kernel of an earlier step gave up on
+            # a bounded on-chip wait (its outputs were incomplete)
+            for a in args:
+                if getattr(a, "is_cuda", False):
+                    _lib.poll_status(a.device)
+                    break
         return self.model(*args, **kwargs)
 
     def load_state_dict(self, state_dict, strict=True):

@@ -147,11 +147,16 @@ def project_and_quantize(input, scheme, rp=True):
                 randmat = _rademacher(input.shape[1], kept_acts, input.device, input.dtype)
                 q_bits = config.activation_compression_bits[0]
                 q_input, q_scale, q_min = ext_quantization.rp_quantize_pack(input, randmat, q_bits)
-            return (q_input, q_bits, q_scale, q_min), randmat, torch.Size([input.shape[0], kept_acts])
+            quantized = (q_input, q_bits, q_scale, q_min)
+            if config.quantized_hook is not None:
+                config.quantized_hook(quantized, randmat)
+            return quantized, randmat, torch.Size([input.shape[0], kept_acts])
         dim_reduced_input, randmat = input2rp(input, kept_acts)
     else:
         dim_reduced_input, randmat = input, None
     quantized = quantize_activation(dim_reduced_input, scheme)
+    if config.quantized_hook is not None:
+        config.quantized_hook(quantized, randmat)
     return quantized, randmat, dim_reduced_input.shape
 
 

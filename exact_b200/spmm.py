@@ -6,6 +6,7 @@ from torch.autograd.function import Function
 
 from .conf import config
 from .cpp_extension import backward_func as ext_backward_func
+from .cpp_extension import rows as ext_rows
 from .cpp_extension import spmm as ext_spmm
 from .ops import linear_backward_from_compressed, project_and_quantize, qspmm_mean, qspmm_sum
 from .qscheme import QScheme
@@ -61,27 +62,61 @@ class QMatmul(torch.nn.Module):
         return qmatmul(src, other, self.reduce, quantized, randmat, self.scheme)
 
 
-def _aggregate(src, other, reduce):
-    """reduce(A, other) with nothing recorded for backward."""
-    from .dist import ShardedSparseTensor, sharded_spmm
-    if isinstance(src, ShardedSparseTensor):
-        return ext_spmm._spmm(src.rowptr, src.col, src.value, sharded_spmm.gathered_operand(src, other), reduce)
-    rowptr, col, value = src.csr()
-    return ext_spmm._spmm(rowptr, col, value, other, reduce)
+def _form_of(obj):
+    form = getattr(obj, "_operand_form", None)
+    if form is None:
+        form = obj._operand_form = ext_rows.OperandForm()
+    return form
 
 
-def _aggregate_transposed(src, grad, reduce):
-    """Gradient of reduce(A, other) with respect to `other` (spmm.cc:70-77, 128-137).  Inside the one-node
-    layer the result is an fp32 regrouping of the separate nodes' anyway, so the SpMM may regroup too."""
+def _operand(src, x, tag, rowscale=None):
+    """The dense operand x (times rowscale[:, None]) of an aggregation over `src`, with every row the local
+    adjacency rows reference in local HBM: a dense matrix or rows.CompactRows."""
     from .dist import ShardedSparseTensor
     if isinstance(src, ShardedSparseTensor):
-        return ext_spmm._spmm(src.t_rowptr, src.t_col, src.t_w, src.gather(grad, "bw"), "sum", regroup=True)
-    t_ptr, t_col, t_w = src.storage.transposed(reduce)
-    return ext_spmm._spmm(t_ptr, t_col, t_w, grad, "sum", regroup=True)
+        return src.exchange(x, tag, rowscale)
+    form = _form_of(src.storage)
+    mode, density = form.mode(tag, x.size(1), x.dtype)
+    if mode != "dense":
+        x = x.contiguous()
+        kept = torch.zeros(1, dtype=torch.int64, device=x.device) if mode == "probe" else None
+        cr = ext_rows.crows_pack(x, rowscale, kept_total=kept)
+        if mode == "probe":
+            density = float(kept.item()) / max(x.numel(), 1)
+            mode = form.decide(tag, density)
+        if mode == "compact":
+            cr.density = density
+            return cr
+    return x if rowscale is None else x * rowscale.unsqueeze(1)
+
+
+def _aggregate(src, other, reduce, tag="fw"):
+    """reduce(A, other) with nothing recorded for backward."""
+    from .dist import ShardedSparseTensor
+    operand = _operand(src, other, tag)
+    if isinstance(src, ShardedSparseTensor):
+        return ext_spmm._spmm(src.rowptr, src.col, src.value, operand, reduce)
+    rowptr, col, value = src.csr()
+    return ext_spmm._spmm(rowptr, col, value, operand, reduce)
+
+
+def _aggregate_transposed(src, grad, reduce, rowscale=None, prescaled=False, tag="bw"):
+    """Gradient of reduce(A, other) with respect to `other` (spmm.cc:70-77, 128-137).  Inside the one-node
+    layer the result is an fp32 regrouping of the separate nodes' anyway, so the SpMM may regroup too.
+    With `rowscale` = 1 / max(deg, 1) the caller asks for A_mean^T g as A^T (D^-1 g): the rows of `grad` are
+    scaled on the way into the SpMM and no per-edge weights are read (one load and one multiply per edge
+    less: 10.0 against 12.0 ms at 125.8 M edges x 256 columns).  `prescaled`: `grad` already holds D^-1 g."""
+    from .dist import ShardedSparseTensor
+    operand = _operand(src, grad, tag, rowscale)
+    unweighted = rowscale is not None or prescaled
+    if isinstance(src, ShardedSparseTensor):
+        return ext_spmm._spmm(src.t_rowptr, src.t_col, None if unweighted else src.t_w, operand, "sum", regroup=True)
+    t_ptr, t_col, t_w = src.storage.transposed("sum" if unweighted else reduce)
+    return ext_spmm._spmm(t_ptr, t_col, None if unweighted else t_w, operand, "sum", regroup=True)
 
 
 def _inverse_degree(src):
-    """1 / max(deg, 1) of this rank's rows as an [rows, 1] fp32 column, or None when the adjacency carries
+    """1 / max(deg, 1) of this rank's rows as an [rows] fp32 vector, or None when the adjacency carries
     edge values (the per-edge weights of the mean's transpose are then not a row scaling)."""
     from .dist import ShardedSparseTensor
     if isinstance(src, ShardedSparseTensor):
@@ -89,7 +124,7 @@ def _inverse_degree(src):
             return None
         inv = getattr(src, "_inv_deg", None)
         if inv is None:
-            inv = (src.rowptr[1:] - src.rowptr[:-1]).to(torch.float32).clamp_(min=1).reciprocal_().unsqueeze(1)
+            inv = (src.rowptr[1:] - src.rowptr[:-1]).to(torch.float32).clamp_(min=1).reciprocal_()
             src._inv_deg = inv
         return inv
     st = src.storage
@@ -97,19 +132,9 @@ def _inverse_degree(src):
         return None
     inv = getattr(st, "_inv_deg", None)
     if inv is None:
-        inv = st.rowcount().to(torch.float32).clamp_(min=1).reciprocal_().unsqueeze(1)
+        inv = st.rowcount().to(torch.float32).clamp_(min=1).reciprocal_()
         st._inv_deg = inv
     return inv
-
-
-def _aggregate_transposed_mean_scaled(src, scaled_grad):
-    """A_mean^T g = A^T (D^-1 g): `scaled_grad` already holds D^-1 g, so the SpMM needs no edge weights
-    (one load and one multiply per edge less: 10.0 against 12.0 ms at 125.8 M edges x 256 columns)."""
-    from .dist import ShardedSparseTensor
-    if isinstance(src, ShardedSparseTensor):
-        return ext_spmm._spmm(src.t_rowptr, src.t_col, None, src.gather(scaled_grad, "bw"), "sum", regroup=True)
-    t_ptr, t_col, _ = src.storage.transposed("sum")
-    return ext_spmm._spmm(t_ptr, t_col, None, scaled_grad, "sum", regroup=True)
 
 
 class qsage_layer(Function):
@@ -130,7 +155,7 @@ class qsage_layer(Function):
         q_x, randmat_x, proj_x = project_and_quantize(x, scheme_x, True)
         if w_r is None:
             q_x = randmat_x = None   # drawn (the noise stream stays that of the separate nodes), read by nothing
-        agg = _aggregate(src, x, reduce)
+        agg = _aggregate(src, x, reduce, tag="fw%d" % x.size(1))
         q_agg, randmat_agg, proj_agg = project_and_quantize(agg, scheme_l, True)
         empty_cache(config.empty_cache_threshold)
         ctx.src, ctx.reduce = src, reduce
@@ -161,20 +186,18 @@ class qsage_layer(Function):
                 pad = (-out_f) % 4   # whole 128-bit column groups for the gather
                 inv = _inverse_degree(ctx.src) if ctx.reduce == "mean" else None
                 gp, wp = g, w_l
+                prescaled = False
                 if pad:
                     gp = g.new_zeros((g.size(0), out_f + pad))
                     if inv is not None:
-                        torch.mul(g, inv, out=gp[:, :out_f])
+                        torch.mul(g, inv.unsqueeze(1), out=gp[:, :out_f])   # pad and scale in one pass
+                        inv, prescaled = None, True
                     else:
                         gp[:, :out_f].copy_(g)
                     wp = w_l.new_zeros((out_f + pad, in_f))
                     wp[:out_f].copy_(w_l)
-                elif inv is not None:
-                    gp = g * inv
-                if inv is not None:
-                    t = _aggregate_transposed_mean_scaled(ctx.src, gp)
-                else:
-                    t = _aggregate_transposed(ctx.src, gp, ctx.reduce)
+                t = _aggregate_transposed(ctx.src, gp, ctx.reduce, rowscale=inv, prescaled=prescaled,
+                                          tag="bw%d" % gp.size(1))
                 grad_x = ext_backward_func.linear_forward(t, wp.t(), None, a2=g if w_r is not None else None,
                                                           weight2=w_r.t() if w_r is not None else None)
             else:

@@ -43,6 +43,20 @@ enum { EXACT_SPMM_REGROUP = 0x100 };
 EXACT_API int exact_version(void);
 EXACT_API const char* exact_last_error(void);
 
+/* Device-side status.  The kernels that wait on on-chip barriers (exact_rp_quantize_pack,
+ * exact_unpack_dequant_rp, exact_linear_forward, exact_grad_weight_from_packed) bound every wait; a kernel
+ * whose wait runs out abandons its tile, returns, and ORs a bit into one status word per device (1, 2, 4, 8
+ * in that order) besides the word in its own workspace.  exact_status copies the word of the current device
+ * to *status (it synchronises `stream`); non-zero means some output since the last exact_clear_status is
+ * incomplete.  exact_set_status writes the word, so that a host can exercise its error path without making
+ * a wait expire.  No counterpart in the reference (its kernels never wait). */
+EXACT_API int exact_status(int* status, void* stream);
+/* The same copy without the synchronisation: *pinned_host_status (page-locked host memory) is valid once the
+ * work enqueued on `stream` so far has completed. */
+EXACT_API int exact_status_async(int* pinned_host_status, void* stream);
+EXACT_API int exact_clear_status(void* stream);
+EXACT_API int exact_set_status(int code, void* stream);
+
 /* Bytes of the packed stream for an [N, D] activation at `bits` per element: ceil(N / (8/bits)) * D.
  * The reference allocates one more byte and never writes it (quantization_cuda_kernel.cu:110-113);
  * callers that mirror its tensor shape allocate exact_packed_bytes() + 1. */
@@ -138,9 +152,58 @@ EXACT_API int exact_spmm(const void* rowptr, const void* col, int idx_bytes, con
  *                                      125.8 M edges x 256 columns).  NULL: piece j writes slot j.
  *   scratch       [n_items, K]  fp32   caller-owned; holds the partial sums of the pieces
  * Rows up to the threshold are summed exactly as exact_spmm sums them; a long row is the in-order sum
- * of its pieces' sums. */
+ * of its pieces' sums.  Every row longer than long_threshold must be listed: with n_items = 0 such rows
+ * are left unwritten.  Column indices are staged as 32-bit values, so M (and the operand) stay below 2^32
+ * rows (refused otherwise). */
 EXACT_API int exact_spmm_split(const void* rowptr, const void* col, int idx_bytes, const float* value,
                                const float* mat, int64_t M, int64_t K, int reduce, int64_t long_threshold,
+                               const int32_t* item_row, const int64_t* item_begin, const int64_t* item_end,
+                               const int32_t* item_slot, int64_t n_items, const int32_t* long_row,
+                               const int32_t* long_item_ptr, int64_t n_long, float* scratch, float* out,
+                               void* stream);
+
+/* Compact rows: a dense operand whose entries are mostly exact zeros, in the form the SpMM gathers it and
+ * row shards exchange it between GPUs.  No counterpart in the reference (it is single-GPU and gathers dense
+ * rows, spmm_cuda.cu:86-93).  Row r of x [n, K] fp32 (0 < K <= 256, row pitch ldx) goes to a slot of
+ * exact_crows_slot_bytes(K) = 16 + pad16(K) + 4 K bytes at slot index row0 + r of each destination buffer:
+ *   +0  uint32 cnt;   +16  uint8 col[cnt] (ascending);   +16 + pad16(K)  fp32 val[cnt].
+ * An entry is kept when any of its 32 bits is set (only +0.0 is dropped: an fp32 sum that starts at +0.0 is
+ * not changed by adding +0.0, so sums over compact rows equal sums over the dense rows bit for bit).
+ *   rowscale   [n] fp32 or NULL: row r is multiplied by rowscale[r] first (the 1/deg scaling of the
+ *              transposed mean, spmm.cc:128-133, folded into this pass)
+ *   dst        host array of n_dst (1..8) device pointers, 16-byte aligned, each with room for every slot
+ *              written.  A pointer may be a peer GPU's buffer (mapped into this process): the rows are then
+ *              written there with plain stores over NVLink; the caller orders those writes before the
+ *              peer's reads (stream order on this GPU, then a collective or event both sides wait on).
+ *   kept_total device uint64 or NULL: the number of kept entries is added to it (one atomic per CTA).
+ * exact_crows_unpack writes dense rows out [n, K] (row pitch ldo) from slots row0 .. row0 + n - 1. */
+EXACT_API int64_t exact_crows_slot_bytes(int64_t K);
+EXACT_API int exact_crows_pack(const float* x, int64_t n, int64_t K, int64_t ldx, const float* rowscale, int64_t row0,
+                               void* const* dst, int n_dst, uint64_t* kept_total, void* stream);
+EXACT_API int exact_crows_unpack(const void* buf, int64_t n, int64_t K, int64_t row0, float* out, int64_t ldo,
+                                 void* stream);
+
+/* Buffers that the ranks of a row-sharded run write into each other (one process per GPU, one node).  No
+ * counterpart in the reference.  These are the only entry points that allocate or free device memory:
+ *   exact_peer_alloc   cudaMalloc of `bytes` on the current device;
+ *   exact_peer_export  the buffer's CUDA IPC handle (EXACT_PEER_HANDLE_BYTES bytes, host memory) for the other
+ *                      processes of the node;
+ *   exact_peer_import  in another process: opens a handle and returns a device pointer to the owner's buffer,
+ *                      valid on the current device (peer access is enabled);  exact_peer_close  unmaps it;
+ *   exact_peer_free    in the owner, after the peers have closed their mappings. */
+#define EXACT_PEER_HANDLE_BYTES 64
+EXACT_API int exact_peer_alloc(int64_t bytes, void** ptr);
+EXACT_API int exact_peer_free(void* ptr);
+EXACT_API int exact_peer_export(const void* ptr, void* handle64);
+EXACT_API int exact_peer_import(const void* handle64, void** ptr);
+EXACT_API int exact_peer_close(void* ptr);
+
+/* exact_spmm / exact_spmm_split with the dense operand given as compact rows: `crows` holds one slot per
+ * operand row (slot index = column index of the adjacency), K <= 256, K % 4 == 0.  Same sums, same order
+ * (spmm_cuda.cu:86-93 for rows up to the threshold), bit-identical to the dense call on the matrix the
+ * slots were packed from.  n_items = 0 with long_threshold = 0: no long-row pieces (every row by one warp). */
+EXACT_API int exact_spmm_crows(const void* rowptr, const void* col, int idx_bytes, const float* value,
+                               const void* crows, int64_t M, int64_t K, int reduce, int64_t long_threshold,
                                const int32_t* item_row, const int64_t* item_begin, const int64_t* item_end,
                                const int32_t* item_slot, int64_t n_items, const int32_t* long_row,
                                const int32_t* long_item_ptr, int64_t n_long, float* scratch, float* out,
@@ -152,6 +215,8 @@ EXACT_API int exact_spmm_split(const void* rowptr, const void* col, int idx_byte
  * partial sums go to an array of EXACT_SPMM_STATIC_SCRATCH_FLOATS floats (16 MiB) that is part of the
  * library image: every GPU that loads the library holds it until the process exits.
  *   - n_items * K must not exceed EXACT_SPMM_STATIC_SCRATCH_FLOATS; larger plans are refused (code 1).
+ *   - The plan arrays live on the device and are trusted: item_slot must be a permutation of
+ *     [0, n_items) and long_item_ptr[n_long] == n_items, or a piece writes outside the array.
  *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress with
  *     that device current) and keeps it; make that first call before recording or capturing anything.
  *   - All calls on a device share the array: calls that may overlap on the GPU (different streams) race.
@@ -169,7 +234,7 @@ EXACT_API int exact_spmm_split_static(const void* rowptr, const void* col, int i
  * exact/exact/ops.py:142-149 (torch.matmul(input, rand_matrix), ops.py:117, then ops.py:61-83) as one
  * TMA-fed tcgen05 (tf32) GEMM whose epilogue computes the row statistics and packs, so the [N, k]
  * product never reaches HBM.
- *   x [N, D] fp32 (D % 4 == 0, 16-byte aligned);  R [D, k] fp32 with entries +-1/sqrt(k) (only the
+ *   x [N, D] fp32 (D % 4 == 0, 16-byte aligned; packed 4-byte aligned when k % 4 == 0);  R [D, k] fp32 with entries +-1/sqrt(k) (only the
  *   signs are read; 1/sqrt(k) is applied in fp32);  k <= 256.  Other shapes return code 3 and the
  *   caller uses the unfused chain.
  *   workspace: exact_rp_workspace_bytes(D, k) bytes, 256-byte aligned, caller-owned.  Its first int32

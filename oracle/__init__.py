@@ -269,3 +269,37 @@ def rows_expand(mask, rowoff, vals, K):
     out = np.zeros((n, K), dtype=np.float32)
     out[keep] = vals[:rowoff[n]]
     return out
+
+
+def crows_slot_bytes(K):
+    """Bytes of one compact-row slot: 16-byte header, column bytes padded to 16, K fp32 values."""
+    return 16 + (K + 15) // 16 * 16 + 4 * K
+
+
+def crows_pack(x, rowscale=None):
+    """Compact rows of x [n, K] fp32 (K <= 256), optionally x * rowscale[:, None] in fp32 first (no counterpart
+    in the reference): a zero-filled uint8 buffer [n, slot] with, per row, uint32 count at +0, the kept columns
+    (any of the 32 bits set) ascending at +16 and their values at +16 + pad16(K)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    if rowscale is not None:
+        x = (x * np.asarray(rowscale, dtype=np.float32).reshape(-1, 1)).astype(np.float32)
+    n, K = x.shape
+    slot = crows_slot_bytes(K)
+    voff = 16 + (K + 15) // 16 * 16
+    buf = np.zeros((n, slot), dtype=np.uint8)
+    bits = x.view(np.uint32)
+    for r in range(n):
+        cols = np.nonzero(bits[r])[0]
+        buf[r, 0:4] = np.array([cols.size], dtype=np.uint32).view(np.uint8)
+        buf[r, 16:16 + cols.size] = cols.astype(np.uint8)
+        buf[r, voff:voff + 4 * cols.size] = bits[r, cols].view(np.uint8)
+    return buf
+
+
+def crows_used_mask(buf, K):
+    """Boolean [n, slot]: the bytes of each slot that crows_pack defines (header word, used columns and values)."""
+    n, slot = buf.shape
+    voff = 16 + (K + 15) // 16 * 16
+    cnt = buf[:, 0:4].copy().view(np.uint32).reshape(n).astype(np.int64)
+    pos = np.arange(slot)[None, :]
+    return (pos < 4) | ((pos >= 16) & (pos < 16 + cnt[:, None])) | ((pos >= voff) & (pos < voff + 4 * cnt[:, None]))

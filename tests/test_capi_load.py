@@ -96,3 +96,77 @@ def test_dense_layer_host_logic_on_cpu():
     big = torch.randn(70000, 6, generator=g)
     x = torch.randn(70000, 3, generator=g)
     assert torch.allclose(B.rows_reduce_mm(big, x), big.t() @ x, rtol=1e-4, atol=1e-3)
+
+
+def test_argument_checks_added_later_reject_before_any_launch():
+    lib = _lib.load()
+    one, odd = ctypes.c_void_p(256), ctypes.c_void_p(258)
+    # the fused projection + pack stores 32-bit words of packed bytes when k % 4 == 0: an unaligned `packed` is
+    # an argument error (code 1), not a misaligned store on the device
+    rc = lib.exact_rp_quantize_pack(one, 128, 64, one, 8, 2, 0, 0, 0, one, odd, one, one, None, None)
+    assert rc == 1 and b"4-byte aligned" in lib.exact_last_error()
+    # the static-scratch entry compares n_items * K with its limit without overflowing int64
+    big = 1 << 62
+    rc = lib.exact_spmm_split_static(one, one, 4, None, one, 8, 256, 0, 256, one, one, one, None, big, one, one, 1, one,
+                                     None)
+    assert rc == 1 and b"built-in scratch" in lib.exact_last_error()
+    # compact rows: at most 256 columns, 1..8 aligned destinations
+    assert lib.exact_crows_slot_bytes(256) == 16 + 256 + 1024 and lib.exact_crows_slot_bytes(100) == 16 + 112 + 400
+    assert lib.exact_crows_slot_bytes(257) == -1
+    dst = (ctypes.c_void_p * 1)(odd.value)
+    rc = lib.exact_crows_pack(one, 4, 64, 64, None, 0, dst, 1, None, None)
+    assert rc == 1 and b"aligned" in lib.exact_last_error()
+    rc = lib.exact_crows_pack(one, 4, 300, 300, None, 0, dst, 1, None, None)
+    assert rc == 1 and b"256" in lib.exact_last_error()
+    rc = lib.exact_crows_pack(one, 4, 64, 64, None, 0, dst, 9, None, None)
+    assert rc == 1
+    rc = lib.exact_spmm_crows(one, one, 4, None, one, 8, 258, 0, 0, None, None, None, None, 0, None, None, 0, None, one,
+                              None)
+    assert rc == 1 and b"multiple of 4" in lib.exact_last_error()
+    rc = lib.exact_spmm(one, one, 4, None, one, (1 << 32) + 8, 4, 0, one, None)
+    assert rc == 1 and b"2^32" in lib.exact_last_error()
+
+
+def test_device_of_a_call_comes_from_its_tensors():
+    """invoke() launches on the device its tensor arguments live on and refuses mixed devices."""
+    import pytest
+    assert _lib.resolve_device({1}, 0) == 1
+    assert _lib.resolve_device(set(), 3) == 3
+    with pytest.raises(_lib.ExactB200Error, match="different CUDA devices"):
+        _lib.resolve_device({0, 1}, 0)
+
+
+def test_status_word_turns_into_an_exception():
+    import pytest
+    _lib.raise_for_status(0)
+    with pytest.raises(_lib.ExactB200Error, match="exact_rp_quantize_pack"):
+        _lib.raise_for_status(1)
+    with pytest.raises(_lib.ExactB200Error, match="exact_unpack_dequant_rp, exact_linear_forward"):
+        _lib.raise_for_status(6)
+
+
+def test_benchmark_knobs_follow_the_reference_driver():
+    """--n_bits / --kept_frac / --act_fp as mem_speed_bench/arxiv/train_full_batch.py:120-137 maps them."""
+    import argparse
+    import importlib.util
+    import os
+    from exact_b200 import config, graphs
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    ns = lambda **kw: argparse.Namespace(**dict(dict(n_bits=None, kept_frac=None, act_fp=False, no_compress=False), **kw))
+    try:
+        c = bench.apply_knobs(graphs.CONFIGS["cfg3"], ns())
+        assert config.compress_activation and config.activation_compression_bits == [2] and config.kept_frac == 0.125
+        assert c["use_qmodule"] and "int2_kf0.125" in bench.workload_name(c, 5)
+        c = bench.apply_knobs(graphs.CONFIGS["cfg3"], ns(n_bits=4, kept_frac=0.5))
+        assert config.activation_compression_bits == [4] and config.kept_frac == 0.5 and c["use_qmodule"]
+        # fp32 activations with a projection: the quantised modules stay, compression is off, the projection applies
+        c = bench.apply_knobs(graphs.CONFIGS["cfg3"], ns(act_fp=True))
+        assert not config.compress_activation and config.kept_frac == 0.125 and c["use_qmodule"]
+        assert "fp32act_kf0.125" in bench.workload_name(c, 5)
+        # fp32 activations without projection: the unwrapped model
+        c = bench.apply_knobs(graphs.CONFIGS["cfg2"], ns(act_fp=True))
+        assert not config.compress_activation and config.kept_frac == 1.0 and not c["use_qmodule"]
+    finally:
+        config.compress_activation, config.activation_compression_bits, config.kept_frac = True, [2], 1.0

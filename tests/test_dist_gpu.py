@@ -1,0 +1,104 @@
+"""The row-sharded training path on a GPU, checked against the unsharded run.
+
+2 and 8 ranks run as child processes that share the one device of the test box (tests/dist_worker.py:
+backend gloo, collectives staged through the host; no kernel of one rank waits for a kernel of another).
+Compared with the single-process run of the same model, seeds and graph:
+  - the packed stream of the first compressed activation (INT2 codes of x R, k = 13): the concatenation of the
+    shards' streams equals the unsharded stream bit for bit, and so do the bf16 row statistics;
+  - the loss of every step and the first step's parameter gradients: equal up to the fp32 regrouping of the
+    sums over ranks (1e-5 of the largest entry; losses 1e-5 relative at step 0, 1e-4 afterwards);
+  - the compact-row aggregation against the dense one on a single rank: identical losses and gradients, bit
+    for bit (the entries it skips are exact zeros)."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(world, out, name, **kw):
+    port = _free_port()
+    procs = []
+    for r in range(world):
+        cmd = [sys.executable, os.path.join(HERE, "dist_worker.py"), "--world", str(world), "--rank", str(r),
+               "--port", str(port), "--out", str(out), "--name", name]
+        for k, v in kw.items():
+            cmd += [f"--{k}", str(v)]
+        procs.append(subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    logs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=600)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        logs.append(o)
+    for r, p in enumerate(procs):
+        assert p.returncode == 0, f"rank {r} of {world} failed:\n{logs[r][-3000:]}"
+    return [torch.load(os.path.join(out, f"w{world}_{name}_r{r}.pt")) for r in range(world)]
+
+
+@pytest.fixture(scope="module")
+def single(tmp_path_factory):
+    out = tmp_path_factory.mktemp("dist1")
+    return _run(1, out, "compact", compact=1)[0]
+
+
+def test_compact_rows_aggregation_changes_nothing(single, tmp_path):
+    dense = _run(1, tmp_path, "dense", compact=0)[0]
+    # the ReLU + dropout outputs and the masked gradients took the compact route
+    assert single["forms"]["fw256"][0] == "compact" and single["forms"]["bw256"][0] == "compact"
+    assert 0.15 < single["forms"]["fw256"][1] < 0.35
+    assert single["forms"]["fw100"][0] == "dense"
+    assert dense["forms"] == {}
+    assert single["losses"] == dense["losses"]
+    for a, b in zip(single["grads0"], dense["grads0"]):
+        assert torch.equal(a, b)
+    for a, b in zip(single["params"], dense["params"]):
+        assert torch.equal(a, b)
+
+
+def _compare_with_single(parts, single):
+    world = len(parts)
+    assert parts[0]["rows"][0] == 0 and all(parts[i]["rows"][1] == parts[i + 1]["rows"][0] for i in range(world - 1))
+    assert all(p["rows"][0] % 8 == 0 for p in parts)
+    packed = torch.cat([p["packed"] for p in parts])
+    assert torch.equal(packed, single["packed"])            # bit-equal packed stream
+    assert torch.equal(torch.cat([p["scale"] for p in parts]).view(torch.int16), single["scale"].view(torch.int16))
+    assert torch.equal(torch.cat([p["min"] for p in parts]).view(torch.int16), single["min"].view(torch.int16))
+    for p in parts:
+        assert p["losses"] == parts[0]["losses"]
+        assert abs(p["losses"][0] - single["losses"][0]) <= 1e-5 * abs(single["losses"][0])
+        for a, b in zip(p["losses"], single["losses"]):
+            assert abs(a - b) <= 1e-4 * abs(b)
+        for a, b in zip(p["grads0"], single["grads0"]):
+            assert float((a - b).abs().max()) <= 1e-5 * float(b.abs().max()) + 1e-9
+        for a, b in zip(p["params"], parts[0]["params"]):
+            assert torch.equal(a, b)                          # replicas stay in step
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_sharded_run_with_peer_written_compact_rows(world, single, tmp_path):
+    parts = _run(world, tmp_path, "peer", peer=1)
+    assert all(p["peers_used"] for p in parts), "the ranks could not map each other's buffers"
+    assert parts[0]["forms"]["fw256"][0] == "compact" and parts[0]["forms"]["bw256"][0] == "compact"
+    _compare_with_single(parts, single)
+
+
+def test_sharded_run_with_collective_exchange(single, tmp_path):
+    parts = _run(2, tmp_path, "coll", peer=0)
+    assert not any(p["peers_used"] for p in parts)
+    _compare_with_single(parts, single)

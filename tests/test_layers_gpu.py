@@ -120,6 +120,31 @@ def test_sage_projection_small(cfg_name, nodes, fused_rp):
         assert relfro(g, ograds[k]) < (0.15 if fused_rp else 5e-2), k
 
 
+def test_fused_projection_flips_few_codes():
+    """Why the fused-projection bound above is looser: the tensor core truncates x to tf32, the projected values
+    move by about 1e-3 relative, and a value that sits next to a stochastic-rounding boundary then takes the
+    neighbouring INT2 code.  Counted here against the oracle fed the fp32 product and the same noise: a few
+    codes per thousand differ, and never by more than one step."""
+    from exact_b200.cpp_extension import quantization as Q
+    N, D, k, bits = 20000, 256, 32, 2
+    x = normal(N, D, 31)
+    seed, off_r, off_n = 5, 1, 2
+    R = oracle.rademacher(seed, off_r, D, k)
+    packed, sb, mb = Q.rp_quantize_pack(torch.from_numpy(x).cuda(), torch.from_numpy(R).cuda(), bits, seed=seed,
+                                        offset=off_n, row_offset=0)
+    noise = oracle.noise_b200_rows(seed, off_n, N, k)
+    op, _, _, _, _ = oracle.quantize_activation(oracle.input2rp(x, R), noise, bits)
+    got = packed.cpu().numpy().view(np.uint8)[:-1]
+    shifts = np.arange(0, 8, bits, dtype=np.uint8)
+    codes_got = ((got[:, None] >> shifts) & 3).astype(np.int16)
+    codes_ref = ((op[:, None] >> shifts) & 3).astype(np.int16)
+    diff = codes_got != codes_ref
+    frac = diff.mean()
+    print(f"fused projection: {frac:.5f} of the INT2 codes differ from the fp32-product oracle")
+    assert frac < 0.01
+    assert np.abs(codes_got - codes_ref)[diff].max() <= 1 if diff.any() else True
+
+
 def test_grad_weight_in_projected_space_equals_reference_order():
     """(g^T Xq) R^T against the reference's g^T (Xq R^T) (ops.py:164-169): same noise, same R."""
     N, D, O_ = 3000, 256, 64

@@ -126,3 +126,29 @@ def test_regrouped_sum_for_narrow_operands(K, with_values, reduce):
     strict = S._spmm(t(rowptr), t(col), None if val is None else t(val), t(wide), reduce).cpu().numpy()
     flagged = S._spmm(t(rowptr), t(col), None if val is None else t(val), t(wide), reduce, regroup=True).cpu().numpy()
     assert np.array_equal(strict, flagged)
+
+
+@pytest.mark.parametrize("K", [256, 64])
+def test_power_law_graph_with_many_out_of_order_pieces(K):
+    """An R-MAT graph of the benchmark's skew: 120,000 nodes, ~6 M edges, hub rows of 10^4 edges cut into dozens
+    of pieces that are listed (= processed) by the column of their first edge, not in row order (item_slot).
+    Rows up to the threshold are bit-exact against the oracle; hub rows are a regrouped fp32 sum."""
+    from exact_b200 import graphs
+    adj = graphs.rmat(120_000, 3_000_000, 5, "cuda", self_loops=False)
+    adj.to_int32_()
+    rowptr, col, _ = adj.csr()
+    plan = S.long_row_plan(rowptr, 256, col)
+    assert plan is not None and plan["n_items"] > 1000
+    pieces = (plan["long_item_ptr"][1:] - plan["long_item_ptr"][:-1])
+    assert int(pieces.max()) >= 10
+    slot = plan["item_slot"].cpu().numpy()
+    assert not np.array_equal(slot, np.arange(slot.size)) and np.array_equal(np.sort(slot), np.arange(slot.size))
+    mat = normal(120_000, K, 21)
+    rp, cl = rowptr.cpu().numpy().astype(np.int64), col.cpu().numpy().astype(np.int64)
+    long = np.diff(rp) > 256
+    for reduce in ("mean", "sum"):
+        out = S._spmm(rowptr, col, None, t(mat), reduce).cpu().numpy()
+        ref = oracle.spmm(rp, cl, None, mat, reduce)
+        assert np.array_equal(out[~long], ref[~long])
+        err = np.abs(out[long] - ref[long]).max(1)
+        assert np.all(err <= 1e-5 * np.abs(ref[long]).max(1) + 1e-6 * np.sqrt(np.diff(rp)[long]) * (reduce == "sum"))
