@@ -49,9 +49,9 @@ class QuantizationConfig:
         # Dense-layer GEMMs over node rows on the tensor cores with operands split into tf32 head and tail
         # (fp32-equivalent accuracy); False: the library's fp32 GEMM.
         self.linear_tensor_core = True
-        # Aggregation inside the one-node GraphSAGE layer: gather the dense operand as compact rows (kept
-        # columns + values per row) when at most this share of its entries is non-zero, as outputs of
-        # ReLU + dropout and gradients that passed their masks are.  Same sums bit for bit.
+        # Row-sharded aggregation inside the one-node GraphSAGE layer: exchange the dense operand as compact
+        # rows (kept columns + values per row) when at most this share of its entries is non-zero, as outputs
+        # of ReLU + dropout and gradients that passed their masks are.  Same dense rows bit for bit.
         self.compact_operand = True
         self.compact_operand_max_density = 0.5
         # Row shards write their compact rows straight into every peer's buffer (plain stores over NVLink,

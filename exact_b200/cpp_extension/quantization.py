@@ -64,8 +64,12 @@ def quantize_pack(data, bits, noise=None, seed=None, offset=None, row_offset=Non
 
 
 def rp_supported(D, k, dtype=torch.float32):
-    """Shapes the fused projection+pack kernel takes (others use the unfused chain)."""
-    return dtype == torch.float32 and D % 4 == 0 and (k + 15) // 16 * 16 <= 256
+    """Shapes the fused projection+pack kernel takes (others use the unfused chain): fp32 rows of any
+    length (rows that are not 16-byte aligned are copied in by cp.async instead of TMA), k up to 512 as long
+    as three pipeline stages of a [128 x 32] A tile and a [k x 32] sign tile fit in shared memory."""
+    kpad = (k + 15) // 16 * 16
+    stage = 128 * 128 + kpad * 128
+    return dtype == torch.float32 and kpad <= 512 and 200 * 1024 // stage >= (3 if D % 4 else 2)
 
 
 def rp_quantize_pack(data, R, bits, seed=None, offset=None, row_offset=None, want_projection=False):
@@ -79,8 +83,8 @@ def rp_quantize_pack(data, R, bits, seed=None, offset=None, row_offset=None, wan
         raise RuntimeError("R must be [D, k]")
     if bits not in (1, 2, 4, 8):
         raise RuntimeError("bits must be 1, 2, 4 or 8")
-    if not rp_supported(D, k) or data.data_ptr() % 16 != 0:
-        raise _lib.ExactB200Error("rp_quantize_pack: unsupported shape (needs fp32, D % 4 == 0, k <= 256)")
+    if not rp_supported(D, k) or data.data_ptr() % 4 != 0:
+        raise _lib.ExactB200Error("rp_quantize_pack: unsupported shape (needs fp32 and k <= 512)")
     lib = _lib.load()
     ws = torch.empty(int(lib.exact_rp_workspace_bytes(D, k)), dtype=torch.uint8, device=data.device)
     packed = torch.empty(packed_numel(N, k, bits), dtype=torch.int8, device=data.device)

@@ -33,10 +33,10 @@ class CompactRows:
 
 
 class OperandForm:
-    """Remembers, per adjacency and call site, whether the dense operand of an aggregation is worth gathering
+    """Remembers, per adjacency and call site, whether the dense operand of an aggregation is worth exchanging
     as compact rows.  The first call and every `reprobe`-th one measure the share of non-zero entries (one
     host read of a device counter); the calls between reuse the decision, so the steady state has no
-    synchronisation.  Either form gives the same sums bit for bit."""
+    synchronisation.  Either route delivers the same dense rows bit for bit."""
 
     reprobe = 64
 
@@ -92,13 +92,15 @@ def crows_pack(x, rowscale=None, out=None, row0=0, dst_ptrs=None, kept_total=Non
     return out
 
 
-def crows_unpack(cr, n=None, row0=0):
-    """Dense [n, K] fp32 matrix of slots row0 .. row0 + n - 1."""
+def crows_unpack(cr, n=None, row0=0, out=None):
+    """Dense [n, K] fp32 matrix of slots row0 .. row0 + n - 1 (into the first n rows of `out` when given)."""
     n = cr.rows - row0 if n is None else n
-    out = torch.empty((n, cr.K), dtype=torch.float32, device=cr.device)
-    _lib.invoke("exact_crows_unpack", 4 * n * cr.K, cr.ptr(), n, cr.K, row0, _lib.ptr(out), cr.K, _lib.stream_ptr(),
-                device=cr.device)
-    return out
+    if out is None:
+        out = torch.empty((n, cr.K), dtype=torch.float32, device=cr.device)
+    assert out.dtype == torch.float32 and out.size(0) >= n and out.size(1) == cr.K and out.stride(1) == 1
+    _lib.invoke("exact_crows_unpack", 4 * n * cr.K + n * (16 + int(cr.density * cr.K) * 5), cr.ptr(), n, cr.K, row0,
+                _lib.ptr(out), out.stride(0), _lib.stream_ptr(), device=cr.device)
+    return out[:n]
 
 
 def _check(x):

@@ -58,54 +58,39 @@ REGROUP = 0x100   # EXACT_SPMM_REGROUP
 
 
 def _spmm(rowptr, col, value, mat, reduce, regroup=False):
-    """spmm.cc:12-18 -> spmm_cuda.cu:106-170.  `mat` is the dense operand [N, K] or its compact rows
-    (rows.CompactRows; same sums bit for bit).  `regroup`: the caller accepts a regrouped per-row fp32 sum
-    (narrow dense operands then gather two edges per load instruction)."""
-    from .rows import CompactRows
-    compact = isinstance(mat, CompactRows)
-    if not rowptr.is_cuda or not col.is_cuda or not (compact or mat.is_cuda):
+    """spmm.cc:12-18 -> spmm_cuda.cu:106-170.  `regroup`: the caller accepts a regrouped per-row fp32 sum
+    (narrow operands then gather two edges per load instruction)."""
+    if not rowptr.is_cuda or not col.is_cuda or not mat.is_cuda:
         raise RuntimeError("rowptr, col and mat must be CUDA tensors")
     if rowptr.dim() != 1 or col.dim() != 1:
         raise RuntimeError("Input mismatch")
     if value is not None and (value.dim() != 1 or value.size(0) != col.size(0)):
         raise RuntimeError("Input mismatch")
-    if not compact:
-        if mat.dim() != 2:
-            raise RuntimeError("mat must be [N, K] (batched operands are not used by the GCN/SAGE layers)")
-        if mat.dtype != torch.float32:
-            raise RuntimeError("mat must be float32")
-        mat = mat.contiguous()
+    if mat.dim() != 2:
+        raise RuntimeError("mat must be [N, K] (batched operands are not used by the GCN/SAGE layers)")
+    if mat.dtype != torch.float32:
+        raise RuntimeError("mat must be float32")
     if rowptr.dtype != col.dtype or col.dtype not in (torch.int32, torch.int64):
         raise RuntimeError("rowptr and col must both be int32 or both int64")
+    mat = mat.contiguous()
     rowptr = rowptr.contiguous()
     col = col.contiguous()
     if value is not None:
         value = value.detach().to(torch.float32).contiguous()
     M = rowptr.numel() - 1
-    K = mat.K if compact else mat.size(1)
-    n_src = mat.rows if compact else mat.size(0)
-    out = torch.empty((M, K), dtype=torch.float32, device=rowptr.device)
+    K = mat.size(1)
+    out = torch.empty((M, K), dtype=mat.dtype, device=mat.device)
     ib = 4 if col.dtype == torch.int32 else 8
     nnz = col.numel()
     index_bytes = nnz * (ib + (4 if value is not None else 0)) + (M + 1) * ib
-    # bytes that must move at least once: the operand (its compact form when that is what is read), the
-    # indices and the output; and the bytes the gathers request from L2 when no source row is reused
-    row_bytes = (16 + int(mat.density * K) * 5) if compact else K * 4
-    nbytes = n_src * row_bytes + index_bytes + M * K * 4
-    l2_bytes = nnz * row_bytes + index_bytes + M * K * 4
+    # bytes that must cross HBM at least once (operand, indices, output), and the bytes the gathers request
+    # from L2 when no source row is reused (what the reference's kernel moves)
+    nbytes = mat.size(0) * K * 4 + index_bytes + M * K * 4
+    l2_bytes = nnz * K * 4 + index_bytes + M * K * 4
     thr = int(config.spmm_long_row)
     plan = long_row_plan(rowptr, thr, col) if thr > 0 else None
     red = _lib.REDUCE[reduce] | (REGROUP if regroup else 0)
-    if compact:
-        pl = plan or {"item_row": None, "item_begin": None, "item_end": None, "item_slot": None, "n_items": 0,
-                      "long_row": None, "long_item_ptr": None, "n_long": 0}
-        scratch = torch.empty((pl["n_items"], K), dtype=torch.float32, device=out.device) if plan else None
-        _lib.invoke("exact_spmm_crows", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), mat.ptr(), M, K,
-                    _lib.REDUCE[reduce], thr if plan else 0, _lib.ptr(pl["item_row"]), _lib.ptr(pl["item_begin"]),
-                    _lib.ptr(pl["item_end"]), _lib.ptr(pl["item_slot"]), pl["n_items"], _lib.ptr(pl["long_row"]),
-                    _lib.ptr(pl["long_item_ptr"]), pl["n_long"], _lib.ptr(scratch), _lib.ptr(out), _lib.stream_ptr(),
-                    l2_bytes=l2_bytes, edge_columns=nnz * K)
-    elif plan is None:
+    if plan is None:
         _lib.invoke("exact_spmm", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), _lib.ptr(mat), M, K,
                     red, _lib.ptr(out), _lib.stream_ptr(), l2_bytes=l2_bytes, edge_columns=nnz * K)
     else:

@@ -49,22 +49,30 @@ crows_pack_kernel(const float* __restrict__ x, long long n, int K, long long ldx
   for (long long row = (long long)blockIdx.x * kCrowsWarps + warp; row < n; row += (long long)gridDim.x * kCrowsWarps) {
     const float* src = x + row * ldx;
     const float sc = rowscale ? __ldg(rowscale + row) : 1.f;
-    int pos = 0;
-    for (int w = 0; w < W; w++) {
+    // all loads of the row first (K <= 256: at most 8 per lane), then the compaction
+    uint32_t bits[8];
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
       const int c = w * 32 + lane;
-      uint32_t bits = 0u;
+      bits[w] = 0u;
       if (c < K) {
         float v = __ldcs(src + c);
         if (rowscale) v = __fmul_rn(v, sc);
-        bits = __float_as_uint(v);
+        bits[w] = __float_as_uint(v);
       }
-      const uint32_t m = __ballot_sync(0xffffffffu, bits != 0u);
-      if (bits != 0u) {
-        const int q = pos + __popc(m & lt);
-        s_col[q] = (unsigned char)c;
-        s_val[q] = bits;
+    }
+    int pos = 0;
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+      if (w < W) {
+        const uint32_t m = __ballot_sync(0xffffffffu, bits[w] != 0u);
+        if (bits[w] != 0u) {
+          const int q = pos + __popc(m & lt);
+          s_col[q] = (unsigned char)(w * 32 + lane);
+          s_val[q] = bits[w];
+        }
+        pos += __popc(m);
       }
-      pos += __popc(m);
     }
     if (lane == 0) *reinterpret_cast<uint32_t*>(stage) = (uint32_t)pos;
     __syncwarp();
@@ -95,21 +103,40 @@ crows_pack_kernel(const float* __restrict__ x, long long n, int K, long long ldx
   }
 }
 
-// Dense rows back from compact slots (used by tests and by consumers that want the dense matrix).
+// Dense rows back from compact slots.  One warp per row: the row is assembled in shared memory (zeros, then
+// the kept entries at their columns) and written out in full 128-bit pieces.
 __global__ void __launch_bounds__(kCrowsWarps * 32)
 crows_unpack_kernel(const unsigned char* __restrict__ buf, long long n, int K, long long row0, float* __restrict__ out,
                     long long ldo) {
+  __shared__ __align__(16) uint32_t s_row[kCrowsWarps][256];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cols_bytes = crows_cols_bytes(K);
   const long long stride = crows_stride_bytes(K);
+  uint32_t* row_s = s_row[warp];
+  const bool vec4 = (K & 3) == 0 && (ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
   for (long long row = (long long)blockIdx.x * kCrowsWarps + warp; row < n; row += (long long)gridDim.x * kCrowsWarps) {
     const unsigned char* slot = buf + (row0 + row) * stride;
-    const int cnt = (int)*reinterpret_cast<const uint32_t*>(slot);
-    uint32_t* dst = reinterpret_cast<uint32_t*>(out + row * ldo);
-    for (int c = lane; c < K; c += 32) dst[c] = 0u;
-    __syncwarp();
+    int cnt = (int)__ldcs(reinterpret_cast<const uint32_t*>(slot));
+    if (cnt > K) cnt = K;
     const uint32_t* v = reinterpret_cast<const uint32_t*>(slot + 16 + cols_bytes);
-    for (int i = lane; i < cnt && i < K; i += 32) dst[slot[16 + i]] = v[i];
+    // issue the loads of the first 64 entries before touching shared memory
+    uint32_t c0 = 0, c1 = 0, v0 = 0, v1 = 0;
+    if (lane < cnt) { c0 = slot[16 + lane]; v0 = __ldcs(v + lane); }
+    if (lane + 32 < cnt) { c1 = slot[48 + lane]; v1 = __ldcs(v + 32 + lane); }
+    for (int c = lane; c < K; c += 32) row_s[c] = 0u;
+    __syncwarp();
+    if (lane < cnt) row_s[c0] = v0;
+    if (lane + 32 < cnt) row_s[c1] = v1;
+    for (int i = lane + 64; i < cnt; i += 32) row_s[slot[16 + i]] = __ldcs(v + i);
+    __syncwarp();
+    float* dst = out + row * ldo;
+    if (vec4) {
+      for (int c = lane * 4; c < K; c += 128)
+        __stcs(reinterpret_cast<uint4*>(dst + c), *reinterpret_cast<const uint4*>(row_s + c));
+    } else {
+      for (int c = lane; c < K; c += 32) reinterpret_cast<uint32_t*>(dst)[c] = row_s[c];
+    }
+    __syncwarp();
   }
 }
 

@@ -24,10 +24,21 @@
 // truncated to tf32 by the tensor core (10-bit mantissa): the product differs from the fp32 one by
 // about 1e-3 relative, inside the 1e-2 relative-Frobenius criterion of this operator.
 //
+// Rows that are not 16-byte aligned (D % 4 != 0, e.g. the 602 features of the reddit-shaped configuration:
+// 2408-byte rows) cannot be described by a tensor map.  For them the A operand is brought in by four more
+// warps with cp.async (8-byte pieces when rows are 8-byte aligned, else 4-byte), each piece written straight
+// to its place in the 128-byte-swizzled tile, columns past D and rows past N zero-filled; a thread signals a
+// stage after its own copies of that stage have landed (cp.async.wait_group) and a fence.proxy.async has made
+// them visible to the tensor core.  Several stages stay in flight per thread.
+//
+// k up to 512: an accumulator wider than one MMA (N <= 256) is produced by two MMAs per K step, side by
+// side in TMEM; when two such accumulators no longer fit the 512 TMEM columns a single buffer is used.
+//
 // Every wait on an mbarrier is bounded (about one second of SM clock).  When a wait expires the CTA
 // raises an abort flag, all roles leave their loops, outstanding bulk copies are waited for (bounded),
 // TMEM is freed and a non-zero status word is left for the host.
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "exact_b200.h"
@@ -38,6 +49,7 @@ namespace exb {
 constexpr int kRpTileM = 128;       // rows per tile = MMA M
 constexpr int kRpTileK = 32;        // fp32 elements per smem row = 128 bytes = one swizzle atom
 constexpr int kRpThreads = 192;     // 6 warps
+constexpr int kRpAsyncThreads = 320;  // + 4 warps that copy A with cp.async
 constexpr int kRpMaxStages = 10;
 
 struct RpParams {
@@ -45,6 +57,10 @@ struct RpParams {
   uint16_t* scale_bf16;
   uint16_t* min_bf16;
   float* y_out;       // optional [N, k] fp32 copy of the projection (tests)
+  const float* x;     // A operand, read directly by the cp.async producers
+  int piece;          // bytes per cp.async piece (8 or 4)
+  int lag;            // stages a cp.async producer thread keeps in flight before it signals one
+  int nbuf;           // accumulator buffers in TMEM (2, or 1 when 2 * kpad columns do not fit)
   int* status;        // device word: 0 = ok
   int* lib_status;    // library-wide status word of this device (capi.cu), or null
   long long N;
@@ -59,8 +75,27 @@ struct RpParams {
 };
 
 // ---- the kernel -----------------------------------------------------------------------------------
-template <int BITS>
-__global__ void __launch_bounds__(kRpThreads, 4)
+__device__ __forceinline__ void cp_async_piece(uint32_t dst, const void* src, int piece, uint32_t src_bytes) {
+  if (piece == 8)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most n of this thread's most recent cp.async groups are still pending.
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+  }
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <int BITS, bool ASYNC_A>
+__global__ void __launch_bounds__(ASYNC_A ? kRpAsyncThreads : kRpThreads, ASYNC_A ? 1 : 4)
 rp_pack_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_rt,
                const __grid_constant__ RpParams p) {
   constexpr int WPT = 8 / BITS;
@@ -79,7 +114,9 @@ rp_pack_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int s = 0; s < p.stages; s++) {
-      mbar_init(smem_u32(&s_full[s]), 1);
+      // a stage is full when the TMA thread's bytes have landed and, with cp.async producers, each of their
+      // 128 threads has signalled its pieces
+      mbar_init(smem_u32(&s_full[s]), ASYNC_A ? 129 : 1);
       mbar_init(smem_u32(&s_empty[s]), 1);
     }
     for (int b = 0; b < 2; b++) {
@@ -110,9 +147,14 @@ rp_pack_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t full = smem_u32(&s_full[s]);
           const uint32_t dst = tiles_base + (uint32_t)s * p.stage_bytes;
-          mbar_arrive_expect_tx(full, a_bytes + b_bytes);
-          tma_load_2d(dst, &tm_x, kb * kRpTileK, tile * kRpTileM, full);
-          tma_load_2d(dst + a_bytes, &tm_rt, kb * kRpTileK, 0, full);
+          mbar_arrive_expect_tx(full, (ASYNC_A ? 0u : a_bytes) + b_bytes);
+          if (!ASYNC_A) tma_load_2d(dst, &tm_x, kb * kRpTileK, tile * kRpTileM, full);
+          if (p.kpad <= 256) {
+            tma_load_2d(dst + a_bytes, &tm_rt, kb * kRpTileK, 0, full);
+          } else {   // two boxes of kpad / 2 rows (a box holds at most 256)
+            tma_load_2d(dst + a_bytes, &tm_rt, kb * kRpTileK, 0, full);
+            tma_load_2d(dst + a_bytes + b_bytes / 2, &tm_rt, kb * kRpTileK, p.kpad / 2, full);
+          }
         }
       }
       if (!ok) {
@@ -129,12 +171,14 @@ rp_pack_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_tf32(kRpTileM, p.kpad);
+      const int n_lo = p.kpad <= 256 ? p.kpad : 256, n_hi = p.kpad - n_lo;
+      const uint32_t idesc = umma_idesc_tf32(kRpTileM, n_lo);
+      const uint32_t idesc_hi = umma_idesc_tf32(kRpTileM, n_hi > 0 ? n_hi : 16);
       int it = 0, t = 0;
       bool ok = true;
       for (int tile = first; tile < p.num_tiles && ok; tile += step, t++) {
-        const int buf = t & 1;
-        const uint32_t tph = (uint32_t)(t >> 1) & 1u;
+        const int buf = p.nbuf == 2 ? (t & 1) : 0;
+        const uint32_t tph = (uint32_t)(p.nbuf == 2 ? (t >> 1) : t) & 1u;
         if (!mbar_wait(smem_u32(&s_tempty[buf]), tph ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.kpad);
@@ -150,11 +194,53 @@ rp_pack_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           for (int k4 = 0; k4 < kRpTileK / 8; k4++) {
             // advance 8 tf32 = 32 bytes along K inside the swizzle atom: +2 in the (addr >> 4) field
             umma_tf32(d_tmem, a_desc + (uint64_t)(k4 * 2), b_desc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0);
+            // columns 256 .. kpad-1: rows 256.. of the B tile (32 KB further: a whole number of swizzle atoms)
+            if (n_hi > 0)
+              umma_tf32(d_tmem + 256u, a_desc + (uint64_t)(k4 * 2), b_desc + (uint64_t)((256 * 128) >> 4) + (uint64_t)(k4 * 2),
+                        idesc_hi, (kb | k4) != 0);
           }
           umma_commit(smem_u32(&s_empty[s]));  // the stage is free once these MMAs have read it
         }
         if (ok) umma_commit(smem_u32(&s_tfull[buf]));  // the tile's accumulator is complete
       }
+    }
+  } else if (ASYNC_A && warp >= 6) {
+    // ---------------- cp.async producers of A: warps 6..9 ----------------
+    const int t = threadIdx.x - kRpThreads;                 // 0 .. 127
+    const int ppr = 128 / p.piece;                          // pieces per 128-byte tile row: 16 or 32
+    const int pi = t % ppr, rg = t / ppr, rpp = 128 / ppr;  // this thread's piece, row group, rows per pass
+    const int cbytes = pi * p.piece;                        // byte offset of the piece inside a tile row
+    const int chunk = cbytes >> 4, within = cbytes & 15;
+    int it = 0;
+    bool ok = true;
+    for (int tile = first; tile < p.num_tiles && ok; tile += step) {
+      for (int kb = 0; kb < p.kblocks; kb++, it++) {
+        const int s = it % p.stages;
+        const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+        if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
+        const uint32_t dst0 = tiles_base + (uint32_t)s * p.stage_bytes;
+        const int col = kb * kRpTileK + (cbytes >> 2);
+        // a piece is inside the row or outside as a whole: 8-byte pieces are only used for even D
+        const bool col_ok = col < p.D;
+        for (int r = rg; r < kRpTileM; r += rpp) {
+          const long long n = (long long)tile * kRpTileM + r;
+          const bool in = col_ok && n < p.N;
+          const uint32_t dst = dst0 + (uint32_t)(r * 128 + ((chunk ^ (r & 7)) << 4) + within);
+          const float* src = in ? p.x + n * p.D + col : p.x;
+          cp_async_piece(dst, src, p.piece, in ? (uint32_t)p.piece : 0u);   // src size 0: zero fill
+        }
+        cp_async_commit();
+        if (it >= p.lag) {
+          cp_async_wait_pending(p.lag);          // the copies of iteration it - lag have landed
+          fence_proxy_async_smem();
+          mbar_arrive(smem_u32(&s_full[(it - p.lag) % p.stages]));
+        }
+      }
+    }
+    cp_async_wait_pending(0);
+    if (ok) {
+      fence_proxy_async_smem();
+      for (int j = it > p.lag ? it - p.lag : 0; j < it; j++) mbar_arrive(smem_u32(&s_full[j % p.stages]));
     }
   } else {
     // ---------------- epilogue: warps 2..5, thread = row ----------------
@@ -165,8 +251,8 @@ rp_pack_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     int t = 0;
     bool ok = true;
     for (int tile = first; tile < p.num_tiles && ok; tile += step, t++) {
-      const int buf = t & 1;
-      const uint32_t tph = (uint32_t)(t >> 1) & 1u;
+      const int buf = p.nbuf == 2 ? (t & 1) : 0;
+      const uint32_t tph = (uint32_t)(p.nbuf == 2 ? (t >> 1) : t) & 1u;
       if (!mbar_wait(smem_u32(&s_tfull[buf]), tph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * p.kpad);
@@ -358,9 +444,10 @@ int exact_rp_quantize_pack(const float* x, int64_t N, int64_t D, const float* R,
   EXB_REQUIRE(x && R && workspace && packed && scale_bf16 && min_bf16, "rp_quantize_pack: null pointer");
   int kpad, Dpad;
   rp_dims(D, k, &kpad, &Dpad);
-  if (D % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
-    return fail(EXB_ERR_UNSUPPORTED, "rp_quantize_pack: the TMA path needs 16-byte aligned rows (D %% 4 == 0); D = %lld", (long long)D);
-  if (kpad > 256) return fail(EXB_ERR_UNSUPPORTED, "rp_quantize_pack: k = %lld exceeds one MMA tile (256)", (long long)k);
+  if (kpad > 512) return fail(EXB_ERR_UNSUPPORTED, "rp_quantize_pack: k = %lld exceeds the 512 accumulator columns of TMEM", (long long)k);
+  EXB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 3) == 0, "rp_quantize_pack: x must be 4-byte aligned");
+  // rows that a tensor map cannot describe (pitch or base not a multiple of 16 bytes) are copied by cp.async
+  const bool async_a = D % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0;
   EXB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "rp_quantize_pack: workspace must be 256-byte aligned");
   // the epilogue stores 32-bit words of packed bytes when k % 4 == 0
   EXB_REQUIRE(k % 4 != 0 || (reinterpret_cast<uintptr_t>(packed) & 3) == 0, "rp_quantize_pack: packed must be 4-byte aligned when k %% 4 == 0");
@@ -373,28 +460,44 @@ int exact_rp_quantize_pack(const float* x, int64_t N, int64_t D, const float* R,
   EXB_CUDA_OK(cudaGetLastError());
 
   CUtensorMap tm_x, tm_rt;
-  int rc = make_tensor_map_2d_f32(&tm_x, x, (unsigned long long)D, (unsigned long long)N, (unsigned long long)D * 4, kRpTileK, kRpTileM);
-  if (rc) return rc;
-  rc = make_tensor_map_2d_f32(&tm_rt, rt, (unsigned long long)Dpad, (unsigned long long)kpad, (unsigned long long)Dpad * 4, kRpTileK, (unsigned)kpad);
+  int rc;
+  if (!async_a) {
+    rc = make_tensor_map_2d_f32(&tm_x, x, (unsigned long long)D, (unsigned long long)N, (unsigned long long)D * 4, kRpTileK, kRpTileM);
+    if (rc) return rc;
+  } else {
+    memset(&tm_x, 0, sizeof(tm_x));   // not read: the cp.async producers take x itself
+  }
+  rc = make_tensor_map_2d_f32(&tm_rt, rt, (unsigned long long)Dpad, (unsigned long long)kpad, (unsigned long long)Dpad * 4, kRpTileK,
+                              (unsigned)(kpad <= 256 ? kpad : kpad / 2));
   if (rc) return rc;
 
   RpParams p{};
   p.packed = packed; p.scale_bf16 = scale_bf16; p.min_bf16 = min_bf16; p.y_out = y_out; p.status = status; p.lib_status = status_word_ptr();
+  p.x = x;
+  p.piece = (D % 2 == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0) ? 8 : 4;
   p.N = N; p.row_offset = row_offset; p.D = (int)D; p.k = (int)k; p.kpad = kpad; p.bits = bits;
   p.num_tiles = (int)((N + kRpTileM - 1) / kRpTileM);
   p.kblocks = Dpad / kRpTileK;
   p.stage_bytes = (unsigned)(kRpTileM * kRpTileK * 4 + kpad * kRpTileK * 4);
+  p.nbuf = 2 * kpad <= 512 ? 2 : 1;
   unsigned cols = 32;
-  while (cols < (unsigned)(2 * kpad)) cols <<= 1;
+  while (cols < (unsigned)(p.nbuf * kpad)) cols <<= 1;
   p.tmem_cols = cols;
-  // Two CTAs per SM when both fit (TMEM: 512 columns per SM; shared memory: about 200 KB for the rings):
-  // their load / MMA / epilogue phases interleave and hide each other's hand-over gaps.
+  // Up to four CTAs per SM when they fit (TMEM: 512 columns per SM; shared memory: about 200 KB for the rings):
+  // their load / MMA / epilogue phases interleave and hide each other's hand-over gaps.  The cp.async variant
+  // runs one CTA of ten warps per SM with a deep ring.
   int ctas_per_sm = 1;
-  for (int c = 2; c <= 4; c++)
-    if ((unsigned)c * cols <= 512 && (long long)c * 2 * p.stage_bytes + 4096 <= 200 * 1024) ctas_per_sm = c;
+  if (!async_a)
+    for (int c = 2; c <= 4; c++)
+      if ((unsigned)c * cols <= 512 && (long long)c * 2 * p.stage_bytes + 4096 <= 200 * 1024) ctas_per_sm = c;
   int stages = (int)((200 * 1024 / ctas_per_sm) / p.stage_bytes);
   if (stages > kRpMaxStages) stages = kRpMaxStages;
-  if (stages < 2) stages = 2;
+  if (async_a) {
+    if (stages < 3) return fail(EXB_ERR_UNSUPPORTED, "rp_quantize_pack: k = %lld leaves room for fewer than three stages", (long long)k);
+    p.lag = stages - 2 < 4 ? stages - 2 : 4;
+  } else if (stages < 2) {
+    stages = 2;
+  }
   p.stages = stages;
   p.inv_sqrt_k = (float)(1.0 / sqrt((double)k));
   p.off_lo = (uint32_t)offset; p.off_hi = (uint32_t)(offset >> 32);
@@ -404,9 +507,12 @@ int exact_rp_quantize_pack(const float* x, int64_t N, int64_t D, const float* R,
   if (grid > p.num_tiles) grid = p.num_tiles;
 
 #define EXB_RP_LAUNCH(BITS_)                                                                                  \
-  {                                                                                                           \
-    EXB_CUDA_OK(cudaFuncSetAttribute(rp_pack_kernel<BITS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn)); \
-    rp_pack_kernel<BITS_><<<grid, kRpThreads, dyn, st>>>(tm_x, tm_rt, p);                                     \
+  if (async_a) {                                                                                              \
+    EXB_CUDA_OK(cudaFuncSetAttribute(rp_pack_kernel<BITS_, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn)); \
+    rp_pack_kernel<BITS_, true><<<grid, kRpAsyncThreads, dyn, st>>>(tm_x, tm_rt, p);                          \
+  } else {                                                                                                    \
+    EXB_CUDA_OK(cudaFuncSetAttribute(rp_pack_kernel<BITS_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn)); \
+    rp_pack_kernel<BITS_, false><<<grid, kRpThreads, dyn, st>>>(tm_x, tm_rt, p);                              \
   }
   switch (bits) {
     case 1: EXB_RP_LAUNCH(1) break;

@@ -153,11 +153,12 @@ class ShardedSparseTensor:
         return pair[turn & 1]
 
     def exchange(self, x_local, tag, rowscale=None):
-        """Every row of the [local_rows, K] operand (times rowscale[:, None]) in local HBM: rows.CompactRows
-        with one slot per global row when the operand is mostly zeros and the ranks can write each other's
-        memory -- each rank compacts its rows once and stores them into all buffers, an all-reduce of one
-        word orders those stores before anyone's gathers, nothing is expanded -- else a dense [n_global, K]
-        matrix from the collective exchange."""
+        """Every row of the [local_rows, K] operand (times rowscale[:, None]) as a dense [n_global, K] matrix in
+        local HBM.  When the operand is mostly zeros and the ranks can write each other's memory, each rank
+        compacts its rows once and stores them into every rank's buffer (one kernel, plain stores over
+        NVLink: a third of the dense bytes), an all-reduce of one word orders those stores before anyone's
+        reads, and one kernel expands the slots into the dense rows the SpMM gathers: no sizes to agree on, no
+        host synchronisation.  Otherwise the rows go through the collective library."""
         K = x_local.size(1)
         dev = x_local.device
         mode, density = self._operand_form.mode(tag, K, x_local.dtype)
@@ -176,7 +177,9 @@ class ShardedSparseTensor:
                 if self._sync is None:
                     self._sync = torch.zeros(1, dtype=torch.int32, device=dev)
                 all_reduce(self._sync, group=self.group)
-                return ext_rows.CompactRows(None, self.n_global, K, density, address=pb.ptrs[self.rank], device=dev)
+                cr = ext_rows.CompactRows(None, self.n_global, K, density, address=pb.ptrs[self.rank], device=dev)
+                out = self._buffer((tag, K, torch.float32), (self.world * self.shard, K), torch.float32, dev)
+                return ext_rows.crows_unpack(cr, self.n_global, out=out)
         if rowscale is not None:
             x_local = x_local * rowscale.unsqueeze(1)
         return self.gather(x_local.contiguous(), tag, try_compact=(mode == "compact"))

@@ -159,8 +159,8 @@ def run_mask(N, D, p, reps):
 
 def run_spmm(nodes, avg_deg, K, reps, reduce, density=None):
     """Mean / sum aggregation over an R-MAT graph.  `density`: the share of non-zero entries of the dense
-    operand; below 1 the operand is also packed into compact rows and the SpMM that gathers those is timed
-    beside the dense one (same output bit for bit), with the packing pass on its own line."""
+    operand; below 1 the packing of the operand into compact rows and its expansion back (the two kernels
+    around the peer exchange of a row-sharded run) are timed too."""
     from . import graphs
     from .cpp_extension import rows as RW
     dev = torch.device("cuda")
@@ -174,25 +174,25 @@ def run_spmm(nodes, avg_deg, K, reps, reduce, density=None):
     nnz = col.numel()
     peak, kind = _peak()
     out = []
-    forms = [("dense", x)]
-    if density is not None and density < 1.0 and K <= 256 and K % 4 == 0:
+    if density is not None and density < 1.0 and K <= 256:
         cr = RW.crows_pack(x)
         cr.density = density
-        ms_pack = _time(lambda: RW.crows_pack(x, out=cr), reps, None)
-        pack_bytes = nodes * K * 4 + nodes * (16 + int(density * K) * 5)
-        out.append({"op": "crows_pack", "nodes": nodes, "K": K, "density": density, "ms": round(ms_pack, 4),
-                    "GB/s": round(pack_bytes / (ms_pack * 1e-3) / 1e9, 1),
-                    "frac": round(pack_bytes / (ms_pack * 1e-3) / 1e9 / peak, 4), "peak": peak, "peak_kind": kind})
-        forms.append(("compact", cr))
-    for form, operand in forms:
-        ms = _time(lambda: S._spmm(rowptr, col, None, operand, reduce), reps, None)
-        row_bytes = K * 4 if form == "dense" else 16 + int(density * K) * 5
-        must = nodes * row_bytes + nnz * 4 + (nodes + 1) * 4 + nodes * K * 4
-        l2 = nnz * row_bytes + nnz * 4 + (nodes + 1) * 4 + nodes * K * 4
-        out.append({"op": "spmm_" + reduce, "operand": form, "nodes": nodes, "nnz": nnz, "K": K, "density": density,
-                    "ms": round(ms, 4), "GB/s": round(must / (ms * 1e-3) / 1e9, 1),
-                    "frac": round(must / (ms * 1e-3) / 1e9 / peak, 4), "l2_side_GB/s": round(l2 / (ms * 1e-3) / 1e9, 1),
-                    "peak": peak, "peak_kind": kind})
+        dense = torch.empty_like(x)
+        compact_bytes = nodes * (16 + int(density * K) * 5)
+        for name, call in (("crows_pack", lambda: RW.crows_pack(x, out=cr)),
+                           ("crows_unpack", lambda: RW.crows_unpack(cr, nodes, out=dense))):
+            ms = _time(call, reps, None)
+            nb = nodes * K * 4 + compact_bytes
+            out.append({"op": name, "nodes": nodes, "K": K, "density": density, "ms": round(ms, 4),
+                        "GB/s": round(nb / (ms * 1e-3) / 1e9, 1), "frac": round(nb / (ms * 1e-3) / 1e9 / peak, 4),
+                        "peak": peak, "peak_kind": kind})
+    ms = _time(lambda: S._spmm(rowptr, col, None, x, reduce), reps, None)
+    must = nodes * K * 4 + nnz * 4 + (nodes + 1) * 4 + nodes * K * 4
+    l2 = nnz * K * 4 + nnz * 4 + (nodes + 1) * 4 + nodes * K * 4
+    out.append({"op": "spmm_" + reduce, "nodes": nodes, "nnz": nnz, "K": K, "density": density,
+                "ms": round(ms, 4), "GB/s": round(must / (ms * 1e-3) / 1e9, 1),
+                "frac": round(must / (ms * 1e-3) / 1e9 / peak, 4), "l2_side_GB/s": round(l2 / (ms * 1e-3) / 1e9, 1),
+                "peak": peak, "peak_kind": kind})
     return out
 
 
@@ -210,7 +210,7 @@ def main():
     ap.add_argument("--avg-deg", type=float, default=50.0)
     ap.add_argument("--K", type=int, nargs="*", default=[256])
     ap.add_argument("--density", type=float, default=None,
-                    help="--op spmm: share of non-zero operand entries; below 1 the compact-rows SpMM is timed too")
+                    help="--op spmm: share of non-zero operand entries; below 1 the compact-rows pack / unpack are timed too")
     ap.add_argument("--max-bytes", type=float, default=12e9, help="skip cases whose input exceeds this")
     a = ap.parse_args()
     _lib.load()

@@ -140,7 +140,7 @@ def project_and_quantize(input, scheme, rp=True):
     if config.kept_frac < 1.0 and rp:
         kept_acts = int(config.kept_frac * input.shape[1] + 0.999)
         if (config.fused_rp and config.compress_activation and not config.simulate and not config.swap
-                and input.dim() == 2 and input.is_contiguous() and input.data_ptr() % 16 == 0
+                and input.dim() == 2 and input.is_contiguous()
                 and ext_quantization.rp_supported(input.shape[1], kept_acts, input.dtype)):
             # one kernel: projection GEMM (tcgen05) with the statistics + quantise + pack in its epilogue
             with torch.no_grad():

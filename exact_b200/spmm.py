@@ -6,7 +6,6 @@ from torch.autograd.function import Function
 
 from .conf import config
 from .cpp_extension import backward_func as ext_backward_func
-from .cpp_extension import rows as ext_rows
 from .cpp_extension import spmm as ext_spmm
 from .ops import linear_backward_from_compressed, project_and_quantize, qspmm_mean, qspmm_sum
 from .qscheme import QScheme
@@ -62,31 +61,12 @@ class QMatmul(torch.nn.Module):
         return qmatmul(src, other, self.reduce, quantized, randmat, self.scheme)
 
 
-def _form_of(obj):
-    form = getattr(obj, "_operand_form", None)
-    if form is None:
-        form = obj._operand_form = ext_rows.OperandForm()
-    return form
-
-
 def _operand(src, x, tag, rowscale=None):
     """The dense operand x (times rowscale[:, None]) of an aggregation over `src`, with every row the local
-    adjacency rows reference in local HBM: a dense matrix or rows.CompactRows."""
+    adjacency rows reference in local HBM."""
     from .dist import ShardedSparseTensor
     if isinstance(src, ShardedSparseTensor):
         return src.exchange(x, tag, rowscale)
-    form = _form_of(src.storage)
-    mode, density = form.mode(tag, x.size(1), x.dtype)
-    if mode != "dense":
-        x = x.contiguous()
-        kept = torch.zeros(1, dtype=torch.int64, device=x.device) if mode == "probe" else None
-        cr = ext_rows.crows_pack(x, rowscale, kept_total=kept)
-        if mode == "probe":
-            density = float(kept.item()) / max(x.numel(), 1)
-            mode = form.decide(tag, density)
-        if mode == "compact":
-            cr.density = density
-            return cr
     return x if rowscale is None else x * rowscale.unsqueeze(1)
 
 

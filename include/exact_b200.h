@@ -162,13 +162,13 @@ EXACT_API int exact_spmm_split(const void* rowptr, const void* col, int idx_byte
                                const int32_t* long_item_ptr, int64_t n_long, float* scratch, float* out,
                                void* stream);
 
-/* Compact rows: a dense operand whose entries are mostly exact zeros, in the form the SpMM gathers it and
- * row shards exchange it between GPUs.  No counterpart in the reference (it is single-GPU and gathers dense
+/* Compact rows: a dense operand whose entries are mostly exact zeros, in the form row shards write it into
+ * each other's memory before an aggregation.  No counterpart in the reference (it is single-GPU and gathers dense
  * rows, spmm_cuda.cu:86-93).  Row r of x [n, K] fp32 (0 < K <= 256, row pitch ldx) goes to a slot of
  * exact_crows_slot_bytes(K) = 16 + pad16(K) + 4 K bytes at slot index row0 + r of each destination buffer:
  *   +0  uint32 cnt;   +16  uint8 col[cnt] (ascending);   +16 + pad16(K)  fp32 val[cnt].
- * An entry is kept when any of its 32 bits is set (only +0.0 is dropped: an fp32 sum that starts at +0.0 is
- * not changed by adding +0.0, so sums over compact rows equal sums over the dense rows bit for bit).
+ * An entry is kept when any of its 32 bits is set: only +0.0 is dropped, so unpack(pack(x)) == x bit for bit
+ * (-0.0, NaN, inf and denormals included).
  *   rowscale   [n] fp32 or NULL: row r is multiplied by rowscale[r] first (the 1/deg scaling of the
  *              transposed mean, spmm.cc:128-133, folded into this pass)
  *   dst        host array of n_dst (1..8) device pointers, 16-byte aligned, each with room for every slot
@@ -197,17 +197,6 @@ EXACT_API int exact_peer_free(void* ptr);
 EXACT_API int exact_peer_export(const void* ptr, void* handle64);
 EXACT_API int exact_peer_import(const void* handle64, void** ptr);
 EXACT_API int exact_peer_close(void* ptr);
-
-/* exact_spmm / exact_spmm_split with the dense operand given as compact rows: `crows` holds one slot per
- * operand row (slot index = column index of the adjacency), K <= 256, K % 4 == 0.  Same sums, same order
- * (spmm_cuda.cu:86-93 for rows up to the threshold), bit-identical to the dense call on the matrix the
- * slots were packed from.  n_items = 0 with long_threshold = 0: no long-row pieces (every row by one warp). */
-EXACT_API int exact_spmm_crows(const void* rowptr, const void* col, int idx_bytes, const float* value,
-                               const void* crows, int64_t M, int64_t K, int reduce, int64_t long_threshold,
-                               const int32_t* item_row, const int64_t* item_begin, const int64_t* item_end,
-                               const int32_t* item_slot, int64_t n_items, const int32_t* long_row,
-                               const int32_t* long_item_ptr, int64_t n_long, float* scratch, float* out,
-                               void* stream);
 
 /* exact_spmm_split without the scratch argument (no counterpart in the reference).  Meant for hosts
  * that must not allocate device memory around the call -- a serving loop with a frozen memory plan, a

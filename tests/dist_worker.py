@@ -92,8 +92,7 @@ def main():
     from exact_b200 import check_status
     check_status(force=True)
     forms = {}
-    holder = adj if a.world > 1 else adj.storage
-    form = getattr(holder, "_operand_form", None)
+    form = getattr(adj, "_operand_form", None) if a.world > 1 else None
     if form is not None:
         forms = {k: (v[0], v[2]) for k, v in form.state.items()}
     peers_used = bool(getattr(adj, "_peers", None))

@@ -120,9 +120,6 @@ def test_argument_checks_added_later_reject_before_any_launch():
     assert rc == 1 and b"256" in lib.exact_last_error()
     rc = lib.exact_crows_pack(one, 4, 64, 64, None, 0, dst, 9, None, None)
     assert rc == 1
-    rc = lib.exact_spmm_crows(one, one, 4, None, one, 8, 258, 0, 0, None, None, None, None, 0, None, None, 0, None, one,
-                              None)
-    assert rc == 1 and b"multiple of 4" in lib.exact_last_error()
     rc = lib.exact_spmm(one, one, 4, None, one, (1 << 32) + 8, 4, 0, one, None)
     assert rc == 1 and b"2^32" in lib.exact_last_error()
 

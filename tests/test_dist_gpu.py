@@ -6,9 +6,9 @@ Compared with the single-process run of the same model, seeds and graph:
   - the packed stream of the first compressed activation (INT2 codes of x R, k = 13): the concatenation of the
     shards' streams equals the unsharded stream bit for bit, and so do the bf16 row statistics;
   - the loss of every step and the first step's parameter gradients: equal up to the fp32 regrouping of the
-    sums over ranks (1e-5 of the largest entry; losses 1e-5 relative at step 0, 1e-4 afterwards);
-  - the compact-row aggregation against the dense one on a single rank: identical losses and gradients, bit
-    for bit (the entries it skips are exact zeros)."""
+    sums over ranks (gradients 2e-5 relative Frobenius and 2e-4 of the largest entry -- sums of ~10^3
+    cancelling terms regrouped 8 ways; losses 1e-5 relative at step 0, 1e-4 afterwards);
+  - the peer-written compact rows against the collective exchange: same numbers."""
 import os
 import socket
 import subprocess
@@ -54,21 +54,7 @@ def _run(world, out, name, **kw):
 @pytest.fixture(scope="module")
 def single(tmp_path_factory):
     out = tmp_path_factory.mktemp("dist1")
-    return _run(1, out, "compact", compact=1)[0]
-
-
-def test_compact_rows_aggregation_changes_nothing(single, tmp_path):
-    dense = _run(1, tmp_path, "dense", compact=0)[0]
-    # the ReLU + dropout outputs and the masked gradients took the compact route
-    assert single["forms"]["fw256"][0] == "compact" and single["forms"]["bw256"][0] == "compact"
-    assert 0.15 < single["forms"]["fw256"][1] < 0.35
-    assert single["forms"]["fw100"][0] == "dense"
-    assert dense["forms"] == {}
-    assert single["losses"] == dense["losses"]
-    for a, b in zip(single["grads0"], dense["grads0"]):
-        assert torch.equal(a, b)
-    for a, b in zip(single["params"], dense["params"]):
-        assert torch.equal(a, b)
+    return _run(1, out, "single")[0]
 
 
 def _compare_with_single(parts, single):
@@ -85,7 +71,8 @@ def _compare_with_single(parts, single):
         for a, b in zip(p["losses"], single["losses"]):
             assert abs(a - b) <= 1e-4 * abs(b)
         for a, b in zip(p["grads0"], single["grads0"]):
-            assert float((a - b).abs().max()) <= 1e-5 * float(b.abs().max()) + 1e-9
+            assert float((a - b).norm()) <= 2e-5 * float(b.norm()) + 1e-12
+            assert float((a - b).abs().max()) <= 2e-4 * float(b.abs().max()) + 1e-9
         for a, b in zip(p["params"], parts[0]["params"]):
             assert torch.equal(a, b)                          # replicas stay in step
 

@@ -20,6 +20,10 @@ CASES = [
     (256, 128, 32, 2), (128, 32, 16, 2), (1000, 256, 32, 2), (1000, 100, 13, 2), (777, 256, 76, 2),
     (4096, 128, 64, 1), (4096, 128, 16, 4), (513, 64, 8, 8), (300, 512, 128, 2), (50000, 256, 32, 2),
     (130, 1024, 256, 2), (9, 36, 5, 2),
+    # rows that are not 16-byte aligned (cp.async producers): the reddit-shaped 602 features, odd D (4-byte pieces)
+    (64, 602, 76, 2), (5000, 602, 76, 2), (1000, 602, 76, 4), (333, 37, 5, 2), (2000, 101, 13, 8), (129, 602, 76, 1),
+    # k beyond one MMA: two MMAs per K step, one accumulator buffer
+    (700, 602, 301, 2), (1000, 1024, 512, 2), (300, 640, 320, 4),
 ]
 
 
@@ -53,11 +57,29 @@ def test_fused_projection_pack(N, D, k, bits):
 
 
 def test_unsupported_shapes_are_refused():
-    x = torch.randn(64, 602, device="cuda")          # 2408-byte rows: not a legal TMA pitch
-    R = torch.randn(602, 76, device="cuda")
+    x = torch.randn(64, 1200, device="cuda")
+    R = torch.randn(1200, 600, device="cuda")         # more accumulator columns than TMEM has
     with pytest.raises(RuntimeError):
         Q.rp_quantize_pack(x, R, 2)
-    assert not Q.rp_supported(602, 76) and not Q.rp_supported(602, 301) and Q.rp_supported(256, 32)
+    assert not Q.rp_supported(1200, 600)
+    assert Q.rp_supported(602, 76) and Q.rp_supported(602, 301) and Q.rp_supported(256, 32) and Q.rp_supported(37, 5)
+
+
+def test_rows_of_a_view_that_is_not_16_byte_aligned():
+    """A [N, 128] matrix that starts 8 bytes into its storage takes the cp.async route and gives the bytes of
+    the aligned call."""
+    N, D, k, bits = 3000, 128, 16, 2
+    x = normal(N, D, 7)
+    R = torch.from_numpy(oracle.rademacher(3, 0, D, k)).cuda()
+    base = torch.zeros(N * D + 2, device="cuda")
+    view = base[2:].view(N, D)
+    view.copy_(torch.from_numpy(x))
+    assert view.data_ptr() % 16 == 8
+    a = Q.rp_quantize_pack(torch.from_numpy(x).cuda(), R, bits, seed=1, offset=2, row_offset=0)
+    b = Q.rp_quantize_pack(view, R, bits, seed=1, offset=2, row_offset=0)
+    assert torch.equal(a[0][:-1], b[0][:-1])          # the last byte is allocated and never written
+    assert torch.equal(a[1].view(torch.int16), b[1].view(torch.int16))
+    assert torch.equal(a[2].view(torch.int16), b[2].view(torch.int16))
 
 
 BWD_CASES = [(256, 128, 32, 2), (1000, 256, 32, 2), (1000, 100, 13, 2), (4096, 128, 16, 4), (513, 64, 8, 8),

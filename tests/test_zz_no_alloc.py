@@ -40,7 +40,7 @@ def _call(name, rowptr, col, val, mat, reduce, thr, plan, scratch, out):
             plan["n_long"]]
     if scratch is not None:
         args.append(_lib.ptr(scratch))
-    args += [_lib.ptr(out), _lib.stream_ptr()]
+    args += [_lib.ptr(out), torch.cuda.current_stream().cuda_stream]
     return getattr(lib, name)(*args)
 
 
