@@ -9,12 +9,13 @@ from .sparse import SparseTensor, gcn_norm
 from .ops import (dequantize_activation, input2rp, qbatch_norm, qlinear, qspmm_mean, qspmm_sum,
                   quantize_activation, rp2input)
 from .spmm import QMatmul, qmatmul
-from .layers import (GCNConv, QBatchNorm1d, QDropout, QDropout2, QGCNConv, QLinear, QReLU, QSAGEConv, SAGEConv)
+from .layers import (GCNConv, QBatchNorm1d, QDropout, QDropout2, QGCNConv, QLeakyReLU, QLinear, QReLU, QSAGEConv,
+                     SAGEConv)
 from .module import QModule
 from ._lib import ExactB200Error, check_status, poll_status
 
 __all__ = [
-    "config", "QModule", "QGCNConv", "QSAGEConv", "QLinear", "QReLU", "QDropout", "QDropout2", "QBatchNorm1d",
+    "config", "QModule", "QGCNConv", "QSAGEConv", "QLinear", "QReLU", "QLeakyReLU", "QDropout", "QDropout2", "QBatchNorm1d",
     "QMatmul", "qmatmul", "GCNConv", "SAGEConv", "SparseTensor", "gcn_norm", "quantize_activation",
     "dequantize_activation", "input2rp", "rp2input", "qlinear", "qbatch_norm", "qspmm_sum", "qspmm_mean",
     "ExactB200Error", "check_status", "poll_status", "get_memory_usage", "compute_tensor_bytes", "exp_recorder", "cast_adj", "cast_low_bit_int",

@@ -34,6 +34,8 @@ SIGNATURES = {
     "exact_mask_words": (c_i64, [c_i64]),
     "exact_act_quantized_relu_forward": (c_int, [c_ptr, c_i64, c_ptr, c_ptr, c_ptr]),
     "exact_act_quantized_relu_backward": (c_int, [c_ptr, c_ptr, c_i64, c_ptr, c_ptr]),
+    "exact_act_quantized_leaky_relu_forward": (c_int, [c_ptr, c_i64, c_f32, c_ptr, c_ptr, c_ptr]),
+    "exact_act_quantized_leaky_relu_backward": (c_int, [c_ptr, c_ptr, c_i64, c_f32, c_ptr, c_ptr]),
     "exact_act_quantized_dropout_forward": (c_int, [c_ptr, c_i64, c_f32, c_ptr, c_u64, c_u64, c_i64, c_ptr, c_ptr,
                                                     c_ptr]),
     "exact_act_quantized_dropout_backward": (c_int, [c_ptr, c_ptr, c_i64, c_f32, c_ptr, c_ptr]),

@@ -296,6 +296,33 @@ def act_quantized_relu_dropout(input, p, train, uniforms=None):
     return _ActQuantizedReLUDropout.apply(input.contiguous(), float(p), uniforms)
 
 
+class _ActQuantizedLeakyReLU(torch.autograd.Function):
+    """quantization.cc:87-107."""
+
+    @staticmethod
+    def forward(ctx, input, slope):
+        lib = _lib.load()
+        n = input.numel()
+        out = torch.empty_like(input)
+        mask = torch.empty(int(lib.exact_mask_words(n)), dtype=torch.int32, device=input.device)
+        _lib.invoke("exact_act_quantized_leaky_relu_forward", 8 * n + n // 8, _lib.ptr(input), n, slope, _lib.ptr(out),
+                    _lib.ptr(mask), _lib.stream_ptr())
+        ctx.save_for_backward(mask)
+        ctx.slope = slope
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (mask,) = ctx.saved_tensors
+        grad_output = grad_output.contiguous()
+        gin = torch.empty_like(grad_output)
+        n = grad_output.numel()
+        _lib.invoke("exact_act_quantized_leaky_relu_backward", 8 * n + n // 8, _lib.ptr(grad_output), _lib.ptr(mask), n,
+                    ctx.slope, _lib.ptr(gin), _lib.stream_ptr())
+        return gin, None
+
+
 def act_quantized_leaky_relu(input, slope):
-    raise NotImplementedError("act_quantized_leaky_relu serves only the GAT layers, which are outside the "
-                              "GCN/GraphSAGE path this library accelerates")
+    """quantization.cc:104-107."""
+    _check_cuda_float(input, "input")
+    return _ActQuantizedLeakyReLU.apply(input.contiguous(), float(slope))

@@ -30,9 +30,12 @@ struct CrowsDst {
   int n;
 };
 
-// One warp per row.  The row is compacted into a staging slot in shared memory (ballot + popcount give
-// every kept entry its place) and the used prefix of the slot is then copied to each destination with
-// 16-byte stores: whole sectors, which is what crosses NVLink well.
+// One warp per row, two rows per step so that twice the loads are in flight.  A row is compacted into a
+// staging slot in shared memory (ballot + popcount give every kept entry its place) and the used prefix of
+// the slot is then copied to each destination with 16-byte stores: whole sectors, which is what crosses
+// NVLink well.
+constexpr int kCrowsRows = 2;   // rows per warp and step
+
 __global__ void __launch_bounds__(kCrowsWarps * 32)
 crows_pack_kernel(const float* __restrict__ x, long long n, int K, long long ldx, const float* __restrict__ rowscale,
                   long long row0, const __grid_constant__ CrowsDst dst, unsigned long long* __restrict__ kept_total) {
@@ -41,52 +44,62 @@ crows_pack_kernel(const float* __restrict__ x, long long n, int K, long long ldx
   const int W = (K + 31) >> 5;
   const int cols_bytes = crows_cols_bytes(K);
   const long long stride = crows_stride_bytes(K);
-  unsigned char* stage = s_stage + (size_t)warp * stride;
-  unsigned char* s_col = stage + 16;
-  uint32_t* s_val = reinterpret_cast<uint32_t*>(stage + 16 + cols_bytes);
   const uint32_t lt = (1u << lane) - 1u;
   unsigned long long kept = 0;
-  for (long long row = (long long)blockIdx.x * kCrowsWarps + warp; row < n; row += (long long)gridDim.x * kCrowsWarps) {
-    const float* src = x + row * ldx;
-    const float sc = rowscale ? __ldg(rowscale + row) : 1.f;
-    // all loads of the row first (K <= 256: at most 8 per lane), then the compaction
-    uint32_t bits[8];
+  const long long step = (long long)gridDim.x * kCrowsWarps * kCrowsRows;
+  for (long long base = ((long long)blockIdx.x * kCrowsWarps + warp) * kCrowsRows; base < n; base += step) {
+    // all loads of the rows first (K <= 256: at most 8 per lane and row), then the compaction
+    uint32_t bits[kCrowsRows][8];
 #pragma unroll
-    for (int w = 0; w < 8; w++) {
-      const int c = w * 32 + lane;
-      bits[w] = 0u;
-      if (c < K) {
-        float v = __ldcs(src + c);
-        if (rowscale) v = __fmul_rn(v, sc);
-        bits[w] = __float_as_uint(v);
+    for (int r = 0; r < kCrowsRows; r++) {
+      const long long row = base + r;
+      const float* src = x + row * ldx;
+#pragma unroll
+      for (int w = 0; w < 8; w++) {
+        const int c = w * 32 + lane;
+        bits[r][w] = 0u;
+        if (row < n && c < K) bits[r][w] = __float_as_uint(__ldcs(src + c));
       }
     }
-    int pos = 0;
 #pragma unroll
-    for (int w = 0; w < 8; w++) {
-      if (w < W) {
-        const uint32_t m = __ballot_sync(0xffffffffu, bits[w] != 0u);
-        if (bits[w] != 0u) {
-          const int q = pos + __popc(m & lt);
-          s_col[q] = (unsigned char)(w * 32 + lane);
-          s_val[q] = bits[w];
+    for (int r = 0; r < kCrowsRows; r++) {
+      const long long row = base + r;
+      if (row >= n) break;
+      unsigned char* stage = s_stage + (size_t)(warp * kCrowsRows + r) * stride;
+      unsigned char* s_col = stage + 16;
+      uint32_t* s_val = reinterpret_cast<uint32_t*>(stage + 16 + cols_bytes);
+      if (rowscale) {
+        const float sc = __ldg(rowscale + row);
+#pragma unroll
+        for (int w = 0; w < 8; w++) bits[r][w] = __float_as_uint(__fmul_rn(__uint_as_float(bits[r][w]), sc));
+      }
+      int pos = 0;
+#pragma unroll
+      for (int w = 0; w < 8; w++) {
+        if (w < W) {
+          const uint32_t m = __ballot_sync(0xffffffffu, bits[r][w] != 0u);
+          if (bits[r][w] != 0u) {
+            const int q = pos + __popc(m & lt);
+            s_col[q] = (unsigned char)(w * 32 + lane);
+            s_val[q] = bits[r][w];
+          }
+          pos += __popc(m);
         }
-        pos += __popc(m);
       }
-    }
-    if (lane == 0) *reinterpret_cast<uint32_t*>(stage) = (uint32_t)pos;
-    __syncwarp();
-    kept += (unsigned long long)pos;
-    const int head16 = (16 + pos + 15) >> 4;     // header + columns, in 16-byte units
-    const int val16 = (pos + 3) >> 2;            // values, in 16-byte units
-    const uint4* sh = reinterpret_cast<const uint4*>(stage);
-    const uint4* sv = reinterpret_cast<const uint4*>(stage + 16 + cols_bytes);
-    for (int d = 0; d < dst.n; d++) {
-      unsigned char* slot = dst.p[d] + (row0 + row) * stride;
-      uint4* gh = reinterpret_cast<uint4*>(slot);
-      uint4* gv = reinterpret_cast<uint4*>(slot + 16 + cols_bytes);
-      for (int i = lane; i < head16; i += 32) gh[i] = sh[i];
-      for (int i = lane; i < val16; i += 32) gv[i] = sv[i];
+      if (lane == 0) *reinterpret_cast<uint32_t*>(stage) = (uint32_t)pos;
+      __syncwarp();
+      kept += (unsigned long long)pos;
+      const int head16 = (16 + pos + 15) >> 4;     // header + columns, in 16-byte units
+      const int val16 = (pos + 3) >> 2;            // values, in 16-byte units
+      const uint4* sh = reinterpret_cast<const uint4*>(stage);
+      const uint4* sv = reinterpret_cast<const uint4*>(stage + 16 + cols_bytes);
+      for (int d = 0; d < dst.n; d++) {
+        unsigned char* slot = dst.p[d] + (row0 + row) * stride;
+        uint4* gh = reinterpret_cast<uint4*>(slot);
+        uint4* gv = reinterpret_cast<uint4*>(slot + 16 + cols_bytes);
+        for (int i = lane; i < head16; i += 32) gh[i] = sh[i];
+        for (int i = lane; i < val16; i += 32) gv[i] = sv[i];
+      }
     }
     __syncwarp();
   }
@@ -103,38 +116,57 @@ crows_pack_kernel(const float* __restrict__ x, long long n, int K, long long ldx
   }
 }
 
-// Dense rows back from compact slots.  One warp per row: the row is assembled in shared memory (zeros, then
-// the kept entries at their columns) and written out in full 128-bit pieces.
+// Dense rows back from compact slots.  One warp per row, two rows per step: the count and the first 64
+// entries of each row are requested together (a row of 256 columns at 25 % density has about 64), the row is
+// assembled in shared memory (zeros, then the kept entries at their columns) and written out in full 128-bit
+// pieces.
 __global__ void __launch_bounds__(kCrowsWarps * 32)
 crows_unpack_kernel(const unsigned char* __restrict__ buf, long long n, int K, long long row0, float* __restrict__ out,
                     long long ldo) {
-  __shared__ __align__(16) uint32_t s_row[kCrowsWarps][256];
+  __shared__ __align__(16) uint32_t s_row[kCrowsWarps][kCrowsRows][256];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cols_bytes = crows_cols_bytes(K);
   const long long stride = crows_stride_bytes(K);
-  uint32_t* row_s = s_row[warp];
   const bool vec4 = (K & 3) == 0 && (ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-  for (long long row = (long long)blockIdx.x * kCrowsWarps + warp; row < n; row += (long long)gridDim.x * kCrowsWarps) {
-    const unsigned char* slot = buf + (row0 + row) * stride;
-    int cnt = (int)__ldcs(reinterpret_cast<const uint32_t*>(slot));
-    if (cnt > K) cnt = K;
-    const uint32_t* v = reinterpret_cast<const uint32_t*>(slot + 16 + cols_bytes);
-    // issue the loads of the first 64 entries before touching shared memory
-    uint32_t c0 = 0, c1 = 0, v0 = 0, v1 = 0;
-    if (lane < cnt) { c0 = slot[16 + lane]; v0 = __ldcs(v + lane); }
-    if (lane + 32 < cnt) { c1 = slot[48 + lane]; v1 = __ldcs(v + 32 + lane); }
-    for (int c = lane; c < K; c += 32) row_s[c] = 0u;
-    __syncwarp();
-    if (lane < cnt) row_s[c0] = v0;
-    if (lane + 32 < cnt) row_s[c1] = v1;
-    for (int i = lane + 64; i < cnt; i += 32) row_s[slot[16 + i]] = __ldcs(v + i);
-    __syncwarp();
-    float* dst = out + row * ldo;
-    if (vec4) {
-      for (int c = lane * 4; c < K; c += 128)
-        __stcs(reinterpret_cast<uint4*>(dst + c), *reinterpret_cast<const uint4*>(row_s + c));
-    } else {
-      for (int c = lane; c < K; c += 32) reinterpret_cast<uint32_t*>(dst)[c] = row_s[c];
+  const bool in0 = lane < K, in1 = lane + 32 < K;
+  const long long step = (long long)gridDim.x * kCrowsWarps * kCrowsRows;
+  for (long long base = ((long long)blockIdx.x * kCrowsWarps + warp) * kCrowsRows; base < n; base += step) {
+    int cnt[kCrowsRows];
+    uint32_t c0[kCrowsRows], c1[kCrowsRows], v0[kCrowsRows], v1[kCrowsRows];
+#pragma unroll
+    for (int r = 0; r < kCrowsRows; r++) {
+      cnt[r] = 0; c0[r] = c1[r] = v0[r] = v1[r] = 0u;
+      if (base + r < n) {
+        // the entries are requested before the count is known: they lie inside the slot whatever the count is
+        const unsigned char* slot = buf + (row0 + base + r) * stride;
+        const uint32_t* v = reinterpret_cast<const uint32_t*>(slot + 16 + cols_bytes);
+        cnt[r] = (int)__ldcs(reinterpret_cast<const uint32_t*>(slot));
+        if (in0) { c0[r] = slot[16 + lane]; v0[r] = __ldcs(v + lane); }
+        if (in1) { c1[r] = slot[48 + lane]; v1[r] = __ldcs(v + 32 + lane); }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kCrowsRows; r++) {
+      if (base + r >= n) break;
+      uint32_t* row_s = s_row[warp][r];
+      const int m = cnt[r] < K ? cnt[r] : K;
+      for (int c = lane; c < K; c += 32) row_s[c] = 0u;
+      __syncwarp();
+      if (lane < m) row_s[c0[r]] = v0[r];
+      if (lane + 32 < m) row_s[c1[r]] = v1[r];
+      if (m > 64) {
+        const unsigned char* slot = buf + (row0 + base + r) * stride;
+        const uint32_t* v = reinterpret_cast<const uint32_t*>(slot + 16 + cols_bytes);
+        for (int i = lane + 64; i < m; i += 32) row_s[slot[16 + i]] = __ldcs(v + i);
+      }
+      __syncwarp();
+      float* dst = out + (base + r) * ldo;
+      if (vec4) {
+        for (int c = lane * 4; c < K; c += 128)
+          __stcs(reinterpret_cast<uint4*>(dst + c), *reinterpret_cast<const uint4*>(row_s + c));
+      } else {
+        for (int c = lane; c < K; c += 32) reinterpret_cast<uint32_t*>(dst)[c] = row_s[c];
+      }
     }
     __syncwarp();
   }
@@ -165,8 +197,8 @@ int exact_crows_pack(const float* x, int64_t n, int64_t K, int64_t ldx, const fl
                 "crows_pack: destination %d is null or not 16-byte aligned", i);
     d.p[i] = static_cast<unsigned char*>(dst[i]);
   }
-  const size_t smem = (size_t)kCrowsWarps * (size_t)crows_stride_bytes((int)K);
-  long long g = (n + kCrowsWarps - 1) / kCrowsWarps;
+  const size_t smem = (size_t)kCrowsWarps * kCrowsRows * (size_t)crows_stride_bytes((int)K);
+  long long g = (n + kCrowsWarps * kCrowsRows - 1) / (kCrowsWarps * kCrowsRows);
   const long long cap = (long long)sm_count() * 8;
   if (g > cap) g = cap;
   crows_pack_kernel<<<(unsigned)g, kCrowsWarps * 32, smem, (cudaStream_t)stream>>>(
@@ -179,7 +211,7 @@ int exact_crows_unpack(const void* buf, int64_t n, int64_t K, int64_t row0, floa
   EXB_REQUIRE(n >= 0 && K > 0 && K <= 256 && ldo >= K && row0 >= 0, "crows_unpack: need 0 < K <= 256, ldo >= K");
   if (n == 0) return EXB_OK;
   EXB_REQUIRE(buf != nullptr && out != nullptr, "crows_unpack: null pointer");
-  long long g = (n + kCrowsWarps - 1) / kCrowsWarps;
+  long long g = (n + kCrowsWarps * kCrowsRows - 1) / (kCrowsWarps * kCrowsRows);
   const long long cap = (long long)sm_count() * 16;
   if (g > cap) g = cap;
   crows_unpack_kernel<<<(unsigned)g, kCrowsWarps * 32, 0, (cudaStream_t)stream>>>(

@@ -1,8 +1,7 @@
 // 1-bit-mask activations: ReLU and dropout that keep one bit per element for backward.
 //
-// Replaces quantization.act_quantized_relu / act_quantized_dropout
-// (exact/exact/cpp_extension/quantization.cc:66-84, 111-134; kernels
-// quantization_cuda_kernel.cu:237-331, 442-594).
+// Replaces quantization.act_quantized_relu / act_quantized_leaky_relu / act_quantized_dropout
+// (exact/exact/cpp_extension/quantization.cc:66-134; kernels quantization_cuda_kernel.cu:237-594).
 //
 // A warp handles 128 consecutive elements per step: each lane loads one float4, and four
 // __ballot_sync calls turn the 128 predicates into four mask words.  Word 4*c + j, bit l holds
@@ -15,7 +14,7 @@
 
 namespace exb {
 
-enum MaskOp { OP_RELU = 0, OP_DROPOUT = 1, OP_RELU_DROPOUT = 2 };
+enum MaskOp { OP_RELU = 0, OP_DROPOUT = 1, OP_RELU_DROPOUT = 2, OP_LEAKY_RELU = 3 };
 
 struct MaskParams {
   const float* x;       // forward input or grad_out
@@ -23,7 +22,7 @@ struct MaskParams {
   float* out;           // output or grad_in
   uint32_t* mask;
   long long n;
-  float p;              // dropout probability
+  float p;              // dropout probability; the negative slope for LeakyReLU
   float pinv;           // float(1 / (1 - p))
   float p1m;            // float(1 - p)
   float p1m_inv_exact;  // 1 / p1m when p1m is a power of two (then g / p1m == g * that, bit for bit), else 0
@@ -69,6 +68,12 @@ __global__ void __launch_bounds__(256) mask_forward_kernel(const __grid_constant
       for (int j = 0; j < 4; j++) {
         keep[j] = v[j] > 0.f;           // quantization_cuda_kernel.cu:253
         o[j] = keep[j] ? v[j] : 0.f;
+      }
+    } else if (OP == OP_LEAKY_RELU) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        keep[j] = v[j] > 0.f;           // quantization_cuda_kernel.cu:356-361
+        o[j] = keep[j] ? v[j] : __fmul_rn(v[j], p.p);
       }
     } else {
       if (OP == OP_RELU_DROPOUT) {
@@ -121,6 +126,8 @@ __global__ void __launch_bounds__(256) mask_backward_kernel(const __grid_constan
       const bool keep = (m[j] >> lane) & 1u;
       if (OP == OP_RELU) {
         o[j] = keep ? g[j] : 0.f;                      // quantization_cuda_kernel.cu:303-308
+      } else if (OP == OP_LEAKY_RELU) {
+        o[j] = keep ? g[j] : __fmul_rn(g[j], p.p);     // quantization_cuda_kernel.cu:408-412
       } else {
         // quantization_cuda_kernel.cu:565-569: g / float(1 - p); a power-of-two divisor (p = 0.5, 0.75, ...)
         // is an exact scaling, done as one multiply
@@ -176,6 +183,22 @@ int exact_act_quantized_relu_backward(const float* grad_out, const uint32_t* mas
   MaskParams p{};
   p.x = grad_out; p.out = grad_in; p.mask = const_cast<uint32_t*>(mask); p.n = n;
   return launch_mask<OP_RELU>(false, p, (cudaStream_t)stream);
+}
+
+int exact_act_quantized_leaky_relu_forward(const float* x, int64_t n, float slope, float* out, uint32_t* mask,
+                                           void* stream) {
+  EXB_REQUIRE(n >= 0, "leaky_relu: negative size");
+  MaskParams p{};
+  p.x = x; p.out = out; p.mask = mask; p.n = n; p.p = slope;
+  return launch_mask<OP_LEAKY_RELU>(true, p, (cudaStream_t)stream);
+}
+
+int exact_act_quantized_leaky_relu_backward(const float* grad_out, const uint32_t* mask, int64_t n, float slope,
+                                            float* grad_in, void* stream) {
+  EXB_REQUIRE(n >= 0, "leaky_relu: negative size");
+  MaskParams p{};
+  p.x = grad_out; p.out = grad_in; p.mask = const_cast<uint32_t*>(mask); p.n = n; p.p = slope;
+  return launch_mask<OP_LEAKY_RELU>(false, p, (cudaStream_t)stream);
 }
 
 int exact_act_quantized_dropout_forward(const float* x, int64_t n, float prob, const float* uniforms,

@@ -3,6 +3,8 @@ bit widths, row counts, column counts and input dtypes (the kernel-level benchma
 
   python -m exact_b200.kernel_sweep                          # default grid, one JSON line per case
   python -m exact_b200.kernel_sweep --op pack --N 1000000 --D 128 --bits 2 --reps 3   # one case (for ncu)
+  python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m exact_b200.kernel_sweep --sharded \
+      --N 10000000 --D 128 256 --bits 2                      # row-sharded over the GPUs of one node
 
 Timing: CUDA events on the launching stream, 3 warm-up launches, inputs larger than L2 or an L2 flush
 between launches (a 256 MB write) when they are not."""
@@ -196,6 +198,99 @@ def run_spmm(nodes, avg_deg, K, reps, reduce, density=None):
     return out
 
 
+def run_sharded(op, N, D, bits, kept_frac, reps):
+    """Row-sharded kernel sweep: every rank runs the kernel on its shard of the N rows (a multiple of 8 rows,
+    noise keyed by global rows), the aggregate is bytes of all ranks / slowest rank's time (no collective on
+    the data path), and rank 0 checks that the shards' packed streams and statistics, concatenated in rank
+    order, are the bytes one GPU produces for the whole matrix (SHA-256 of both)."""
+    import hashlib
+
+    import torch.distributed as dist
+
+    from . import dist as xdist
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    shard = xdist.shard_rows(N, world)
+    r0, r1 = min(rank * shard, N), min(rank * shard + shard, N)
+    n = r1 - r0
+
+    def rows(a, b):   # rows [a, b) of the synthetic matrix (every rank draws the same whole matrix and slices it)
+        g = torch.Generator(device=dev).manual_seed(1234)
+        full = torch.randn(N, D, device=dev, generator=g).relu_()
+        return full[a:b].contiguous()
+
+    x = rows(r0, r1)
+    k = D if kept_frac >= 1.0 else int(kept_frac * D + 0.999)
+    if op == "rp_pack":
+        from .ops import _rademacher
+        R = _rademacher(D, k, dev, torch.float32, seed=1, offset=0)
+        call = lambda t, off: Q.rp_quantize_pack(t, R, bits, seed=1, offset=1, row_offset=off)
+        nbytes = n * D * 4 + D * k * 4 + ((n + 8 // bits - 1) // (8 // bits)) * k + 4 * n
+    else:
+        call = lambda t, off: Q.quantize_pack(t, bits, seed=1, offset=1, row_offset=off)
+        nbytes = n * D * 4 + ((n + 8 // bits - 1) // (8 // bits)) * D + 4 * n
+    flush = torch.empty(64 * 1024 * 1024, device=dev) if n * D * 4 < 256e6 else None
+    ms = torch.tensor([_time(lambda: call(x, r0), reps, flush)], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    tot = torch.tensor([float(nbytes)], device=dev, dtype=torch.float64)
+    dist.all_reduce(tot)
+    pk, sb, mb = call(x, r0)
+    body = torch.cat([pk.view(torch.uint8)[:-1], sb.view(torch.uint8), mb.view(torch.uint8)])
+    sizes = torch.zeros(world, dtype=torch.int64, device=dev)
+    sizes[rank] = body.numel()
+    dist.all_reduce(sizes)
+    sizes = [int(v) for v in sizes.tolist()]
+    pad = torch.zeros(max(sizes), dtype=torch.uint8, device=dev)
+    pad[:body.numel()] = body
+    allb = torch.empty(world * max(sizes), dtype=torch.uint8, device=dev)
+    dist.all_gather_into_tensor(allb, pad)
+    if rank != 0:
+        return None
+    peak, kind = _peak()
+    parts = [allb[r * max(sizes):r * max(sizes) + sizes[r]].cpu() for r in range(world)]
+    # split each rank's bytes back into stream / scale / min and concatenate per kind in rank order
+    streams, scales, mins = [], [], []
+    for r, part in enumerate(parts):
+        nr = min(r * shard + shard, N) - min(r * shard, N)
+        streams.append(part[:part.numel() - 4 * nr])
+        scales.append(part[part.numel() - 4 * nr:part.numel() - 2 * nr])
+        mins.append(part[part.numel() - 2 * nr:])
+    sharded = hashlib.sha256(torch.cat(streams + scales + mins).numpy().tobytes()).hexdigest()
+    del x
+    torch.cuda.empty_cache()
+    pk1, sb1, mb1 = call(rows(0, N), 0)
+    whole = hashlib.sha256(torch.cat([pk1.view(torch.uint8)[:-1].cpu(), sb1.view(torch.uint8).cpu(),
+                                      mb1.view(torch.uint8).cpu()]).numpy().tobytes()).hexdigest()
+    gbs = float(tot.item()) / (float(ms.item()) * 1e-3) / 1e9
+    return {"op": op, "sharded_over": world, "N": N, "D": D, "k": k, "bits": bits, "ms_slowest_rank": round(float(ms.item()), 4),
+            "aggregate_GB/s": round(gbs, 1), "frac_of_n_peaks": round(gbs / (peak * world), 4), "peak_per_gpu": peak,
+            "peak_kind": kind, "shard_streams_equal_one_gpu_stream": sharded == whole, "sha256": whole}
+
+
+def main_sharded(a):
+    """torchrun entry of the row-sharded sweep: pack and fused projection + pack over N x D x bits x kept_frac."""
+    import torch.distributed as dist
+
+    from . import dist as xdist
+    rank, world, _ = xdist.init_process_group_from_env()
+    assert world > 1, "--sharded runs under torchrun with more than one rank"
+    for N in a.N:
+        for D in a.D:
+            if N * D * 4 > a.max_bytes:
+                continue
+            for bits in a.bits:
+                for kf in [1.0] + list(a.kept_frac):
+                    op = "pack" if kf >= 1.0 else "rp_pack"
+                    if op == "rp_pack" and not Q.rp_supported(D, int(kf * D + 0.999)):
+                        continue
+                    r = run_sharded(op, N, D, bits, kf, a.reps)
+                    if r is not None:
+                        print(json.dumps(r), flush=True)
+                    torch.cuda.empty_cache()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp", "linear", "mask"])
@@ -212,8 +307,13 @@ def main():
     ap.add_argument("--density", type=float, default=None,
                     help="--op spmm: share of non-zero operand entries; below 1 the compact-rows pack / unpack are timed too")
     ap.add_argument("--max-bytes", type=float, default=12e9, help="skip cases whose input exceeds this")
+    ap.add_argument("--sharded", action="store_true",
+                    help="row-sharded sweep of pack and fused projection + pack; launch with torchrun on 2, 4 or 8 GPUs")
     a = ap.parse_args()
     _lib.load()
+    if a.sharded:
+        main_sharded(a)
+        return
     if a.op == "spmm":
         for K in a.K:
             for r in run_spmm(a.nodes, a.avg_deg, K, a.reps, "mean", a.density):

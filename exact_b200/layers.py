@@ -136,6 +136,17 @@ class QReLU(torch.nn.Module):
         return F.relu(input)
 
 
+class QLeakyReLU(torch.nn.Module):
+    """layers.py:295-301 (the reference applies the masked kernel in training and in evaluation alike)."""
+
+    def __init__(self, negative_slope, inplace=False):
+        super().__init__()
+        self.negative_slope = negative_slope
+
+    def forward(self, input):
+        return ext_quantization.act_quantized_leaky_relu(input, self.negative_slope)
+
+
 class QDropout(torch.nn.Module):
     """layers.py:316-325."""
 

