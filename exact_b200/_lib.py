@@ -59,6 +59,9 @@ SIGNATURES = {
     "exact_unpack_rp_workspace_bytes": (c_i64, [c_i64, c_i64]),
     "exact_unpack_dequant_rp": (c_int, [c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_i64, c_ptr, c_ptr, c_ptr]),
     "exact_rademacher": (c_int, [c_u64, c_u64, c_i64, c_i64, c_ptr, c_ptr]),
+    "exact_grad_weight_workspace_bytes": (c_i64, [c_i64, c_i64, c_int]),
+    "exact_grad_weight_from_packed": (c_int, [c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_i64,
+                                              c_int, c_ptr, c_i64, c_ptr, c_i64, c_ptr]),
     "exact_rows_mask_count": (c_int, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr]),
     "exact_rows_compact_write": (c_int, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr]),
     "exact_rows_expand": (c_int, [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_i64, c_i64, c_ptr, c_i64, c_ptr]),

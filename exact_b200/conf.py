@@ -49,6 +49,10 @@ class QuantizationConfig:
         # Dense-layer GEMMs over node rows on the tensor cores with operands split into tf32 head and tail
         # (fp32-equivalent accuracy); False: the library's fp32 GEMM.
         self.linear_tensor_core = True
+        # Weight gradients of the quantised linear layers straight from the packed activation on the tensor
+        # cores (tf32 inputs, fp32 accumulation: about 5e-4 relative, far below the quantisation noise of the
+        # activation); False: unpack, then the library's fp32 GEMM.
+        self.grad_weight_tensor_core = True
         # Row-sharded aggregation inside the one-node GraphSAGE layer: exchange the dense operand as compact
         # rows (kept columns + values per row) when at most this share of its entries is non-zero, as outputs
         # of ReLU + dropout and gradients that passed their masks are.  Same dense rows bit for bit.

@@ -81,6 +81,48 @@ def rows_reduce_mm(g, x, batches=512):
     return out
 
 
+def grad_weight_supported(g, k0, k1, bits):
+    """Shapes exact_grad_weight_from_packed takes: fp32 g [N, O] with O % 4 == 0, O <= 256, at least 4,096 rows
+    (below that the library GEMM on the unpacked activation is as fast), and few enough activation columns for
+    four producer warps (k0 + k1 <= 1024 * bits / 256)."""
+    if not (config.grad_weight_tensor_core and g.is_cuda and g.dtype == torch.float32 and g.dim() == 2):
+        return False
+    N, O = g.shape
+    kpad = (k0 + 15) // 16 * 16 + ((k1 + 15) // 16 * 16 if k1 else 0)
+    return (N >= 4096 and O % 4 == 0 and O <= 256 and kpad <= 256 and (k0 + k1) * (32 // (8 // bits)) <= 1024
+            and g.is_contiguous() and g.data_ptr() % 16 == 0)
+
+
+_SM_COUNT = {}
+
+
+def grad_weight_from_packed(g, q0, k0, q1=None, k1=0):
+    """(g^T Xq0 [O, k0], g^T Xq1 [O, k1] or None) for packed activations q = (packed, bits, scale_bf16, min_bf16)
+    of N rows: backward_func.cc:87 with the dequantisation of ops.py:164 folded in, one pass over g."""
+    lib = _lib.load()
+    N, O = g.shape
+    bits = q0[1]
+    k0pad = (k0 + 15) // 16 * 16
+    kpad = k0pad + ((k1 + 15) // 16 * 16 if q1 is not None else 0)
+    dev = g.device
+    sms = _SM_COUNT.get(dev.index)
+    if sms is None:
+        sms = _SM_COUNT[dev.index] = torch.cuda.get_device_properties(dev).multi_processor_count
+    ws_bytes = int(lib.exact_grad_weight_workspace_bytes(O, kpad, sms))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    out = torch.empty((O, kpad), dtype=torch.float32, device=dev)
+    nbytes = 4 * N * O + (N * (k0 + (k1 if q1 is not None else 0)) * bits) // 8 + 4 * N * (2 if q1 is not None else 1)
+    _lib.invoke("exact_grad_weight_from_packed", nbytes, _lib.ptr(g), N, O, _lib.ptr(q0[0]), _lib.ptr(q0[2]), _lib.ptr(q0[3]),
+                k0, _lib.ptr(q1[0]) if q1 is not None else None, _lib.ptr(q1[2]) if q1 is not None else None,
+                _lib.ptr(q1[3]) if q1 is not None else None, k1 if q1 is not None else 0, bits, _lib.ptr(ws), ws_bytes,
+                _lib.ptr(out), kpad, _lib.stream_ptr(), flops=2.0 * N * O * kpad)
+    if config.check_device_status:
+        status = int(ws[:4].view(torch.int32).item())
+        if status != 0:
+            raise _lib.ExactB200Error(f"grad_weight_from_packed: device status {status} (a bounded on-chip wait expired)")
+    return out[:, :k0], (out[:, k0pad:k0pad + k1] if q1 is not None else None)
+
+
 def linear_backward(grad_output, input, weight, bias=None, need_grad_input=True):
     """backward_func.cc:83-93.  The input gradient is left out (None) when the caller has no use for it."""
     grad_input = linear_forward(grad_output, weight.t()) if need_grad_input else None

@@ -139,6 +139,32 @@ def run_linear(M, K, N, reps):
             "rel_err_vs_fp64": err, "library_rel_err_vs_fp64": err_lib, "peak_kind": kind}
 
 
+def run_grad_weight(N, O, k, bits, reps):
+    """g^T . dequantise([Xq_a | Xq_b]) (two packed activations of k columns, one pass over g) against the route
+    it replaces: two unpacks and two batched library GEMMs."""
+    from .cpp_extension import backward_func as B
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev).manual_seed(0)
+    g = torch.randn(N, O, device=dev, generator=gen)
+    qs = []
+    for s in (1, 2):
+        x = torch.randn(N, k, device=dev, generator=gen)
+        pk, sb, mb = Q.quantize_pack(x, bits, seed=s, offset=0)
+        qs.append((pk, bits, sb, mb))
+    ms = _time(lambda: B.grad_weight_from_packed(g, qs[0], k, qs[1], k), reps, None)
+
+    def old():
+        for q in qs:
+            B.rows_reduce_mm(g, Q.unpack_single_precision(q[0], bits, q[2], q[3], N, k))
+    ms_old = _time(old, reps, None)
+    nbytes = 4 * N * O + 2 * (N * k * bits // 8 + 4 * N)
+    peak, kind = _peak()
+    return {"op": "grad_weight_from_packed", "N": N, "O": O, "k": [k, k], "bits": bits, "ms": round(ms, 4),
+            "unpack_plus_library_gemm_ms": round(ms_old, 4), "GB/s": round(nbytes / (ms * 1e-3) / 1e9, 1),
+            "frac": round(nbytes / (ms * 1e-3) / 1e9 / peak, 4), "TFLOP/s": round(4.0 * N * O * k / (ms * 1e-3) / 1e12, 1),
+            "peak": peak, "peak_kind": kind}
+
+
 def run_mask(N, D, p, reps):
     """ReLU + dropout of a hidden layer in one pass (forward) and its backward: GB/s on 8 bytes + 1 bit per element."""
     dev = torch.device("cuda")
@@ -293,7 +319,7 @@ def main_sharded(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp", "linear", "mask"])
+    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp", "linear", "mask", "grad_weight"])
     ap.add_argument("--kept-frac", type=float, nargs="*", default=[0.5, 0.125])
     ap.add_argument("--N", type=int, nargs="*", default=[100_000, 1_000_000, 10_000_000])
     ap.add_argument("--D", type=int, nargs="*", default=[64, 128, 256, 602])
@@ -318,6 +344,11 @@ def main():
         for K in a.K:
             for r in run_spmm(a.nodes, a.avg_deg, K, a.reps, "mean", a.density):
                 print(json.dumps(r), flush=True)
+        return
+    if a.op == "grad_weight":
+        for N in a.N:
+            for bits in a.bits:
+                print(json.dumps(run_grad_weight(N, 256, 32, bits, a.reps)), flush=True)
         return
     if a.op == "mask":
         for N in a.N:

@@ -199,6 +199,19 @@ def linear_backward_from_compressed(quantized, weight, bias, randmat, ori_input_
     """ops.py:152-178: (grad_input, grad_weight, grad_bias) of y = x W^T + b from the compressed x."""
     projected = config.kept_frac < 1.0 and rp and randmat is not None
     input = None
+    if (config.compress_activation and not config.simulate and not config.swap and quantized[1] is not None
+            and len(q_input_shape) == 2 and (not projected or config.grad_weight_in_projected_space)
+            and ext_backward_func.grad_weight_supported(grad_output, q_input_shape[1], 0, quantized[1])):
+        # g^T Xq on the tensor cores with the dequantisation in the operand path: the [N, k] fp32 activation is
+        # never written; with a projection, (g^T Xq) R^T instead of g^T (Xq R^T)
+        grad_weight, _ = ext_backward_func.grad_weight_from_packed(grad_output, quantized, q_input_shape[1])
+        if projected:
+            grad_weight = grad_weight.mm(randmat.t())
+        else:
+            grad_weight = grad_weight.contiguous()
+        grad_input = ext_backward_func.linear_forward(grad_output, weight.t()) if need_grad_input else None
+        grad_bias = grad_output.sum(0) if bias is not None else None
+        return grad_input, grad_weight, grad_bias
     if (projected and not config.grad_weight_in_projected_space and config.fused_rp and config.compress_activation
             and not config.simulate and not config.swap and len(ori_input_shape) == 2
             and ext_quantization.unpack_rp_supported(ori_input_shape[1], q_input_shape[1])):

@@ -149,12 +149,25 @@ class qsage_layer(Function):
         x_shape, proj_x, proj_agg = ctx.other_args
         del ctx.saved
         g = grad_output.contiguous()
-        _, grad_w_l, grad_b = linear_backward_from_compressed(q_agg, w_l, b_l, randmat_agg, x_shape, proj_agg, True,
-                                                              g, False)
         grad_w_r = None
-        if w_r is not None:
-            _, grad_w_r, _ = linear_backward_from_compressed(q_x, w_r, None, randmat_x, x_shape, proj_x, True, g,
-                                                             False)
+        k_agg, k_x = proj_agg[1], proj_x[1]
+        both_projected = randmat_agg is not None and (w_r is None or randmat_x is not None)
+        if (config.compress_activation and not config.simulate and not config.swap and q_agg[1] is not None
+                and config.grad_weight_in_projected_space and both_projected
+                and ext_backward_func.grad_weight_supported(g, k_agg, k_x if w_r is not None else 0, q_agg[1])):
+            # both weight gradients in one pass over g: g^T [Xq_agg | Xq_x] on the tensor cores, dequantised
+            # on the way in, then the two small transposed projections
+            ga, gx = ext_backward_func.grad_weight_from_packed(g, q_agg, k_agg, q_x if w_r is not None else None, k_x)
+            grad_w_l = ga.mm(randmat_agg.t())
+            grad_b = g.sum(0) if b_l is not None else None
+            if w_r is not None:
+                grad_w_r = gx.mm(randmat_x.t())
+        else:
+            _, grad_w_l, grad_b = linear_backward_from_compressed(q_agg, w_l, b_l, randmat_agg, x_shape, proj_agg, True,
+                                                                  g, False)
+            if w_r is not None:
+                _, grad_w_r, _ = linear_backward_from_compressed(q_x, w_r, None, randmat_x, x_shape, proj_x, True, g,
+                                                                 False)
         grad_x = None
         if ctx.needs_input_grad[1]:
             out_f, in_f = w_l.shape

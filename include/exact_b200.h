@@ -278,6 +278,26 @@ EXACT_API int exact_linear_forward(const float* A, int64_t M, int64_t K, int64_t
                                    int64_t N, const float* bias, int accumulate, void* workspace, float* C,
                                    int64_t ldc, void* stream);
 
+/* Weight gradient of a quantised linear layer from the packed activation(s), on the tensor cores:
+ *     out[O, kpad] = g^T [O x N] . dequantise(packed) [N x k]
+ * grad_weight = grad_output.t().mm(input) of linear_backward (exact/exact/cpp_extension/backward_func.cc:87) with
+ * `input` as qlinear.forward saved it (exact/exact/ops.py:149-154: packed codes + bf16 row statistics), fusing
+ * dequantize_activation (ops.py:164) into the product.  With a random projection the caller multiplies the
+ * result by R^T ((g^T Xq) R^T = g^T (Xq R^T), ops.py:165-169).  Two packed activations that share g (the two
+ * inputs of a GraphSAGE layer, layers.py:163-170) go in one pass: columns [0, k0) of `out` belong to the first,
+ * columns [pad16(k0), pad16(k0) + k1) to the second (k1 = 0: one activation); ldo >= pad16(k0) + pad16(k1).
+ *   g [N, O] fp32, 16-byte aligned, O % 4 == 0, O <= 256; other shapes return code 3 (the caller unpacks and
+ *   uses a library GEMM).  tf32 inputs, fp32 accumulation: about 5e-4 relative.
+ *   workspace: exact_grad_weight_workspace_bytes(O, pad16(k0) + pad16(k1), SM count) bytes, 256-byte aligned:
+ *   its first int32 is the status word (see exact_rp_quantize_pack), the rest holds one partial result per CTA,
+ *   added in CTA order by a second kernel (the result does not depend on timing). */
+EXACT_API int64_t exact_grad_weight_workspace_bytes(int64_t O, int64_t k_total_padded, int max_ctas);
+EXACT_API int exact_grad_weight_from_packed(const float* g, int64_t N, int64_t O, const uint8_t* packed0,
+                                            const uint16_t* scale0, const uint16_t* min0, int64_t k0,
+                                            const uint8_t* packed1, const uint16_t* scale1, const uint16_t* min1,
+                                            int64_t k1, int bits, void* workspace, int64_t workspace_bytes,
+                                            float* out, int64_t ldo, void* stream);
+
 /* Zero-compacted rows, the exchange format of the row-sharded aggregation.  No counterpart in the
  * reference (it is single-GPU).  A shard x [n, K] fp32 (row pitch ldx, K % 32 == 0) whose entries are
  * mostly exact zeros (outputs of ReLU + dropout, gradients that passed their masks) is sent as
