@@ -9,13 +9,18 @@
 //
 // Shape of the work.  N is the number of nodes (millions), O <= 256, k <= 128: 2 N O k flop against
 // 4 N O bytes of g, so the kernel is bound by reading g once; the tensor core makes the multiply-adds
-// free.  The contraction runs over node rows, which are the slow dimension of both operands:
-//   A = g^T   arrives by TMA as [32 rows x 32 columns] boxes of g (128-byte swizzle): 32 consecutive
-//             outputs of one node row are contiguous, i.e. the tile is MN-major for the MMA (descriptor with
-//             leading-dimension offset = one box, instruction descriptor with the transpose-A bit);
+// free.  The contraction runs over node rows, which are the slow dimension of both operands in memory,
+// while the MMA wants the contraction dimension contiguous in shared memory (K-major tiles):
+//   A = g^T   [32 rows x O] boxes of g arrive by TMA (no swizzle) in a ring of raw stages; four converter
+//             warps transpose them: a thread reads one output column of the box (conflict-free: the 32
+//             lanes read 32 consecutive words of a row) and writes the 32 node rows of that output as one
+//             128-byte row of the 128-byte-swizzled K-major tile (eight 16-byte stores);
 //   B = Xq    is produced K-major by four warps that read the packed bytes (one byte = 8/bits consecutive
 //             node rows of one column, which is one 16-byte chunk of the tile at INT2) and the bf16 row
 //             statistics, dequantise (code / scale + min) and store to the swizzled tile.
+// A tile whose contraction dimension is the slow one (MN-major) could be fed to tcgen05.mma directly by
+// setting the transpose bit of the instruction descriptor; with tf32 operands and the 128-byte swizzle that
+// TMA writes the unit returned zeros on this hardware, hence the transposition in shared memory.
 // Each CTA owns a contiguous range of 32-row blocks and accumulates its partial G in TMEM over the whole
 // range (split over node rows across the SMs); partials go to the workspace and a second kernel adds them
 // in CTA order, so the result does not depend on timing.  tf32 inputs, fp32 accumulation: about 5e-4
@@ -30,7 +35,7 @@
 namespace exb {
 
 constexpr int kGwRows = 32;          // node rows per pipeline stage (= the K extent of a stage)
-constexpr int kGwThreads = 192;      // warp 0 TMA, warp 1 MMA, warps 2-5 producers of B and epilogue
+constexpr int kGwThreads = 320;      // warp 0 TMA, warp 1 MMA, warps 2-5 producers of B and epilogue, 6-9 converters
 constexpr int kGwMaxStages = 6;
 constexpr int kGwMaxSeg = 2;
 
@@ -51,23 +56,11 @@ struct GwParams {
   long long N;
   int O, Opad, kpad, bits;
   int mtiles;         // Opad / 128
-  int oblocks;        // ceil(O / 32): boxes of g per stage
   long long kblocks;  // ceil(N / 32)
-  int stages;
+  int raw_stages, stages;
+  unsigned raw_bytes;                    // one raw box of g: 32 rows x O fp32, padded to 1024 bytes
   unsigned a_bytes, b_bytes, stage_bytes, tmem_cols;
 };
-
-// MN-major operand tile, 128-byte swizzle: blocks of 32 contiguous MN elements (128 bytes) x 8 K rows are
-// 1024 bytes; K groups of 8 rows follow each other (stride 1024), blocks along MN are `lbo` bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t saddr, uint32_t lbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3fffu);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= (uint64_t)(1024u >> 4) << 32;
-  d |= 1ull << 46;
-  d |= 2ull << 61;
-  return d;
-}
 
 __device__ __forceinline__ void gw_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -78,8 +71,10 @@ grad_weight_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_consta
   constexpr uint32_t MASK = (1u << BITS) - 1u;
   constexpr int GROUPS = kGwRows / WPT;     // packed bytes per column and stage
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) unsigned long long s_full[kGwMaxStages];
-  __shared__ __align__(8) unsigned long long s_empty[kGwMaxStages];
+  __shared__ __align__(8) unsigned long long s_rfull[kGwMaxStages];    // raw box of g landed
+  __shared__ __align__(8) unsigned long long s_rempty[kGwMaxStages];   // raw box transposed
+  __shared__ __align__(8) unsigned long long s_full[kGwMaxStages];     // A^T and B of an MMA stage written
+  __shared__ __align__(8) unsigned long long s_empty[kGwMaxStages];    // MMA stage read by the tensor core
   __shared__ __align__(8) unsigned long long s_done;
   // row statistics of the stage a producer warp works on and of the next one: a private copy per warp, so the
   // producers need no barrier among themselves
@@ -91,13 +86,19 @@ grad_weight_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* tiles_ptr = smem_raw + (tiles_base - smem_u32(smem_raw));
+  // layout of the dynamic shared memory: raw ring, then the MMA stages (A^T tiles, B tile)
+  const uint32_t mma_off = (uint32_t)p.raw_stages * p.raw_bytes;
   volatile int* abort_flag = &s_abort;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
+    for (int s = 0; s < p.raw_stages; s++) {
+      mbar_init(smem_u32(&s_rfull[s]), 1);    // the TMA thread's bytes
+      mbar_init(smem_u32(&s_rempty[s]), 4);   // one arrival per converter warp
+    }
     for (int s = 0; s < p.stages; s++) {
-      mbar_init(smem_u32(&s_full[s]), 5);    // the TMA thread's bytes + one arrival per producer warp
-      mbar_init(smem_u32(&s_empty[s]), 1);   // tcgen05.commit
+      mbar_init(smem_u32(&s_full[s]), 8);     // one arrival per producer warp and per converter warp
+      mbar_init(smem_u32(&s_empty[s]), 1);    // tcgen05.commit
     }
     mbar_init(smem_u32(&s_done), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -105,7 +106,7 @@ grad_weight_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_consta
   if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), p.tmem_cols);
   // B rows that hold no column of any activation stay zero for the whole kernel
   for (int s = 0; s < p.stages; s++) {
-    uint4* b = reinterpret_cast<uint4*>(tiles_ptr + (size_t)s * p.stage_bytes + p.a_bytes);
+    uint4* b = reinterpret_cast<uint4*>(tiles_ptr + mma_off + (size_t)s * p.stage_bytes + p.a_bytes);
     for (unsigned i = threadIdx.x; i < p.b_bytes / 16; i += kGwThreads) b[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   gw_fence_proxy_async();
@@ -121,26 +122,24 @@ grad_weight_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_consta
   const long long nblk = kb1 > kb0 ? kb1 - kb0 : 0;
 
   if (warp == 0) {
-    // ---------------- TMA producer of A = g^T ----------------
+    // ---------------- TMA producer: raw boxes of g ----------------
     if (lane == 0) {
       bool ok = true;
       long long it = 0;
       for (; it < nblk && ok; it++) {
-        const int s = (int)(it % p.stages);
-        const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
-        if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
-        const uint32_t full = smem_u32(&s_full[s]);
-        const uint32_t dst = tiles_base + (uint32_t)s * p.stage_bytes;
-        mbar_arrive_expect_tx(full, (uint32_t)p.oblocks * (kGwRows * 128));
-        const int row = (int)((kb0 + it) * kGwRows);
-        for (int ob = 0; ob < p.oblocks; ob++) tma_load_2d(dst + (uint32_t)ob * (kGwRows * 128), &tm_g, ob * 32, row, full);
+        const int s = (int)(it % p.raw_stages);
+        const uint32_t ph = (uint32_t)(it / p.raw_stages) & 1u;
+        if (!mbar_wait(smem_u32(&s_rempty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
+        const uint32_t full = smem_u32(&s_rfull[s]);
+        mbar_arrive_expect_tx(full, (uint32_t)(kGwRows * p.O * 4));
+        tma_load_2d(tiles_base + (uint32_t)s * p.raw_bytes, &tm_g, 0, (int)((kb0 + it) * kGwRows), full);
       }
-      if (!ok) {
+      if (!ok) {   // leave no bulk copy in flight
         const long long t0 = clock64();
-        for (int j = 0; j < p.stages && j < it; j++) {
+        for (int j = 0; j < p.raw_stages && j < it; j++) {
           const long long jt = it - 1 - j;
-          const uint32_t bar = smem_u32(&s_full[jt % p.stages]);
-          const uint32_t ph = (uint32_t)(jt / p.stages) & 1u;
+          const uint32_t bar = smem_u32(&s_rfull[jt % p.raw_stages]);
+          const uint32_t ph = (uint32_t)(jt / p.raw_stages) & 1u;
           while (!mbar_try_wait(bar, ph) && clock64() - t0 < kWaitLimitCycles) {}
         }
       }
@@ -148,75 +147,124 @@ grad_weight_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_consta
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      // transpose-A bit (15): A is MN-major
-      const uint32_t idesc = umma_idesc_tf32(128, p.kpad) | (1u << 15);
+      const uint32_t idesc = umma_idesc_tf32(128, p.kpad);
       bool ok = true;
       for (long long it = 0; it < nblk && ok; it++) {
         const int s = (int)(it % p.stages);
         const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
         if (!mbar_wait(smem_u32(&s_full[s]), ph, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t a_addr = tiles_base + (uint32_t)s * p.stage_bytes;
+        const uint32_t a_addr = tiles_base + mma_off + (uint32_t)s * p.stage_bytes;
         const uint64_t b_desc = umma_desc_sw128(a_addr + p.a_bytes);
         for (int mt = 0; mt < p.mtiles; mt++) {
-          // four boxes (32 outputs each) make the 128 rows of one M tile
-          const uint64_t a_desc = umma_desc_mn_sw128(a_addr + (uint32_t)mt * 4u * (kGwRows * 128), kGwRows * 128);
+          const uint64_t a_desc = umma_desc_sw128(a_addr + (uint32_t)mt * (128 * 128));
 #pragma unroll
-          for (int k8 = 0; k8 < kGwRows / 8; k8++) {
-            // A: the next 8 node rows are 1024 bytes further; B: 8 tf32 = 32 bytes along its 128-byte rows
-            umma_tf32(tmem_base + (uint32_t)(mt * p.kpad), a_desc + (uint64_t)(k8 * 64), b_desc + (uint64_t)(k8 * 2), idesc,
+          for (int k8 = 0; k8 < kGwRows / 8; k8++)   // 8 tf32 = 32 bytes along the 128-byte rows of both tiles
+            umma_tf32(tmem_base + (uint32_t)(mt * p.kpad), a_desc + (uint64_t)(k8 * 2), b_desc + (uint64_t)(k8 * 2), idesc,
                       (it | k8) != 0);
-          }
         }
         umma_commit(smem_u32(&s_empty[s]));
       }
       if (ok) umma_commit(smem_u32(&s_done));
     }
+  } else if (warp >= 6) {
+    // ---------------- converters (warps 6..9): raw box [32 rows x O] -> A^T tiles [128 outputs x 32 rows] ----------------
+    const int t = threadIdx.x - 192;           // 0 .. 127: output within an M tile
+    bool ok = true;
+    for (long long it = 0; it < nblk; it++) {
+      const int rs = (int)(it % p.raw_stages), s = (int)(it % p.stages);
+      const uint32_t rph = (uint32_t)(it / p.raw_stages) & 1u, ph = (uint32_t)(it / p.stages) & 1u;
+      // the same verdict in every lane, so that a warp leaves the loop as a whole
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_rfull[rs]), rph, abort_flag))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, abort_flag))) { ok = false; break; }
+      const float* raw = reinterpret_cast<const float*>(tiles_ptr + (size_t)rs * p.raw_bytes);
+      uint8_t* at = tiles_ptr + mma_off + (size_t)s * p.stage_bytes;
+      for (int mt = 0; mt < p.mtiles; mt++) {
+        const int o = mt * 128 + t;
+        float v[kGwRows];
+#pragma unroll
+        for (int n = 0; n < kGwRows; n++) v[n] = o < p.O ? raw[n * p.O + o] : 0.f;
+        uint8_t* row = at + (size_t)mt * (128 * 128) + t * 128;
+#pragma unroll
+        for (int c = 0; c < kGwRows / 4; c++)
+          *reinterpret_cast<float4*>(row + ((c ^ (t & 7)) << 4)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+      }
+      gw_fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&s_rempty[rs]));
+        mbar_arrive(smem_u32(&s_full[s]));
+      }
+    }
+    (void)ok;
   } else {
     // ---------------- producers of B = dequantised activation (warps 2..5), then the epilogue ----------------
     const int t = threadIdx.x - 64;            // 0 .. 127
     bool ok = true;
-    // items of a stage: (segment, column j, byte group q); thread t takes items t, t + 128, ...
+    // Items of a stage: (segment, column j, byte group q); thread t takes items t, t + 128, ...  Everything
+    // about an item that does not change from stage to stage is worked out once, here: a producer warp has
+    // an SM sub-partition to itself, so every dependent instruction inside the loop costs its full latency.
     int total_items = 0;
     for (int sg = 0; sg < p.nseg; sg++) total_items += p.seg[sg].k * GROUPS;
     constexpr int kMaxItems = 8;               // per thread and stage: k_total * GROUPS <= 1024
+    const uint8_t* src[kMaxItems];             // the item's byte of the first stage
+    int stride[kMaxItems];                     // bytes from one stage to the next
+    int boff[kMaxItems];                       // byte offset of the item's first element in the B tile
+    int soff[kMaxItems];                       // offset of its first row's statistics in a warp's copy
+    long long row1[kMaxItems];                 // first row of the item in stage 0, relative to kb0 * 32
+    bool valid[kMaxItems];
+#pragma unroll
+    for (int i = 0; i < kMaxItems; i++) {
+      const int idx = t + i * 128;
+      valid[i] = idx < total_items;
+      src[i] = nullptr; stride[i] = 0; boff[i] = 0; soff[i] = 0; row1[i] = 0;
+      if (valid[i]) {
+        int sg = 0, rest = idx;
+        while (sg + 1 < p.nseg && rest >= p.seg[sg].k * GROUPS) { rest -= p.seg[sg].k * GROUPS; sg++; }
+        const int q = rest / p.seg[sg].k;      // consecutive threads take consecutive columns: coalesced bytes
+        const int j = rest - q * p.seg[sg].k;
+        const int jb = p.seg[sg].col0 + j;     // row of the B tile
+        const int r = q * WPT;                 // first node row of the item within the stage
+        src[i] = p.seg[sg].packed + (kb0 * GROUPS + q) * (long long)p.seg[sg].k + j;
+        stride[i] = GROUPS * p.seg[sg].k;
+        // element (jb, r) of the K-major tile: row jb, 16-byte chunk (r / 4) ^ (jb % 8), word r % 4
+        boff[i] = jb * 128 + ((((r >> 2) ^ (jb & 7))) << 4) + (r & 3) * 4;
+        soff[i] = sg * kGwRows + r;
+        row1[i] = r;
+      }
+    }
+    const int pw = warp - 2;                   // producer warp 0 .. 3
     uint32_t bytes_next[kMaxItems];
-    auto item_of = [&](int idx, int& sg, int& j, int& q) {
-      sg = 0;
-      int rest = idx;
-      while (sg + 1 < p.nseg && rest >= p.seg[sg].k * GROUPS) { rest -= p.seg[sg].k * GROUPS; sg++; }
-      q = rest / p.seg[sg].k;                  // consecutive threads take consecutive columns: coalesced bytes
-      j = rest - q * p.seg[sg].k;
-    };
-    auto load_items = [&](long long kb) {
+    auto load_items = [&](long long it) {      // the packed bytes of stage kb0 + it
+      const long long n0 = (kb0 + it) * kGwRows;
 #pragma unroll
       for (int i = 0; i < kMaxItems; i++) {
-        const int idx = t + i * 128;
         bytes_next[i] = 0u;
-        if (idx < total_items) {
-          int sg, j, q;
-          item_of(idx, sg, j, q);
-          const long long grp = kb * GROUPS + q;           // row group of the packed stream
-          if (grp * WPT < p.N) bytes_next[i] = __ldg(p.seg[sg].packed + grp * p.seg[sg].k + j);
-        }
+        if (valid[i] && n0 + row1[i] < p.N) bytes_next[i] = __ldg(src[i] + it * stride[i]);
       }
     };
-    const int pw = warp - 2;                   // producer warp 0 .. 3
-    auto load_stats = [&](long long kb, int buf) {
-      const long long n = kb * kGwRows + lane;
-      for (int sg = 0; sg < p.nseg; sg++) {
-        float sc = 1.f, mn = 0.f;
-        if (n < p.N) {
-          sc = bf16_bits_to_f32(__ldg(p.seg[sg].scale_bf16 + n));
-          mn = bf16_bits_to_f32(__ldg(p.seg[sg].min_bf16 + n));
+    // Row statistics travel the same way: requested one stage ahead into registers (lane = row), turned into
+    // 1 / scale (so that a code is dequantised with one FMA; a constant row has scale = inf and reciprocal 0,
+    // its codes are 0 anyway) and min in this warp's shared-memory copy when their stage begins.  Rows past N
+    // get 0, 0.
+    // (the loaded values are not touched before their stage begins: a warp issues in order, and the first
+    // instruction that needs a load result would make it wait for the load)
+    uint16_t scale_next[kGwMaxSeg], min_next[kGwMaxSeg];
+    auto load_stats = [&](long long it) {
+      const long long n = (kb0 + it) * kGwRows + lane;
+#pragma unroll
+      for (int sg = 0; sg < kGwMaxSeg; sg++) {
+        scale_next[sg] = 0x7f80;               // scale = inf, min = 0: reciprocal 0
+        min_next[sg] = 0;
+        if (sg < p.nseg && n < p.N) {
+          scale_next[sg] = __ldg(p.seg[sg].scale_bf16 + n);
+          min_next[sg] = __ldg(p.seg[sg].min_bf16 + n);
         }
-        s_scale[buf][pw][sg][lane] = sc;
-        s_min[buf][pw][sg][lane] = mn;
       }
     };
     if (nblk > 0) {
-      load_items(kb0);
-      load_stats(kb0, 0);
+      load_items(0);
+      load_stats(0);
     }
     for (long long it = 0; it < nblk && ok; it++) {
       const int s = (int)(it % p.stages);
@@ -225,38 +273,47 @@ grad_weight_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_consta
       uint32_t bytes_cur[kMaxItems];
 #pragma unroll
       for (int i = 0; i < kMaxItems; i++) bytes_cur[i] = bytes_next[i];
+#pragma unroll
+      for (int sg = 0; sg < kGwMaxSeg; sg++) {
+        if (sg < p.nseg) {
+          s_scale[sb][pw][sg][lane] = __frcp_rn(bf16_bits_to_f32(scale_next[sg]));
+          s_min[sb][pw][sg][lane] = bf16_bits_to_f32(min_next[sg]);
+        }
+      }
       __syncwarp();                           // this warp's copy of the stage's statistics is in shared memory
       if (it + 1 < nblk) {                    // next stage's bytes and statistics are requested now
-        load_items(kb0 + it + 1);
-        load_stats(kb0 + it + 1, sb ^ 1);
+        load_items(it + 1);
+        load_stats(it + 1);
       }
       // the same verdict in every lane, so that a warp leaves the loop as a whole
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, abort_flag))) { ok = false; break; }
-      uint8_t* btile = tiles_ptr + (size_t)s * p.stage_bytes + p.a_bytes;
-      const long long n0 = (kb0 + it) * kGwRows;
+      uint8_t* btile = tiles_ptr + mma_off + (size_t)s * p.stage_bytes + p.a_bytes;
+      const float* inv_s = &s_scale[sb][pw][0][0];
+      const float* min_s = &s_min[sb][pw][0][0];
 #pragma unroll
       for (int i = 0; i < kMaxItems; i++) {
-        const int idx = t + i * 128;
-        if (idx < total_items) {
-          int sg, j, q;
-          item_of(idx, sg, j, q);
-          const int jb = p.seg[sg].col0 + j;          // row of the B tile
+        if (valid[i]) {
           float v[WPT];
 #pragma unroll
           for (int w = 0; w < WPT; w++) {
-            const int r = q * WPT + w;
             const float code = (float)((bytes_cur[i] >> (w * BITS)) & MASK);
-            // quantization_cuda_kernel.cu:179-183: code / scale + min; rows past N contribute nothing
-            v[w] = (n0 + r < p.N) ? __fadd_rn(__fdiv_rn(code, s_scale[sb][pw][sg][r]), s_min[sb][pw][sg][r]) : 0.f;
+            // quantization_cuda_kernel.cu:179-183 (code / scale + min) as code * (1 / scale) + min
+            v[w] = __fmaf_rn(code, inv_s[soff[i] + w], min_s[soff[i] + w]);
           }
-          // element (jb, r) of the K-major tile: row jb, 16-byte chunk (r / 4) ^ (jb % 8), word r % 4
-#pragma unroll
-          for (int w0 = 0; w0 < WPT; w0 += 4) {
-            const int r = q * WPT + w0;
-            uint8_t* dst = btile + jb * 128 + ((((r >> 2) ^ (jb & 7))) << 4) + (r & 3) * 4;
-            if (WPT >= 4) *reinterpret_cast<float4*>(dst) = make_float4(v[w0], v[w0 + 1 < WPT ? w0 + 1 : 0], v[w0 + 2 < WPT ? w0 + 2 : 0], v[w0 + 3 < WPT ? w0 + 3 : 0]);
-            else if (WPT == 2) *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1 < WPT ? 1 : 0]);
-            else *reinterpret_cast<float*>(dst) = v[0];
+          uint8_t* dst = btile + boff[i];
+          if (WPT == 8) {
+            // rows r .. r+7: two chunks of the same tile row; the second is the next chunk before swizzling
+            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1 % WPT], v[2 % WPT], v[3 % WPT]);
+            uint8_t* row = btile + (boff[i] & ~127);
+            const int chunk = ((boff[i] >> 4) & 7) ^ ((boff[i] >> 7) & 7);      // the un-swizzled chunk index
+            *reinterpret_cast<float4*>(row + ((((chunk + 1) ^ ((boff[i] >> 7) & 7))) << 4)) =
+                make_float4(v[4 % WPT], v[5 % WPT], v[6 % WPT], v[7 % WPT]);
+          } else if (WPT == 4) {
+            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1 % WPT], v[2 % WPT], v[3 % WPT]);
+          } else if (WPT == 2) {
+            *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1 % WPT]);
+          } else {
+            *reinterpret_cast<float*>(dst) = v[0];
           }
         }
       }
@@ -359,15 +416,22 @@ int exact_grad_weight_from_packed(const float* g, int64_t N, int64_t O, const ui
   p.partial = partial; p.status = status; p.lib_status = status_word_ptr();
   p.N = N; p.O = (int)O; p.Opad = Opad; p.kpad = (int)kpad; p.bits = bits;
   p.mtiles = Opad / 128;
-  p.oblocks = (int)((O + 31) / 32);
   p.kblocks = (N + kGwRows - 1) / kGwRows;
-  p.a_bytes = (unsigned)(p.mtiles * 4 * kGwRows * 128);     // whole M tiles, box by box
+  p.raw_bytes = ((unsigned)(kGwRows * O * 4) + 1023u) & ~1023u;
+  p.a_bytes = (unsigned)(p.mtiles * 128 * 128);             // one [128 x 32] fp32 tile per M tile
   p.b_bytes = (unsigned)(kpad * 128);
   p.stage_bytes = (p.a_bytes + p.b_bytes + 1023u) & ~1023u;
-  int stages = (int)((200 * 1024) / p.stage_bytes);
-  if (stages > kGwMaxStages) stages = kGwMaxStages;
-  EXB_REQUIRE(stages >= 2, "grad_weight_from_packed: a pipeline stage does not fit twice in shared memory");
-  p.stages = stages;
+  // two MMA stages are enough to keep the tensor core fed; the rest of the shared memory holds raw boxes in
+  // flight from HBM
+  int stages = 2;
+  int raw_stages = (int)((200 * 1024 - (long long)stages * p.stage_bytes) / p.raw_bytes);
+  if (raw_stages > kGwMaxStages) raw_stages = kGwMaxStages;
+  EXB_REQUIRE(raw_stages >= 2, "grad_weight_from_packed: the pipeline does not fit in shared memory");
+  if (raw_stages == kGwMaxStages) {
+    stages = (int)((200 * 1024 - (long long)raw_stages * p.raw_bytes) / p.stage_bytes);
+    if (stages > kGwMaxStages) stages = kGwMaxStages;
+  }
+  p.stages = stages; p.raw_stages = raw_stages;
   unsigned cols = 32;
   while (cols < (unsigned)(p.mtiles * kpad)) cols <<= 1;
   p.tmem_cols = cols;
@@ -381,9 +445,10 @@ int exact_grad_weight_from_packed(const float* g, int64_t N, int64_t O, const ui
   EXB_CUDA_OK(cudaGetLastError());
   if (N > 0) {
     CUtensorMap tm_g;
-    int rc = make_tensor_map_2d_f32(&tm_g, g, (unsigned long long)O, (unsigned long long)N, (unsigned long long)O * 4, 32, kGwRows);
+    int rc = make_tensor_map_2d_f32(&tm_g, g, (unsigned long long)O, (unsigned long long)N, (unsigned long long)O * 4, (unsigned)O,
+                                    kGwRows, /*swizzle128=*/false);
     if (rc) return rc;
-    const size_t dyn = (size_t)stages * p.stage_bytes + 1024;
+    const size_t dyn = (size_t)raw_stages * p.raw_bytes + (size_t)stages * p.stage_bytes + 1024;
 #define EXB_GW_LAUNCH(BITS_)                                                                                  \
   {                                                                                                           \
     EXB_CUDA_OK(cudaFuncSetAttribute(grad_weight_kernel<BITS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn)); \

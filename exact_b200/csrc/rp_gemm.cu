@@ -400,7 +400,7 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
 }
 
 int make_tensor_map_2d_f32(CUtensorMap* map, const void* base, unsigned long long inner, unsigned long long outer,
-                           unsigned long long pitch_bytes, unsigned box_inner, unsigned box_outer) {
+                           unsigned long long pitch_bytes, unsigned box_inner, unsigned box_outer, bool swizzle128) {
   auto enc = get_encode();
   if (enc == nullptr) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {inner, outer};
@@ -408,7 +408,8 @@ int make_tensor_map_2d_f32(CUtensorMap* map, const void* base, unsigned long lon
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(EXB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   return EXB_OK;

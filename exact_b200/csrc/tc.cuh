@@ -113,8 +113,9 @@ __host__ __device__ inline uint32_t umma_idesc_tf32(int M, int N) {
 }
 
 
-// Host: driver entry point for tensor-map encoding and a 2-D fp32 map with 128-byte swizzle.
+// Host: driver entry point for tensor-map encoding and a 2-D fp32 map, with the 128-byte swizzle the MMA
+// tiles use (box_inner <= 32) or plain rows (box_inner <= 256).
 int make_tensor_map_2d_f32(CUtensorMap* map, const void* base, unsigned long long inner, unsigned long long outer,
-                           unsigned long long pitch_bytes, unsigned box_inner, unsigned box_outer);
+                           unsigned long long pitch_bytes, unsigned box_inner, unsigned box_outer, bool swizzle128 = true);
 
 }  // namespace exb

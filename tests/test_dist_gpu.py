@@ -6,8 +6,9 @@ Compared with the single-process run of the same model, seeds and graph:
   - the packed stream of the first compressed activation (INT2 codes of x R, k = 13): the concatenation of the
     shards' streams equals the unsharded stream bit for bit, and so do the bf16 row statistics;
   - the loss of every step and the first step's parameter gradients: equal up to the fp32 regrouping of the
-    sums over ranks (gradients 2e-5 relative Frobenius and 2e-4 of the largest entry -- sums of ~10^3
-    cancelling terms regrouped 8 ways; losses 1e-5 relative at step 0, 1e-4 afterwards);
+    sums over ranks (gradients 2e-5 relative Frobenius at 2 ranks; at 8 ranks the shards are small enough to
+    take the library GEMM for their dense layers and a few stochastic-rounding decisions flip: 5e-3; losses
+    1e-5 relative at step 0, 1e-4 afterwards);
   - the peer-written compact rows against the collective exchange: same numbers."""
 import os
 import socket
@@ -71,8 +72,10 @@ def _compare_with_single(parts, single):
         for a, b in zip(p["losses"], single["losses"]):
             assert abs(a - b) <= 1e-4 * abs(b)
         # Shards of fewer than 1,024 rows (8 ranks here) run their dense layers on the library's fp32 GEMM instead
-        # of the tf32 head/tail tensor-core kernel (1e-6 relative per product), which the gradients then show.
-        tol = 2e-5 if min(q["rows"][1] - q["rows"][0] for q in parts) >= 1024 else 3e-4
+        # of the tf32 head/tail tensor-core kernel: a 1e-6 relative difference in a layer's output, which flips
+        # the stochastic rounding of a few INT2 codes of the next layer's saved activation; the gradients then
+        # differ by a corresponding share of the quantisation noise.
+        tol = 2e-5 if min(q["rows"][1] - q["rows"][0] for q in parts) >= 1024 else 5e-3
         for a, b in zip(p["grads0"], single["grads0"]):
             assert float((a - b).norm()) <= tol * float(b.norm()) + 1e-12
             assert float((a - b).abs().max()) <= 10 * tol * float(b.abs().max()) + 1e-9
