@@ -200,10 +200,12 @@ def run_b200(args):
     del full
     torch.cuda.empty_cache()
     g = torch.Generator().manual_seed(1)
-    # features live in pinned host memory (the end-to-end leg copies them in every step)
+    # features live in pinned host memory (the end-to-end leg copies them in every step); every rank draws the
+    # whole matrix from the same seed and keeps its rows, so that every world size trains on the same data
     x_host = torch.empty((r1 - r0, c["feats"]), dtype=torch.float32).pin_memory()
-    gd = torch.Generator(device=dev).manual_seed(1 + rank)
-    x_dev = torch.randn((r1 - r0, c["feats"]), device=dev, generator=gd)
+    gd = torch.Generator(device=dev).manual_seed(1)
+    x_dev = torch.randn((n, c["feats"]), device=dev, generator=gd)[r0:r1].clone()
+    torch.cuda.empty_cache()
     x_host.copy_(x_dev)
     y = torch.randint(c["classes"], (n,), generator=g)[r0:r1].to(dev)
     torch.manual_seed(0)
@@ -327,7 +329,9 @@ def run_b200(args):
     if rank == 0 and not args.no_kernels:
         kern = kernel_bandwidths(torch, Q, _lib, dev, hbm_peak, workload_shape=(r1 - r0, c["hidden"]))
 
+    exchange = "none"
     if world > 1:
+        exchange = adj.describe_exchange() + ", input features exchanged every step"
         adj.close()
         dist.barrier()
         dist.destroy_process_group()
@@ -344,11 +348,7 @@ def run_b200(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(c, n), "nodes": n, "directed_edges": nnz, "parallelism": f"rows/{world}",
                    "activations": "uncompressed (comparison run)" if args.no_compress else "compressed",
-                   "exchange": "none" if world == 1 else (
-                       ("dense rows" if args.dense_gather else
-                        ("compact rows written into the peers' buffers" if getattr(adj, "_peers", None) else
-                         "zero-compacted rows through the collective library"))
-                       + ", input features exchanged every step"),
+                   "exchange": exchange,
                    "l2": "inputs larger than L2" if n * c["hidden"] * 4 > 126e6 else "working set fits L2",
                    "setup_s": round(setup_s, 1)},
         "e2e": {"value": round(args.steps / (ms_e2e * 1e-3), 4), "unit": "epoch/s",

@@ -48,6 +48,8 @@ SIGNATURES = {
     "exact_crows_slot_bytes": (c_i64, [c_i64]),
     "exact_crows_pack": (c_int, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_i64, ctypes.POINTER(c_ptr), c_int, c_ptr, c_ptr]),
     "exact_crows_unpack": (c_int, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_i64, c_ptr]),
+    "exact_cols_scatter": (c_int, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_i64, c_i64, ctypes.POINTER(c_ptr), c_int, c_ptr]),
+    "exact_rows_scatter": (c_int, [c_ptr, c_i64, c_i64, c_i64, c_i64, c_i64, ctypes.POINTER(c_ptr), c_int, c_ptr]),
     "exact_peer_alloc": (c_int, [c_i64, ctypes.POINTER(c_ptr)]),
     "exact_peer_free": (c_int, [c_ptr]),
     "exact_peer_export": (c_int, [c_ptr, c_ptr]),

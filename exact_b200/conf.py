@@ -58,6 +58,10 @@ class QuantizationConfig:
         # of ReLU + dropout and gradients that passed their masks are.  Same dense rows bit for bit.
         self.compact_operand = True
         self.compact_operand_max_density = 0.5
+        # Row-sharded runs: aggregate feature-parallel (every rank multiplies the whole adjacency with a column
+        # slice of the operand; two all-to-all exchanges written into the peers' buffers) instead of gathering
+        # all rows of the operand on every rank.  Needs peer_exchange; per-row sums are then regrouped.
+        self.column_split_aggregation = True
         # Row shards write their compact rows straight into every peer's buffer (plain stores over NVLink,
         # buffers mapped with CUDA IPC) instead of going through a collective; off, or when the mapping
         # fails, the collective-library exchange is used.

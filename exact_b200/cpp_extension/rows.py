@@ -103,6 +103,28 @@ def crows_unpack(cr, n=None, row0=0, out=None):
     return out[:n]
 
 
+def cols_scatter(x, rowscale, row0, Kp, dst_ptrs):
+    """Column slice q of the rows of x [n, K] (times rowscale[:, None]) into rows row0 .. row0 + n - 1 of the
+    [*, Kp] buffer at dst_ptrs[q], for every q (first exchange of the feature-parallel aggregation)."""
+    n, K = x.shape
+    if rowscale is not None:
+        rowscale = rowscale.reshape(-1)
+        assert rowscale.dtype == torch.float32 and rowscale.numel() == n and rowscale.is_contiguous()
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    _lib.invoke("exact_cols_scatter", 4 * n * K + 4 * n * Kp * len(dst_ptrs), _lib.ptr(x), n, K, x.stride(0) if n else K,
+                _lib.ptr(rowscale), row0, Kp, arr, len(dst_ptrs), _lib.stream_ptr(), device=x.device)
+
+
+def rows_scatter(y, shard, col0, ldd, dst_ptrs):
+    """Row block p of y [n_total, Kp] into columns col0 .. col0 + Kp - 1 of the [shard, ldd] buffer at
+    dst_ptrs[p], for every p (second exchange of the feature-parallel aggregation)."""
+    assert y.dtype == torch.float32 and y.is_contiguous()
+    n_total, Kp = y.shape
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    _lib.invoke("exact_rows_scatter", 8 * n_total * Kp, _lib.ptr(y), n_total, Kp, shard, col0, ldd, arr, len(dst_ptrs),
+                _lib.stream_ptr(), device=y.device)
+
+
 def _check(x):
     if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1):
         raise RuntimeError("rows: expected a CUDA fp32 matrix with unit column stride")

@@ -216,24 +216,26 @@ __global__ void __launch_bounds__(128) spmm_long_reduce_kernel(const __grid_cons
   }
 }
 
-// Two edges per load instruction: lanes 0-15 gather 64 columns (16 x float4) of the even entries of the
-// staged edge list, lanes 16-31 of the odd entries; the two partial sums are added at the end.  For
-// operands far larger than L2 the narrow column tile keeps four times more source rows cached per pass
-// than a 256-column tile, and for K <= 64 it keeps most lanes busy.  The sum of a row is formed as
-// (even edges) + (odd edges), so it differs from the strict edge order of spmm_csr_kernel by fp32
-// reassociation.
-template <typename IdxT, bool HAS_VAL, int MODE>
-__global__ void __launch_bounds__(kSpmmWarps * 32) spmm_csr_pair_kernel(const __grid_constant__ SpmmParams p) {
+// Several edges per load instruction for narrow operands: a group of LPE lanes (16, 8 or 4) gathers 4 * LPE
+// columns (LPE x float4) of one edge, so the 32 / LPE groups of a warp take that many consecutive entries of
+// the staged edge list at once, each keeping its own partial sum; the partial sums are added at the end.  For
+// operands far larger than L2 the narrow column tile keeps more source rows cached per pass than a wide one,
+// and for K <= 64 it keeps the lanes busy (column slices of 16 to 64 columns are what a rank multiplies in
+// the feature-parallel aggregation).  The sum of a row is formed from interleaved partial sums, so it differs
+// from the strict edge order of spmm_csr_kernel by fp32 reassociation.
+template <typename IdxT, bool HAS_VAL, int MODE, int LPE>
+__global__ void __launch_bounds__(kSpmmWarps * 32) spmm_csr_multi_kernel(const __grid_constant__ SpmmParams p) {
   __shared__ uint32_t s_idx[kSpmmWarps][32];
   __shared__ float s_val[kSpmmWarps][32];
-  constexpr int kPairs = 8;   // pairs of edges in flight
+  constexpr int kGroups = 32 / LPE;   // edges per load instruction
+  constexpr int kDepth = 8;           // load instructions in flight
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int half = lane >> 4, hl = lane & 15;
+  const int grp = lane / LPE, hl = lane % LPE;
   const long long unit = (long long)blockIdx.x * kSpmmWarps + warp;
   const IdxT* __restrict__ rowptr = reinterpret_cast<const IdxT*>(p.rowptr);
   const IdxT* __restrict__ col = reinterpret_cast<const IdxT*>(p.col);
   const long long K = p.K;
-  const long long coff = ((long long)blockIdx.y * 16 + hl) * 4;
+  const long long coff = ((long long)blockIdx.y * LPE + hl) * 4;
   const bool cvalid = coff < K;
 
   long long begin, end;
@@ -270,19 +272,21 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_csr_pair_kernel(const __
     if (HAS_VAL) sval[lane] = v;
     __syncwarp();
     const int cnt = (end - base) < 32 ? (int)(end - base) : 32;
-    for (int t0 = 0; 2 * t0 < cnt; t0 += kPairs) {
-      float4 m[kPairs];
-      float w[kPairs];
+    for (int t0 = 0; kGroups * t0 < cnt; t0 += kDepth) {
+      float4 m[kDepth];
+      float w[kDepth];
 #pragma unroll
-      for (int u = 0; u < kPairs; u++) {
-        const int i = 2 * (t0 + u) + half;
+      for (int u = 0; u < kDepth; u++) {
+        const int i = kGroups * (t0 + u) + grp;
         m[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (HAS_VAL) w[u] = sval[i];
-        if (i < cnt && cvalid)
-          m[u] = __ldg(reinterpret_cast<const float4*>(mat0 + (unsigned long long)sidx[i] * row_bytes));
+        w[u] = 0.f;
+        if (i < cnt) {
+          if (HAS_VAL) w[u] = sval[i];
+          if (cvalid) m[u] = __ldg(reinterpret_cast<const float4*>(mat0 + (unsigned long long)sidx[i] * row_bytes));
+        }
       }
 #pragma unroll
-      for (int u = 0; u < kPairs; u++) {
+      for (int u = 0; u < kDepth; u++) {
         if (HAS_VAL) {
           acc[0] = __fmaf_rn(w[u], m[u].x, acc[0]); acc[1] = __fmaf_rn(w[u], m[u].y, acc[1]);
           acc[2] = __fmaf_rn(w[u], m[u].z, acc[2]); acc[3] = __fmaf_rn(w[u], m[u].w, acc[3]);
@@ -294,32 +298,41 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_csr_pair_kernel(const __
     }
   }
 #pragma unroll
-  for (int x = 0; x < 4; x++) acc[x] = __fadd_rn(acc[x], __shfl_xor_sync(0xffffffffu, acc[x], 16));
+  for (int off = 16; off >= LPE; off >>= 1) {
+#pragma unroll
+    for (int x = 0; x < 4; x++) acc[x] = __fadd_rn(acc[x], __shfl_xor_sync(0xffffffffu, acc[x], off));
+  }
   if (MODE == MODE_ROWS && p.mean) {
     const float dv = (float)(count > 0 ? count : 1);  // reducer.cuh:75-76
 #pragma unroll
     for (int x = 0; x < 4; x++) acc[x] = __fdiv_rn(acc[x], dv);
   }
-  if (half == 0 && cvalid) *reinterpret_cast<float4*>(dst + coff) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  if (grp == 0 && cvalid) *reinterpret_cast<float4*>(dst + coff) = make_float4(acc[0], acc[1], acc[2], acc[3]);
 }
 
-
-template <typename IdxT, bool HAS_VAL>
-static int launch_spmm_pair(const SpmmParams& p, cudaStream_t st) {
-  const unsigned gy = (unsigned)((p.K + 63) / 64);
+template <typename IdxT, bool HAS_VAL, int LPE>
+static int launch_spmm_multi(const SpmmParams& p, cudaStream_t st) {
+  const unsigned gy = (unsigned)((p.K + 4 * LPE - 1) / (4 * LPE));
   {
     dim3 grid((unsigned)((p.M + kSpmmWarps - 1) / kSpmmWarps), gy);
-    spmm_csr_pair_kernel<IdxT, HAS_VAL, MODE_ROWS><<<grid, kSpmmWarps * 32, 0, st>>>(p);
+    spmm_csr_multi_kernel<IdxT, HAS_VAL, MODE_ROWS, LPE><<<grid, kSpmmWarps * 32, 0, st>>>(p);
     EXB_CUDA_OK(cudaGetLastError());
   }
   if (p.n_items > 0) {
     dim3 grid((unsigned)((p.n_items + kSpmmWarps - 1) / kSpmmWarps), gy);
-    spmm_csr_pair_kernel<IdxT, HAS_VAL, MODE_ITEMS><<<grid, kSpmmWarps * 32, 0, st>>>(p);
+    spmm_csr_multi_kernel<IdxT, HAS_VAL, MODE_ITEMS, LPE><<<grid, kSpmmWarps * 32, 0, st>>>(p);
     EXB_CUDA_OK(cudaGetLastError());
     spmm_long_reduce_kernel<IdxT><<<(unsigned)p.n_long, 128, 0, st>>>(p);
     EXB_CUDA_OK(cudaGetLastError());
   }
   return EXB_OK;
+}
+
+template <typename IdxT, bool HAS_VAL>
+static int launch_spmm_pair(const SpmmParams& p, cudaStream_t st) {
+  if (p.K <= 16) return launch_spmm_multi<IdxT, HAS_VAL, 4>(p, st);
+  if (p.K <= 32) return launch_spmm_multi<IdxT, HAS_VAL, 8>(p, st);
+  return launch_spmm_multi<IdxT, HAS_VAL, 16>(p, st);
 }
 
 template <typename IdxT, int VEC, int KVT, bool HAS_VAL, bool FULL>

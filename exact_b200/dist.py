@@ -76,6 +76,17 @@ class PeerBuffers:
                 self._imported.append(p)
                 self.ptrs[r] = p.value
 
+    def local_tensor(self):
+        """This rank's buffer as a uint8 tensor (no copy; the memory stays owned by this object)."""
+        class _Raw:
+            pass
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (self.nbytes,), "typestr": "|u1", "data": (self.local.value, False),
+                                        "version": 2}
+        t = torch.as_tensor(raw, device=self.device)
+        t._exact_owner = self     # keep the allocation alive as long as the view
+        return t
+
     def close(self):
         """Unmap the peers' buffers, wait for every rank to have done so, free this rank's own."""
         lib = _lib.load()
@@ -114,6 +125,18 @@ class ShardedSparseTensor:
         self.t_rowptr = (t_ptr[r0:r1 + 1] - f0).to(index_dtype).contiguous()
         self.t_col = t_col[f0:f1].to(index_dtype).contiguous()
         self.t_w = None if t_w is None else t_w[f0:f1].contiguous()
+        # the whole adjacency and its transpose (feature-parallel aggregation: every rank multiplies all rows
+        # with its column slice)
+        self.full_rowptr = rowptr.to(index_dtype).contiguous()
+        self.full_col = col.to(index_dtype).contiguous()
+        self.full_value = None if val is None else val.contiguous()
+        self.full_t = {self.reduce: (t_ptr.to(index_dtype).contiguous(), t_col.to(index_dtype).contiguous(),
+                                     None if t_w is None else t_w.contiguous())}
+        if self.reduce != "sum" and val is None:
+            # the transposed mean with pre-scaled rows needs no weights: same structure, no values
+            self.full_t["sum"] = (self.full_t[self.reduce][0], self.full_t[self.reduce][1], None)
+        self._col_bufs = {}         # (kind, width) -> [PeerBuffers, PeerBuffers] of the feature-parallel exchange
+        self._col_turn = {}
         self._gather_buf = {}
         self._dense_streak = {}     # tag -> calls left before compaction is tried again after a dense operand
         self._const_gather = None   # (tensor, version, gathered): input features do not change between epochs
@@ -152,6 +175,84 @@ class ShardedSparseTensor:
         self._peer_turn[K] = turn + 1
         return pair[turn & 1]
 
+    def _column_buffers(self, kind, width, nbytes, device):
+        """Double-buffered peer buffers of one exchange kind and width, or None when the ranks cannot map each
+        other's memory (see _peer_buffers for why there are two)."""
+        if self._peers_failed or not (config.peer_exchange and device.type == "cuda" and dist.is_initialized()):
+            return None
+        key = (kind, width)
+        pair = self._col_bufs.get(key)
+        if pair is None:
+            ok, made = 1, []
+            try:
+                for _ in range(2):
+                    made.append(PeerBuffers(nbytes, self.rank, self.world, self.group, device))
+            except Exception as e:   # every rank must learn of it: agree below
+                ok = 0
+                warnings.warn(f"peer buffers unavailable ({e}); using the collective exchange")
+            flag = torch.tensor([ok], dtype=torch.int32, device=device)
+            all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            if int(flag.item()) == 0:
+                self._peers_failed = True
+                return None
+            pair = self._col_bufs[key] = made
+            self._col_turn[key] = 0
+        turn = self._col_turn[key]
+        self._col_turn[key] = turn + 1
+        return pair[turn & 1]
+
+    def _order_peer_stores(self, device):
+        """All ranks' stores into each other's buffers, enqueued so far, happen before anything enqueued after."""
+        if self._sync is None:
+            self._sync = torch.zeros(1, dtype=torch.int32, device=device)
+        all_reduce(self._sync, group=self.group)
+
+    def aggregate(self, x_local, reduce, transposed=False, rowscale=None, unweighted=False):
+        """reduce(A, x) (or A^T x when `transposed`: spmm.cc:70-77, 128-137) for this rank's rows, with x given
+        by rows: [local_rows, K] on every rank.  Feature-parallel: every rank receives a slice of Kp = ceil(K / P)
+        columns of ALL rows (each rank stores its rows' slices into the peers' buffers), multiplies the whole
+        adjacency with it, and stores each row block of its result slice into the owner's output buffer.  Two
+        all-to-all exchanges of N K / P elements per rank instead of an all-gather of N K (P - 1) / P, equal work
+        on every rank whatever the degree distribution, and gathers over a P times narrower operand.  Per-row
+        sums are regrouped (several edges per load instruction on the narrow slices).  Returns None when the
+        ranks cannot write each other's memory (the caller takes the row-split route)."""
+        n_loc, K = x_local.shape
+        dev = x_local.device
+        P, S, N = self.world, self.shard, self.n_global
+        if not (config.column_split_aggregation and x_local.dtype == torch.float32 and K % 4 == 0):
+            return None
+        Kp = ((K + P - 1) // P + 3) // 4 * 4
+        inb = self._column_buffers("in", Kp, P * S * Kp * 4, dev)
+        if inb is None:
+            return None
+        outb = self._column_buffers("out", Kp, S * P * Kp * 4, dev)
+        if outb is None:
+            return None
+        x_local = x_local if (x_local.stride(1) == 1 and x_local.stride(0) % 4 == 0 and x_local.data_ptr() % 16 == 0) \
+            else x_local.contiguous()
+        ext_rows.cols_scatter(x_local, rowscale, self.row_start, Kp, inb.ptrs)
+        self._order_peer_stores(dev)
+        slice_all = inb.local_tensor().view(torch.float32).view(P * S, Kp)[:N]
+        if transposed:
+            # rows already scaled by 1 / deg (here or by the caller): A_mean^T g = A^T (D^-1 g), no edge weights
+            unweighted = unweighted or rowscale is not None
+            t_ptr, t_col, t_w = self.full_t["sum" if (unweighted and "sum" in self.full_t) else self.reduce]
+            y = ext_spmm._spmm(t_ptr, t_col, None if unweighted else t_w, slice_all, "sum", regroup=True)
+        else:
+            y = ext_spmm._spmm(self.full_rowptr, self.full_col, self.full_value, slice_all, reduce, regroup=True)
+        ext_rows.rows_scatter(y, S, self.rank * Kp, P * Kp, outb.ptrs)
+        self._order_peer_stores(dev)
+        out = outb.local_tensor().view(torch.float32).view(S, P * Kp)[:n_loc]
+        # the buffer is written again two aggregations of this width later: callers consume the result at once
+        return out if K == P * Kp else out[:, :K].contiguous()
+
+    def describe_exchange(self):
+        if self._col_bufs:
+            return "feature-parallel aggregation: two all-to-all exchanges written into the peers' buffers"
+        if self._peers:
+            return "compact rows written into the peers' buffers"
+        return "rows through the collective library" + (" (zero-compacted)" if config.compact_gather else "")
+
     def exchange(self, x_local, tag, rowscale=None):
         """Every row of the [local_rows, K] operand (times rowscale[:, None]) as a dense [n_global, K] matrix in
         local HBM.  When the operand is mostly zeros and the ranks can write each other's memory, each rank
@@ -185,10 +286,10 @@ class ShardedSparseTensor:
         return self.gather(x_local.contiguous(), tag, try_compact=(mode == "compact"))
 
     def close(self):
-        for pair in self._peers.values():
+        for pair in list(self._peers.values()) + list(self._col_bufs.values()):
             for pb in pair:
                 pb.close()
-        self._peers = {}
+        self._peers, self._col_bufs = {}, {}
 
     @property
     def local_rows(self):

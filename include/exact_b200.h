@@ -33,10 +33,10 @@ extern "C" {
 
 enum { EXACT_DTYPE_F32 = 0, EXACT_DTYPE_BF16 = 1 };
 enum { EXACT_REDUCE_SUM = 0, EXACT_REDUCE_MEAN = 1 };
-/* OR-ed into `reduce`: the caller accepts a per-row sum that is regrouped (two interleaved partial sums
- * instead of strict edge order; same terms, fp32 reassociation).  Lets operands of at most 64 columns use a
- * kernel that gathers two edges per load instruction.  Without it every row up to the long-row threshold
- * is summed in edge order, bit-identical to the reference kernel. */
+/* OR-ed into `reduce`: the caller accepts a per-row sum that is regrouped (2, 4 or 8 interleaved partial sums
+ * for operands of at most 64, 32 or 16 columns instead of strict edge order; same terms, fp32 reassociation).
+ * Lets narrow operands use a kernel that gathers several edges per load instruction.  Without it every row up
+ * to the long-row threshold is summed in edge order, bit-identical to the reference kernel. */
 enum { EXACT_SPMM_REGROUP = 0x100 };
 
 /* Library version (major * 100 + minor) and the last error message of the calling thread. */
@@ -190,6 +190,22 @@ EXACT_API int exact_crows_pack(const float* x, int64_t n, int64_t K, int64_t ldx
                                void* const* dst, int n_dst, uint64_t* kept_total, void* stream);
 EXACT_API int exact_crows_unpack(const void* buf, int64_t n, int64_t K, int64_t row0, float* out, int64_t ldo,
                                  void* stream);
+
+/* The two exchanges of the feature-parallel aggregation of a row-sharded run (no counterpart in the reference).
+ * Between aggregations rank p holds rows [p * shard, (p + 1) * shard) with all K columns.  For out = A x the
+ * ranks switch to a column split and back:
+ *   exact_cols_scatter  x [n, K] fp32 (pitch ldx; K, ldx multiples of 4; 16-byte aligned), optionally times
+ *       rowscale[r]: dst[q][(row0 + r) * Kp + c] = x[r, q * Kp + c] for every rank q (columns past K: zero).
+ *       Rank q then owns columns [q Kp, (q + 1) Kp) of all rows and multiplies the whole adjacency with them.
+ *   exact_rows_scatter  y [n_total, Kp], this rank's column slice of the result:
+ *       dst[p][(row - p * shard) * ldd + col0 + c] = y[row, c] for the rows of block p (col0 = rank * Kp).
+ * dst: host array of n_dst (1..8) device pointers, one per rank, which may be peers' buffers (exact_peer_import):
+ * plain 16-byte stores over NVLink; the caller orders them before the readers (stream order, then a collective).
+ * Two all-to-all exchanges of N K / P elements per rank replace the all-gather of N K (P - 1) / P. */
+EXACT_API int exact_cols_scatter(const float* x, int64_t n, int64_t K, int64_t ldx, const float* rowscale, int64_t row0,
+                                 int64_t Kp, void* const* dst, int n_dst, void* stream);
+EXACT_API int exact_rows_scatter(const float* y, int64_t n_total, int64_t Kp, int64_t shard, int64_t col0, int64_t ldd,
+                                 void* const* dst, int n_dst, void* stream);
 
 /* Buffers that the ranks of a row-sharded run write into each other (one process per GPU, one node).  No
  * counterpart in the reference.  These are the only entry points that allocate or free device memory:

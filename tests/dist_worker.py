@@ -24,6 +24,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--peer", type=int, default=1)
     ap.add_argument("--compact", type=int, default=1)
+    ap.add_argument("--colsplit", type=int, default=1)
     a = ap.parse_args()
 
     import torch
@@ -44,6 +45,7 @@ def main():
     n = full.size(0)
     config.peer_exchange = bool(a.peer)
     config.compact_operand = bool(a.compact)
+    config.column_split_aggregation = bool(a.colsplit)
     config.cache_constant_gather = False
     if a.world > 1:
         adj = xdist.shard_graph(full, "mean", a.rank, a.world)
@@ -95,10 +97,11 @@ def main():
     form = getattr(adj, "_operand_form", None) if a.world > 1 else None
     if form is not None:
         forms = {k: (v[0], v[2]) for k, v in form.state.items()}
-    peers_used = bool(getattr(adj, "_peers", None))
+    peers_used = bool(getattr(adj, "_peers", None)) or bool(getattr(adj, "_col_bufs", None))
+    exchange = adj.describe_exchange() if a.world > 1 else "none"
     torch.save({"losses": losses, "grads0": grads0, "params": [p.detach().cpu() for p in params],
                 "packed": first["packed"].cpu()[:-1], "scale": first["scale"].cpu(), "min": first["min"].cpu(),
-                "rows": (r0, r1), "forms": forms, "peers_used": peers_used},
+                "rows": (r0, r1), "forms": forms, "peers_used": peers_used, "exchange": exchange},
                os.path.join(a.out, f"w{a.world}_{a.name}_r{a.rank}.pt"))
     if a.world > 1:
         adj.close()

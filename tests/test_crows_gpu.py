@@ -71,3 +71,31 @@ def test_unpack_into_a_larger_buffer_overwrites_stale_rows():
     got = R.crows_unpack(cr, n, out=out)
     assert got.data_ptr() == out.data_ptr() and np.array_equal(got.cpu().numpy(), x)
     assert float(out[n:].min()) == 7.0
+
+
+@pytest.mark.parametrize("n,K,P", [(1000, 256, 8), (999, 100, 8), (512, 48, 4), (300, 256, 2), (77, 100, 2)])
+def test_feature_parallel_exchange_kernels(n, K, P):
+    """exact_cols_scatter / exact_rows_scatter with all P "ranks" played on one device: column slices of every
+    shard's rows to every rank, then row blocks of every rank's slice back, reproduce the matrix (padding zero)."""
+    x = normal(n, K, 5)
+    shard = ((n + P - 1) // P + 7) // 8 * 8
+    Kp = ((K + P - 1) // P + 3) // 4 * 4
+    scale = (np.random.default_rng(6).random(n).astype(np.float32) + 0.5)
+    inb = [torch.full((P * shard, Kp), 7.0, device="cuda") for _ in range(P)]
+    outb = [torch.full((shard, P * Kp), 9.0, device="cuda") for _ in range(P)]
+    xt, st = t(x), t(scale)
+    for r in range(P):                      # rank r scatters its rows' column slices to everyone
+        r0, r1 = min(r * shard, n), min(r * shard + shard, n)
+        if r1 > r0:
+            R.cols_scatter(xt[r0:r1], st[r0:r1], r0, Kp, [b.data_ptr() for b in inb])
+    xs = (x * scale[:, None]).astype(np.float32)
+    padded = np.zeros((n, P * Kp), np.float32)
+    padded[:, :K] = xs
+    for q in range(P):
+        assert np.array_equal(inb[q][:n].cpu().numpy(), padded[:, q * Kp:(q + 1) * Kp])
+        assert float(inb[q][n:].min()) == 7.0 if n < P * shard else True
+    for q in range(P):                      # rank q sends the row blocks of its slice back to their owners
+        R.rows_scatter(inb[q][:n].contiguous(), shard, q * Kp, P * Kp, [b.data_ptr() for b in outb])
+    for r in range(P):
+        r0, r1 = min(r * shard, n), min(r * shard + shard, n)
+        assert np.array_equal(outb[r][:r1 - r0].cpu().numpy(), padded[r0:r1])

@@ -99,11 +99,12 @@ def test_qmatmul_forward_and_grad(reduce, with_values):
 
 @pytest.mark.parametrize("reduce", ["sum", "mean"])
 @pytest.mark.parametrize("with_values", [True, False])
-@pytest.mark.parametrize("K", [48, 64, 40, 16, 4])
+@pytest.mark.parametrize("K", [48, 64, 40, 32, 24, 16, 8, 4])
 def test_regrouped_sum_for_narrow_operands(K, with_values, reduce):
-    """EXACT_SPMM_REGROUP: operands of at most 64 columns gather two edges per load instruction and add
-    (even edges) + (odd edges); the result equals the edge-order sum up to fp32 reassociation, hub rows
-    (cut into pieces) and empty rows included.  Wider operands ignore the flag and stay bit-exact."""
+    """EXACT_SPMM_REGROUP: operands of at most 64 / 32 / 16 columns gather two / four / eight edges per load
+    instruction and add the interleaved partial sums; the result equals the edge-order sum up to fp32
+    reassociation, hub rows (cut into pieces) and empty rows included.  Wider operands ignore the flag and
+    stay bit-exact."""
     n = 4000
     rng = np.random.default_rng(11)
     hub = np.stack([np.zeros(1500, np.int64), rng.choice(n, 1500, replace=False)])
