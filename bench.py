@@ -281,7 +281,8 @@ def run_b200(args):
     torch.cuda.reset_peak_memory_stats(dev)
     timed_losses = []
     ms = timed(lambda: timed_losses.append(step(x_dev)), args.steps)
-    peak_mem = torch.cuda.max_memory_allocated(dev)
+    # torch's allocator plus the exchange buffers the library allocates itself for the peers to write into
+    peak_mem = torch.cuda.max_memory_allocated(dev) + xdist.PeerBuffers.peak_allocated_bytes
     loss_first = float(global_loss(timed_losses[0]).item())
     loss_last = float(global_loss(timed_losses[-1]).item())
     del timed_losses

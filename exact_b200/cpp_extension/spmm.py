@@ -113,30 +113,45 @@ def spmm_mean_fw(row, rowptr, col, value, rowcount, colptr, csr2csc, mat):
     return _spmm(rowptr, col, value, mat, "mean")
 
 
-def _value_grad_unsupported():
-    raise NotImplementedError("gradient with respect to edge values (spmm_value_bw) is not part of the "
-                              "GCN/GraphSAGE path: their adjacency values never require grad")
+def spmm_value_bw(row, rowptr, col, mat, grad, reduce):
+    """spmm.cc:20-24 -> spmm_cuda.cu:211-252: gradient with respect to the edge values, [nnz] fp32."""
+    if not (row.is_cuda and col.is_cuda and mat.is_cuda and grad.is_cuda):
+        raise RuntimeError("row, col, mat and grad must be CUDA tensors")
+    if mat.dtype != torch.float32 or grad.dtype != torch.float32 or mat.dim() != 2 or grad.dim() != 2:
+        raise RuntimeError("mat and grad must be float32 matrices")
+    if not (row.dtype == col.dtype == rowptr.dtype) or col.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("row, rowptr and col must all be int32 or all int64")
+    mat, grad = mat.contiguous(), grad.contiguous()
+    row, col, rowptr = row.contiguous(), col.contiguous(), rowptr.contiguous()
+    E, K = col.numel(), mat.size(1)
+    out = torch.empty(E, dtype=torch.float32, device=mat.device)
+    ib = 4 if col.dtype == torch.int32 else 8
+    _lib.invoke("exact_spmm_value_bw", E * (8 * K + 2 * ib + 4), _lib.ptr(row), _lib.ptr(rowptr), _lib.ptr(col), ib,
+                _lib.ptr(mat), _lib.ptr(grad), E, K, _lib.REDUCE[reduce], _lib.ptr(out), _lib.stream_ptr())
+    return out
 
 
 def spmm_sum_bw(row, rowptr, col, value, colptr, csr2csc, mat, grad_out, has_value, value_requires_grad,
                 mat_requires_grad, transposed=None):
     """spmm.cc:57-79.  `transposed` = (colptr, row[csr2csc], value[csr2csc]) when the caller caches it."""
+    grad_value = None
     if has_value and value_requires_grad:
-        _value_grad_unsupported()
+        grad_value = spmm_value_bw(row, rowptr, col, mat, grad_out, "sum")
     grad_mat = None
     if mat_requires_grad:
         if transposed is None:
             w = value.index_select(0, csr2csc) if has_value else None
             transposed = (colptr, row.index_select(0, csr2csc), w)
         grad_mat = _spmm(transposed[0], transposed[1], transposed[2], grad_out, "sum")
-    return None, grad_mat
+    return grad_value, grad_mat
 
 
 def spmm_mean_bw(row, rowptr, col, value, rowcount, colptr, csr2csc, mat, grad_out, has_value,
                  value_requires_grad, mat_requires_grad, transposed=None):
     """spmm.cc:115-139."""
+    grad_value = None
     if has_value and value_requires_grad:
-        _value_grad_unsupported()
+        grad_value = spmm_value_bw(row, rowptr, col, mat, grad_out, "mean")
     grad_mat = None
     if mat_requires_grad:
         if transposed is None:
@@ -145,4 +160,4 @@ def spmm_mean_bw(row, rowptr, col, value, rowcount, colptr, csr2csc, mat, grad_o
             w = value.index_select(0, csr2csc).div(cnt) if has_value else cnt.pow_(-1)
             transposed = (colptr, row_t, w)
         grad_mat = _spmm(transposed[0], transposed[1], transposed[2], grad_out, "sum")
-    return None, grad_mat
+    return grad_value, grad_mat

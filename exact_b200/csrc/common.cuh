@@ -145,6 +145,19 @@ __device__ __forceinline__ f32x2 noise16_to_unit(f32x2 one_plus) {
   return f2_fma(one_plus, f2_pack(128.f, 128.f), f2_pack(-127.99999237060546875f, -127.99999237060546875f));
 }
 
+// Byte k (0..3, may be a run-time value) of a Philox word -> the float 1 + h * 2^-23 (bits 0x3F8000:h), by one
+// byte permute; noise8_to_unit() turns those into (h + 0.5) * 2^-8 with one FMA:
+// (1 + h 2^-23) * 2^15 - (2^15 - 2^-9), exact.
+__device__ __forceinline__ float u8_to_1p(uint32_t w, uint32_t k) {
+  return __uint_as_float(__byte_perm(w, 0x3f800000u, 0x7640u + k));
+}
+__device__ __forceinline__ f32x2 noise8_to_unit(f32x2 one_plus) {
+  return f2_fma(one_plus, f2_pack(32768.f, 32768.f), f2_pack(-32767.998046875f, -32767.998046875f));
+}
+__device__ __forceinline__ float noise8_to_unit(float one_plus) {
+  return __fmaf_rn(one_plus, 32768.f, -32767.998046875f);
+}
+
 // NaN-propagating min/max (torch.min / torch.max semantics) and their warp-wide forms.  redux.sync on
 // f32 is an sm_100a instruction.
 __device__ __forceinline__ float min_nan(float a, float b) {

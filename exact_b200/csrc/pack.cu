@@ -128,11 +128,15 @@ __device__ __forceinline__ void quantize_rows(const PackParams& p, const TileCtx
 #pragma unroll
     for (int g = 0; g < GPT; g++) acc[g] = 0u;
 
-    uint32_t w[VEC][4];
+    // One Philox block per 8-row tile and PAIR of columns: its 16 bytes are the noise of rows 0..7 of the
+    // even and the odd column (byte 2 r + (column & 1)), 8 bits per element: u = (h + 0.5) / 256.
+    constexpr int NP = (VEC + 1) / 2;
+    uint32_t w[NP][4];
+    const uint32_t odd = (VEC == 1) ? (uint32_t)(col[v] & 1) : 0u;
     if (FAST || p.noise == nullptr) {
-      const unsigned long long q0 = (unsigned long long)(noise_tile * c.D + col[v]);
+      const unsigned long long q0 = (unsigned long long)(noise_tile * ((c.D + 1) >> 1) + (col[v] >> 1));
 #pragma unroll
-      for (int e = 0; e < VEC; e++) {
+      for (int e = 0; e < NP; e++) {
         const unsigned long long q = q0 + e;
         philox4x32_10((uint32_t)q, (uint32_t)(q >> 32), p.off_lo, p.off_hi, p.key, w[e]);
       }
@@ -154,9 +158,10 @@ __device__ __forceinline__ void quantize_rows(const PackParams& p, const TileCtx
             if (!FAST && nbase != nullptr) {
               u2 = f2_pack(un[e], un[(e + 1) % VEC]);
             } else {
-              const float f0 = (r & 1) ? u16_hi_to_1p(w[e][r >> 1]) : u16_lo_to_1p(w[e][r >> 1]);
-              const float f1 = (r & 1) ? u16_hi_to_1p(w[(e + 1) % VEC][r >> 1]) : u16_lo_to_1p(w[(e + 1) % VEC][r >> 1]);
-              u2 = noise16_to_unit(f2_pack(f0, f1));
+              // columns e (even) and e + 1 of this thread share the block w[e / 2]
+              const float f0 = u8_to_1p(w[e >> 1][r >> 1], (r & 1) * 2);
+              const float f1 = u8_to_1p(w[e >> 1][r >> 1], (r & 1) * 2 + 1);
+              u2 = noise8_to_unit(f2_pack(f0, f1));
             }
             const f32x2 a2 = f2_sub(f2_pack(xv[r][v][e], xv[r][v][(e + 1) % VEC]), mn2);
             f32x2 t2 = f2_add(f2_fma(a2, sc2, u2), neg_half);
@@ -174,7 +179,7 @@ __device__ __forceinline__ void quantize_rows(const PackParams& p, const TileCtx
           }
         } else {
           const float u = (!FAST && nbase != nullptr) ? un[0]
-                          : ((r & 1) ? u16_hi_to_unit(w[0][r >> 1]) : u16_lo_to_unit(w[0][r >> 1]));
+                          : noise8_to_unit(u8_to_1p(w[0][r >> 1], (r & 1) * 2 + odd));
           const float t = __fsub_rn(__fmaf_rn(__fsub_rn(xv[r][v][0], mn[r]), sc[r], u), 0.5f);
           code[0] = __float2uint_rn(t) & 0xffu;
         }
@@ -390,7 +395,7 @@ __global__ void __launch_bounds__(256) pack_given_stats_kernel(const __grid_cons
     const long long row0 = tile << 3;
     uint32_t w[4] = {0u, 0u, 0u, 0u};
     if (p.noise == nullptr) {
-      const unsigned long long q = (unsigned long long)(((row0 + p.row_offset) >> 3) * p.D + d);
+      const unsigned long long q = (unsigned long long)(((row0 + p.row_offset) >> 3) * ((p.D + 1) >> 1) + (d >> 1));
       philox4x32_10((uint32_t)q, (uint32_t)(q >> 32), p.off_lo, p.off_hi, p.key, w);
     }
     uint32_t acc[GPT];
@@ -403,7 +408,7 @@ __global__ void __launch_bounds__(256) pack_given_stats_kernel(const __grid_cons
         float xv[1];
         Ld<InT, 1>::load(x + n * p.D + d, xv);
         const float u = (p.noise != nullptr) ? __ldcs(p.noise + n * p.D + d)
-                        : ((r & 1) ? u16_hi_to_unit(w[r >> 1]) : u16_lo_to_unit(w[r >> 1]));
+                        : noise8_to_unit(u8_to_1p(w[r >> 1], (r & 1) * 2 + (uint32_t)(d & 1)));
         const float t = __fsub_rn(__fmaf_rn(__fsub_rn(xv[0], __ldg(p.mn_in + n)), __ldg(p.scale_in + n), u), 0.5f);
         const uint32_t code = (uint32_t)__float2int_rn(fmaxf(t, 0.f));  // quantization_cuda_kernel.cu:89
         acc[r / WPT] |= code << ((r % WPT) * BITS);

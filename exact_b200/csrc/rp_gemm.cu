@@ -75,12 +75,6 @@ struct RpParams {
 };
 
 // ---- the kernel -----------------------------------------------------------------------------------
-__device__ __forceinline__ void cp_async_piece(uint32_t dst, const void* src, int piece, uint32_t src_bytes) {
-  if (piece == 8)
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-  else
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 // Waits until at most n of this thread's most recent cp.async groups are still pending.
 __device__ __forceinline__ void cp_async_wait_pending(int n) {
@@ -218,16 +212,35 @@ rp_pack_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         const int s = it % p.stages;
         const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
         if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
-        const uint32_t dst0 = tiles_base + (uint32_t)s * p.stage_bytes;
         const int col = kb * kRpTileK + (cbytes >> 2);
         // a piece is inside the row or outside as a whole: 8-byte pieces are only used for even D
         const bool col_ok = col < p.D;
-        for (int r = rg; r < kRpTileM; r += rpp) {
-          const long long n = (long long)tile * kRpTileM + r;
-          const bool in = col_ok && n < p.N;
-          const uint32_t dst = dst0 + (uint32_t)(r * 128 + ((chunk ^ (r & 7)) << 4) + within);
-          const float* src = in ? p.x + n * p.D + col : p.x;
-          cp_async_piece(dst, src, p.piece, in ? (uint32_t)p.piece : 0u);   // src size 0: zero fill
+        // A producer warp has an SM sub-partition to itself, so the per-piece address arithmetic is kept to a
+        // few independent instructions: source and destination advance by constants from row to row.
+        const long long n0 = (long long)tile * kRpTileM + rg;
+        const float* src = p.x + n0 * p.D + col;
+        const long long src_step = (long long)rpp * p.D;
+        uint32_t dst_row = tiles_base + (uint32_t)s * p.stage_bytes + (uint32_t)(rg * 128 + within);
+        const long long rows_left = p.N - n0;     // rows n0, n0 + rpp, ... below N are real
+        const int passes = kRpTileM / rpp;        // 16 (8-byte pieces) or 32 (4-byte pieces)
+        if (p.piece == 8) {
+#pragma unroll 4
+          for (int i = 0; i < passes; i++) {
+            const bool in = col_ok && (long long)(i * rpp) < rows_left;
+            // rows advance by 8: the swizzle term (row % 8) is that of the first row
+            const uint32_t dst = dst_row + (uint32_t)(i * rpp * 128) + (uint32_t)((chunk ^ (rg & 7)) << 4);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(in ? src : p.x), "r"(in ? 8u : 0u) : "memory");
+            src += src_step;
+          }
+        } else {
+#pragma unroll 4
+          for (int i = 0; i < passes; i++) {
+            const int r = rg + i * rpp;
+            const bool in = col_ok && (long long)(i * rpp) < rows_left;
+            const uint32_t dst = dst_row + (uint32_t)(i * rpp * 128) + (uint32_t)((chunk ^ (r & 7)) << 4);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(in ? src : p.x), "r"(in ? 4u : 0u) : "memory");
+            src += src_step;
+          }
         }
         cp_async_commit();
         if (it >= p.lag) {

@@ -404,11 +404,61 @@ static int spmm_common(SpmmParams& p, int idx_bytes, int reduce, cudaStream_t st
   return p.val ? launch_spmm_vec<int64_t, true>(p, st) : launch_spmm_vec<int64_t, false>(p, st);
 }
 
+// Gradient with respect to the edge values (spmm_cuda.cu:172-209): one warp per edge,
+// out[e] = dot(mat[col[e], :], grad[row[e], :]) (/ max(row length, 1) for mean).  Lane l accumulates columns
+// l, l + 32, ... with one FMA each, then the lanes are added by the reference's shuffle-down tree, so the
+// value equals the reference's bit for bit.
+template <typename IdxT>
+__global__ void __launch_bounds__(256) spmm_value_bw_kernel(const IdxT* __restrict__ row, const IdxT* __restrict__ rowptr,
+                                                            const IdxT* __restrict__ col, const float* __restrict__ mat,
+                                                            const float* __restrict__ grad, long long E, long long K,
+                                                            int mean, float* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const long long e = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (e >= E) return;
+  const long long r = (long long)row[e], c = (long long)col[e];
+  const float* m = mat + c * K;
+  const float* g = grad + r * K;
+  float val = 0.f;
+  for (long long k = lane; k < K; k += 32) val = __fmaf_rn(__ldg(m + k), __ldg(g + k), val);
+#pragma unroll
+  for (int i = 16; i > 0; i >>= 1) val = __fadd_rn(val, __shfl_down_sync(0xffffffffu, val, i));
+  if (lane == 0) {
+    if (mean) {
+      const long long deg = (long long)rowptr[r + 1] - (long long)rowptr[r];
+      val = __fdiv_rn(val, (float)(deg > 1 ? deg : 1));
+    }
+    out[e] = val;
+  }
+}
+
 }  // namespace exb
 
 using namespace exb;
 
 extern "C" {
+
+int exact_spmm_value_bw(const void* row, const void* rowptr, const void* col, int idx_bytes, const float* mat,
+                        const float* grad, int64_t E, int64_t K, int reduce, float* out, void* stream) {
+  EXB_REQUIRE(idx_bytes == 4 || idx_bytes == 8, "spmm_value_bw: idx_bytes must be 4 or 8 (got %d)", idx_bytes);
+  EXB_REQUIRE(reduce == EXACT_REDUCE_SUM || reduce == EXACT_REDUCE_MEAN, "spmm_value_bw: reduce must be sum or mean");
+  EXB_REQUIRE(E >= 0 && K >= 0, "spmm_value_bw: negative shape");
+  if (E == 0) return EXB_OK;
+  EXB_REQUIRE(row && col && mat && grad && out && (reduce == EXACT_REDUCE_SUM || rowptr), "spmm_value_bw: null pointer");
+  EXB_REQUIRE((E + 7) / 8 <= 2147483647LL, "spmm_value_bw: too many edges");
+  const unsigned blocks = (unsigned)((E + 7) / 8);
+  const int mean = reduce == EXACT_REDUCE_MEAN;
+  if (idx_bytes == 4)
+    spmm_value_bw_kernel<int32_t><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+        static_cast<const int32_t*>(row), static_cast<const int32_t*>(rowptr), static_cast<const int32_t*>(col), mat, grad, E,
+        K, mean, out);
+  else
+    spmm_value_bw_kernel<int64_t><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+        static_cast<const int64_t*>(row), static_cast<const int64_t*>(rowptr), static_cast<const int64_t*>(col), mat, grad, E,
+        K, mean, out);
+  EXB_CUDA_OK(cudaGetLastError());
+  return EXB_OK;
+}
 
 int exact_spmm(const void* rowptr, const void* col, int idx_bytes, const float* value, const float* mat,
                int64_t M, int64_t K, int reduce, float* out, void* stream) {

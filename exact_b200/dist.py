@@ -54,6 +54,9 @@ class PeerBuffers:
     owner, exported as a CUDA IPC handle, opened by the other processes.  `ptrs[r]` is the address of rank
     r's buffer as seen from this process (this rank's own allocation at ptrs[rank])."""
 
+    allocated_bytes = 0     # device memory held by live buffers of this process (outside torch's allocator)
+    peak_allocated_bytes = 0
+
     def __init__(self, nbytes, rank, world, group, device):
         lib = _lib.load()
         self.rank, self.world, self.group, self.device, self.nbytes = rank, world, group, device, nbytes
@@ -62,6 +65,8 @@ class PeerBuffers:
         self._imported = []
         with torch.cuda.device(device):
             _lib.check(lib.exact_peer_alloc(nbytes, ctypes.byref(self.local)), "exact_peer_alloc")
+            PeerBuffers.allocated_bytes += nbytes
+            PeerBuffers.peak_allocated_bytes = max(PeerBuffers.peak_allocated_bytes, PeerBuffers.allocated_bytes)
             handle = ctypes.create_string_buffer(64)
             _lib.check(lib.exact_peer_export(self.local, handle), "exact_peer_export")
             handles = [None] * world
@@ -100,6 +105,7 @@ class PeerBuffers:
             if self.local:
                 lib.exact_peer_free(self.local)
                 self.local = ctypes.c_void_p()
+                PeerBuffers.allocated_bytes -= self.nbytes
 
 
 class ShardedSparseTensor:

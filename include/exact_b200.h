@@ -143,6 +143,14 @@ EXACT_API int exact_act_quantized_relu_dropout_forward(const float* x, int64_t n
 EXACT_API int exact_spmm(const void* rowptr, const void* col, int idx_bytes, const float* value,
                          const float* mat, int64_t M, int64_t K, int reduce, float* out, void* stream);
 
+/* Gradient with respect to the edge values, spmm_value_bw of spmm.cc:66-68, 125-126 (kernel
+ * spmm_cuda.cu:172-209): out[e] = dot(mat[col[e], :], grad[row[e], :]), divided by max(length of row[e], 1)
+ * for mean.  row [E] is the COO row of every edge, rowptr [M+1] is read for mean only.  Same lane-strided
+ * FMAs and the same shuffle tree as the reference kernel: bit-identical. */
+EXACT_API int exact_spmm_value_bw(const void* row, const void* rowptr, const void* col, int idx_bytes,
+                                  const float* mat, const float* grad, int64_t E, int64_t K, int reduce,
+                                  float* out, void* stream);
+
 /* exact_spmm with long rows cut into pieces (no counterpart in the reference, whose kernel gives
  * every row to one warp: spmm_cuda.cu:35-57).  Rows with more than long_threshold edges are left out
  * of the row kernel; the caller lists them and their pieces:

@@ -248,6 +248,18 @@ def spmm_bw_mat(rowptr, col, val, grad_out, n_cols, reduce="sum"):
     return spmm(colptr, row_t, w, grad_out, "sum")
 
 
+def spmm_value_bw(rowptr, col, mat, grad, reduce="sum"):
+    """Gradient wrt the edge values (spmm_cuda.cu:172-209): [nnz] fp32."""
+    rowptr = np.ascontiguousarray(rowptr, np.int64)
+    col = np.ascontiguousarray(col, np.int64)
+    row = np.repeat(np.arange(rowptr.size - 1, dtype=np.int64), np.diff(rowptr))
+    mat, grad = _f32(mat), _f32(grad)
+    out = np.zeros(col.size, np.float32)
+    lib().orc_spmm_value_bw(_p(row), _p(rowptr), _p(col), _p(mat), _p(grad), i64(col.size), i64(mat.shape[1]),
+                            ctypes.c_int(1 if reduce == "mean" else 0), _p(out))
+    return out
+
+
 def rows_compact(x):
     """Zero-compacted rows of x [n, K] fp32, K % 32 == 0 (the exchange format of the row-sharded
     aggregation; no counterpart in the reference): mask uint32 [n, K/32] (bit c % 32 of word c / 32 set

@@ -245,24 +245,25 @@ ORC_API void orc_noise_reference_pack(uint64_t seed, uint64_t offset, int64_t N,
 }
 
 /* Production noise of the B200 library (no reference counterpart: the reference draws from torch's
- * global generator).  One Philox4x32-10 call serves one column of an 8-row tile with 16 bits per row:
- * call index q = (n/8) * D + d, counter = (q_lo, q_hi, offset_lo, offset_hi), key = seed;
- * element (n, d) takes word (n%8)/2, low half for even n, high half for odd n;
- * u = (h + 0.5) * 2^-16, in (0, 1).  n is the GLOBAL row index (row_offset + local row). */
+ * global generator).  One Philox4x32-10 call serves a pair of columns of an 8-row tile with 8 bits per
+ * element: call index q = (n/8) * ceil(D/2) + d/2, counter = (q_lo, q_hi, offset_lo, offset_hi), key = seed;
+ * element (n, d) takes byte 2 * (n%8) + d%2 of the 16 output bytes (byte b = bits 8*(b%4).. of word b/4);
+ * u = (h + 0.5) * 2^-8, in (0, 1).  n is the GLOBAL row index (row_offset + local row). */
 ORC_API void orc_noise_b200(uint64_t seed, uint64_t offset, int64_t row_offset, int64_t N, int64_t D,
                             float *noise) {
   const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  const int64_t Dh = (D + 1) / 2;
 #pragma omp parallel for schedule(static)
   for (int64_t n = 0; n < N; n++) {
     int64_t gn = n + row_offset;
     for (int64_t d = 0; d < D; d++) {
-      uint64_t q = (uint64_t)((gn >> 3) * D + d);
+      uint64_t q = (uint64_t)((gn >> 3) * Dh + (d >> 1));
       uint32_t out[4];
       philox4x32_10((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)offset, (uint32_t)(offset >> 32), k0,
                     k1, out);
-      uint32_t w = out[(gn & 7) >> 1];
-      uint32_t h = (gn & 1) ? (w >> 16) : (w & 0xffffu);
-      noise[n * D + d] = ((float)h + 0.5f) * 1.52587890625e-05f;
+      int b = (int)(gn & 7) * 2 + (int)(d & 1);
+      uint32_t h = (out[b >> 2] >> (8 * (b & 3))) & 0xffu;
+      noise[n * D + d] = ((float)h + 0.5f) * 0.00390625f;
     }
   }
 }
@@ -425,5 +426,31 @@ ORC_API void orc_spmm(const int64_t *rowptr, const int64_t *col, const float *va
       float dv = (float)(cnt > 0 ? cnt : 1);
       for (int64_t c = 0; c < K; c++) o[c] = o[c] / dv;
     }
+  }
+}
+
+/* spmm_value_bw.  spmm_cuda.cu:172-209: one warp per edge; lane l accumulates val += mat[col, k] * grad[row, k]
+ * for k = l, l + 32, ... (one FMA each: nvcc contracts the mul+add), then the lanes are added by
+ * val += shfl_down(val, i) for i = 16, 8, 4, 2, 1 (lane 0 holds the result; lanes beyond 31 - i add the value
+ * of their own lane, which lane 0 never sees), and mean divides by max(row length, 1). */
+ORC_API void orc_spmm_value_bw(const int64_t *row, const int64_t *rowptr, const int64_t *col, const float *mat,
+                               const float *grad, int64_t E, int64_t K, int mean, float *out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t e = 0; e < E; e++) {
+    float lane[32];
+    const float *m = mat + col[e] * K, *g = grad + row[e] * K;
+    for (int l = 0; l < 32; l++) {
+      float v = 0.0f;
+      for (int64_t k = l; k < K; k += 32) v = fmaf(m[k], g[k], v);
+      lane[l] = v;
+    }
+    for (int i = 16; i > 0; i >>= 1)
+      for (int l = 0; l < i; l++) lane[l] = lane[l] + lane[l + i];
+    float val = lane[0];
+    if (mean) {
+      int64_t deg = rowptr[row[e] + 1] - rowptr[row[e]];
+      val = val / (float)(deg > 1 ? deg : 1);
+    }
+    out[e] = val;
   }
 }

@@ -227,3 +227,37 @@ def test_philox_path_with_constant_inf_and_nan_rows(bits, D):
     assert np.array_equal(sf.cpu().numpy().view(np.uint32)[~np.isnan(osf)], osf.view(np.uint32)[~np.isnan(osf)])
     assert np.array_equal(np.isnan(sf.cpu().numpy()), np.isnan(osf))
     assert np.array_equal(u8(packed)[:-1], op)
+
+
+def test_swap_round_trip_equals_on_device_result():
+    """config.swap (utils.py:31-34, ops.py:41-42, 50-51): the packed stream is parked in pinned host memory and
+    brought back for backward; the dequantised activation equals the one that never left the device."""
+    from exact_b200 import dequantize_activation, quantize_activation
+    config.compress_activation, config.kept_frac, config.activation_compression_bits = True, 1.0, [2]
+    x = torch.from_numpy(relu_normal(3001, 96, 17)).cuda()
+    u = torch.from_numpy(uniform01((3001, 96), 18)).cuda()
+    try:
+        config.swap = False
+        q_dev = quantize_activation(x, None, noise=u)
+        ref = dequantize_activation(q_dev, x.shape)
+        config.swap = True
+        q_host = quantize_activation(x, None, noise=u)
+        assert not q_host[0].is_cuda and q_host[0].is_pinned()
+        assert torch.equal(q_host[0][:-1], q_dev[0][:-1].cpu())
+        back = dequantize_activation(q_host, x.shape)
+        assert back.is_cuda and torch.equal(back, ref)
+        # a layer's backward through the swapped copy
+        lin = torch.nn.Linear(96, 8).cuda()
+        from exact_b200.ops import qlinear
+        xa = x.clone().requires_grad_()
+        config.manual_seed(5)
+        qlinear.apply(xa, lin.weight, lin.bias).sum().backward()
+        g_swap, w_swap = xa.grad.clone(), lin.weight.grad.clone()
+        lin.weight.grad = None
+        config.swap = False
+        xb = x.clone().requires_grad_()
+        config.manual_seed(5)
+        qlinear.apply(xb, lin.weight, lin.bias).sum().backward()
+        assert torch.equal(g_swap, xb.grad) and torch.equal(w_swap, lin.weight.grad)
+    finally:
+        config.swap = False

@@ -84,3 +84,24 @@ def test_reference_spmm_equals_oracle(reduce, with_values):
     else:
         out = rs.spmm_mean_fw(None, t(rowptr), t(col), v, None, None, None, t(mat))
     assert np.array_equal(out.cpu().numpy(), oracle.spmm(rowptr, col, val, mat, reduce))
+
+
+@pytest.mark.parametrize("reduce", ["sum", "mean"])
+def test_reference_value_gradient_equals_oracle(reduce):
+    """spmm_sum_bw / spmm_mean_bw with value_requires_grad (spmm.cc:57-79, 115-139 -> spmm_value_bw_kernel)."""
+    rs = _ref("ref_spmm")
+    n, K = 4000, 100
+    rowptr, col, val = random_csr(n, n, 30000, 3, True)
+    row = np.repeat(np.arange(n), np.diff(rowptr))
+    mat, g = normal(n, K, 4), normal(n, K, 5)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    perm = np.argsort(col * n + row, kind="stable")
+    colptr = np.zeros(n + 1, np.int64)
+    np.cumsum(np.bincount(col, minlength=n), out=colptr[1:])
+    args = [t(row), t(rowptr), t(col), t(val)]
+    if reduce == "mean":
+        args.append(t(np.diff(rowptr)))
+    args += [t(colptr), t(perm), t(mat), t(g), True, True, False]
+    fn = rs.spmm_sum_bw if reduce == "sum" else rs.spmm_mean_bw
+    grad_value = fn(*args)[0]
+    assert np.array_equal(grad_value.cpu().numpy(), oracle.spmm_value_bw(rowptr, col, mat, g, reduce))

@@ -153,3 +153,33 @@ def test_power_law_graph_with_many_out_of_order_pieces(K):
         assert np.array_equal(out[~long], ref[~long])
         err = np.abs(out[long] - ref[long]).max(1)
         assert np.all(err <= 1e-5 * np.abs(ref[long]).max(1) + 1e-6 * np.sqrt(np.diff(rp)[long]) * (reduce == "sum"))
+
+
+@pytest.mark.parametrize("idx", [torch.int64, torch.int32])
+@pytest.mark.parametrize("reduce", ["sum", "mean"])
+@pytest.mark.parametrize("K", [128, 100, 40, 13])
+def test_value_gradient_bit_exact(K, reduce, idx):
+    """spmm_value_bw (spmm_cuda.cu:172-209): the same lane-strided FMAs and shuffle tree as the reference."""
+    rowptr, col, val = random_csr(5000, 5000, 40000, 3, True)
+    row = np.repeat(np.arange(5000), np.diff(rowptr))
+    mat, g = normal(5000, K, 4), normal(5000, K, 5)
+    out = S.spmm_value_bw(t(row, idx), t(rowptr, idx), t(col, idx), t(mat), t(g), reduce)
+    assert np.array_equal(out.cpu().numpy(), oracle.spmm_value_bw(rowptr, col, mat, g, reduce))
+
+
+@pytest.mark.parametrize("reduce", ["sum", "mean"])
+def test_qmatmul_edge_value_gradient(reduce):
+    """Edge values that require grad: the saved dense operand is dequantised (and projected back) and the value
+    gradient computed from it (ops.py:291-307, 341-371); with compression off it is exact."""
+    config.compress_activation = False
+    n, K = 3000, 64
+    rowptr, col, val = random_csr(n, n, 20000, 5, True)
+    row = np.repeat(np.arange(n), np.diff(rowptr))
+    v = t(val).requires_grad_()
+    adj = SparseTensor(row=t(row), col=t(col), value=v, sparse_sizes=(n, n), is_sorted=True)
+    mat, g = normal(n, K, 6), normal(n, K, 7)
+    x = t(mat).requires_grad_()
+    out = qmatmul(adj, x, reduce)
+    out.backward(t(g))
+    assert np.array_equal(v.grad.cpu().numpy(), oracle.spmm_value_bw(rowptr, col, mat, g, reduce))
+    config.compress_activation = True
