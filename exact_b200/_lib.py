@@ -70,6 +70,7 @@ SIGNATURES = {
     "exact_linear_workspace_bytes": (c_i64, [c_i64, c_i64, c_i64]),
     "exact_linear_forward": (c_int, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_i64, c_ptr, c_i64, c_i64, c_ptr, c_i64,
                                      c_i64, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_ptr]),
+    "exact_spmm_minmax": (c_int, [c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_int, c_ptr, c_ptr, c_ptr]),
     "exact_spmm_value_bw": (c_int, [c_ptr, c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_int, c_ptr, c_ptr]),
     "exact_spmm": (c_int, [c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_int, c_ptr, c_ptr]),
 }

@@ -161,3 +161,62 @@ def spmm_mean_bw(row, rowptr, col, value, rowcount, colptr, csr2csc, mat, grad_o
             transposed = (colptr, row_t, w)
         grad_mat = _spmm(transposed[0], transposed[1], transposed[2], grad_out, "sum")
     return grad_value, grad_mat
+
+
+def _spmm_minmax(rowptr, col, value, mat, is_max):
+    if not (rowptr.is_cuda and col.is_cuda and mat.is_cuda):
+        raise RuntimeError("rowptr, col and mat must be CUDA tensors")
+    if mat.dim() != 2 or mat.dtype != torch.float32:
+        raise RuntimeError("mat must be a float32 matrix")
+    if rowptr.dtype != col.dtype or col.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("rowptr and col must both be int32 or both int64")
+    mat, rowptr, col = mat.contiguous(), rowptr.contiguous(), col.contiguous()
+    if value is not None:
+        value = value.detach().to(torch.float32).contiguous()
+    M, K, nnz = rowptr.numel() - 1, mat.size(1), col.numel()
+    out = torch.empty((M, K), dtype=torch.float32, device=mat.device)
+    arg_out = torch.empty((M, K), dtype=col.dtype, device=mat.device)
+    ib = 4 if col.dtype == torch.int32 else 8
+    _lib.invoke("exact_spmm_minmax", nnz * (K * 4 + ib) + M * K * (4 + ib), _lib.ptr(rowptr), _lib.ptr(col), ib,
+                _lib.ptr(value), _lib.ptr(mat), M, K, nnz, 1 if is_max else 0, _lib.ptr(out), _lib.ptr(arg_out),
+                _lib.stream_ptr())
+    return out, arg_out
+
+
+def spmm_max_fw(rowptr, col, value, mat):
+    """spmm.cc:145-157 -> (out, arg_out)."""
+    return _spmm_minmax(rowptr, col, value, mat, True)
+
+
+def spmm_min_fw(rowptr, col, value, mat):
+    """spmm.cc:195-208 -> (out, arg_out)."""
+    return _spmm_minmax(rowptr, col, value, mat, False)
+
+
+def spmm_max_bw(col, value, mat, arg_out, grad_out, has_value, value_requires_grad, mat_requires_grad):
+    """spmm.cc:159-193 (and 210-241 for min, the same arithmetic): gradients routed to the winning edges."""
+    arg_out = arg_out.to(torch.int64)
+    invalid = arg_out == col.size(0)
+    arg_out = arg_out.masked_fill(invalid, 0)
+    ind = col.to(torch.int64).index_select(0, arg_out.flatten()).view_as(arg_out)
+    grad_value = None
+    if has_value and value_requires_grad:
+        out = mat.gather(-2, ind)
+        out.mul_(grad_out)
+        out.masked_fill_(invalid, 0)
+        grad_value = torch.zeros_like(value)
+        grad_value.scatter_add_(0, arg_out.flatten(), out.flatten())
+    grad_mat = None
+    if mat_requires_grad:
+        if has_value:
+            v = value.detach().index_select(0, arg_out.flatten()).view_as(arg_out)
+            v = v * grad_out
+        else:
+            v = grad_out.clone()
+        v.masked_fill_(invalid, 0)
+        grad_mat = torch.zeros_like(mat)
+        grad_mat.scatter_add_(-2, ind, v)
+    return grad_value, grad_mat
+
+
+spmm_min_bw = spmm_max_bw

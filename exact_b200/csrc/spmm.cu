@@ -432,11 +432,68 @@ __global__ void __launch_bounds__(256) spmm_value_bw_kernel(const IdxT* __restri
   }
 }
 
+// max / min aggregation with the position of the winning edge (spmm_cuda.cu:27-104 with REDUCE = MAX / MIN;
+// reducer.cuh:43-85): out[r, c] = max_e value[e] * mat[col[e], c], arg[r, c] = the first edge that attains it
+// (a later edge replaces the current one only when strictly greater / smaller), rows without edges give 0 and
+// arg = nnz.  One warp per row and 32 columns; lane = column, edges in CSR order.
+template <typename IdxT, bool HAS_VAL, bool IS_MAX>
+__global__ void __launch_bounds__(256) spmm_minmax_kernel(const IdxT* __restrict__ rowptr, const IdxT* __restrict__ col,
+                                                          const float* __restrict__ val, const float* __restrict__ mat,
+                                                          long long M, long long K, long long nnz, float* __restrict__ out,
+                                                          IdxT* __restrict__ arg_out) {
+  const int lane = threadIdx.x & 31;
+  const long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long c = (long long)blockIdx.y * 32 + lane;
+  if (r >= M) return;
+  const long long begin = (long long)rowptr[r], end = (long long)rowptr[r + 1];
+  float best = IS_MAX ? -3.402823466e+38f : 3.402823466e+38f;   // numeric_limits lowest() / max()
+  long long arg = nnz;
+  for (long long e = begin; e < end; e++) {
+    const long long src = (long long)col[e];
+    if (c < K) {
+      float v = __ldg(mat + src * K + c);
+      if (HAS_VAL) v = __fmul_rn(__ldg(val + e), v);
+      if (IS_MAX ? (v > best) : (v < best)) {
+        best = v;
+        arg = e;
+      }
+    }
+  }
+  if (c < K) {
+    out[r * K + c] = end > begin ? best : 0.f;           // reducer.cuh:78-84
+    arg_out[r * K + c] = end > begin ? (IdxT)arg : (IdxT)nnz;
+  }
+}
+
 }  // namespace exb
 
 using namespace exb;
 
 extern "C" {
+
+int exact_spmm_minmax(const void* rowptr, const void* col, int idx_bytes, const float* value, const float* mat,
+                      int64_t M, int64_t K, int64_t nnz, int is_max, float* out, void* arg_out, void* stream) {
+  EXB_REQUIRE(idx_bytes == 4 || idx_bytes == 8, "spmm_minmax: idx_bytes must be 4 or 8 (got %d)", idx_bytes);
+  EXB_REQUIRE(M >= 0 && K >= 0 && nnz >= 0, "spmm_minmax: negative shape");
+  if (M == 0 || K == 0) return EXB_OK;
+  EXB_REQUIRE(rowptr && mat && out && arg_out && (nnz == 0 || col), "spmm_minmax: null pointer");
+  EXB_REQUIRE((M + 7) / 8 <= 2147483647LL && (K + 31) / 32 <= 65535, "spmm_minmax: shape too large");
+  dim3 grid((unsigned)((M + 7) / 8), (unsigned)((K + 31) / 32));
+  cudaStream_t st = (cudaStream_t)stream;
+#define EXB_MM(IDX_, HV_, MX_)                                                                                   \
+  spmm_minmax_kernel<IDX_, HV_, MX_><<<grid, 256, 0, st>>>(static_cast<const IDX_*>(rowptr), static_cast<const IDX_*>(col), \
+                                                           value, mat, M, K, nnz, out, static_cast<IDX_*>(arg_out))
+  if (idx_bytes == 4) {
+    if (value) { if (is_max) EXB_MM(int32_t, true, true); else EXB_MM(int32_t, true, false); }
+    else { if (is_max) EXB_MM(int32_t, false, true); else EXB_MM(int32_t, false, false); }
+  } else {
+    if (value) { if (is_max) EXB_MM(int64_t, true, true); else EXB_MM(int64_t, true, false); }
+    else { if (is_max) EXB_MM(int64_t, false, true); else EXB_MM(int64_t, false, false); }
+  }
+#undef EXB_MM
+  EXB_CUDA_OK(cudaGetLastError());
+  return EXB_OK;
+}
 
 int exact_spmm_value_bw(const void* row, const void* rowptr, const void* col, int idx_bytes, const float* mat,
                         const float* grad, int64_t E, int64_t K, int reduce, float* out, void* stream) {

@@ -359,3 +359,55 @@ class qspmm_mean(Function):
                                                  mat_requires_grad, transposed=transposed)
         empty_cache(config.empty_cache_threshold)
         return None, None, None, grad_value, None, None, None, None, grad_mat, None, None, None, None
+
+
+def _minmax_forward(ctx, is_max, rowptr, col, value, has_value, other, quantized, scheme):
+    """ops.py:378-391 / 410-423: the dense operand is saved quantised WITHOUT projection
+    (quantize_activation(other, scheme)) and dequantised in backward for the gather."""
+    fw = spmm.spmm_max_fw if is_max else spmm.spmm_min_fw
+    output, arg_out = fw(rowptr, col, value, other)
+    if quantized is None:
+        quantized = quantize_activation(other, scheme)
+    else:
+        assert isinstance(quantized, tuple)
+    empty_cache(config.empty_cache_threshold)
+    ctx.saved = col, value, quantized, arg_out
+    ctx.other_args = has_value, other.shape, value.requires_grad if has_value else False, other.requires_grad
+    ctx.scheme = scheme
+    return output
+
+
+def _minmax_backward(ctx, grad_outputs):
+    """ops.py:393-403 / 425-436."""
+    col, value, quantized, arg_out = ctx.saved
+    has_value, q_input_shape, value_requires_grad, mat_requires_grad = ctx.other_args
+    other = dequantize_activation(quantized, q_input_shape)
+    del quantized, ctx.saved
+    empty_cache(config.empty_cache_threshold)
+    grad_value, grad_mat = spmm.spmm_max_bw(col, value, other, arg_out, grad_outputs.contiguous(), has_value,
+                                            value_requires_grad, mat_requires_grad)
+    return None, None, grad_value, None, grad_mat, None, None, None
+
+
+class qspmm_max(Function):
+    """ops.py:374-403."""
+
+    @staticmethod
+    def forward(ctx, rowptr, col, value, has_value, other, quantized=None, randmat=None, scheme=None):
+        return _minmax_forward(ctx, True, rowptr, col, value, has_value, other, quantized, scheme)
+
+    @staticmethod
+    def backward(ctx, grad_outputs):
+        return _minmax_backward(ctx, grad_outputs)
+
+
+class qspmm_min(Function):
+    """ops.py:406-436."""
+
+    @staticmethod
+    def forward(ctx, rowptr, col, value, has_value, other, quantized=None, randmat=None, scheme=None):
+        return _minmax_forward(ctx, False, rowptr, col, value, has_value, other, quantized, scheme)
+
+    @staticmethod
+    def backward(ctx, grad_outputs):
+        return _minmax_backward(ctx, grad_outputs)

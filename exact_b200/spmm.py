@@ -7,7 +7,8 @@ from torch.autograd.function import Function
 from .conf import config
 from .cpp_extension import backward_func as ext_backward_func
 from .cpp_extension import spmm as ext_spmm
-from .ops import linear_backward_from_compressed, project_and_quantize, qspmm_mean, qspmm_sum
+from .ops import (linear_backward_from_compressed, project_and_quantize, qspmm_max, qspmm_mean, qspmm_min,
+                  qspmm_sum)
 from .qscheme import QScheme
 from .utils import empty_cache
 
@@ -41,9 +42,10 @@ def qmatmul(src, other, reduce="sum", quantized=None, randmat=None, scheme=None)
             row, rowcount, csr2csc, colptr = st.row(), st.rowcount(), st.csr2csc(), st.colptr()
         return qspmm_mean.apply(row, rowptr, col, value, rowcount, colptr, csr2csc, has_value, other, quantized,
                                 randmat, scheme, st)
-    elif reduce in ("min", "max"):
-        raise NotImplementedError("min/max aggregation is used by neither GCN nor GraphSAGE-mean; "
-                                  "only sum and mean are provided")
+    elif reduce == "min":      # spmm.py:46-48
+        return qspmm_min.apply(rowptr, col, value, has_value, other, quantized, randmat, scheme)
+    elif reduce == "max":      # spmm.py:49-51
+        return qspmm_max.apply(rowptr, col, value, has_value, other, quantized, randmat, scheme)
     raise ValueError(reduce)
 
 

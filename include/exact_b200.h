@@ -143,6 +143,15 @@ EXACT_API int exact_act_quantized_relu_dropout_forward(const float* x, int64_t n
 EXACT_API int exact_spmm(const void* rowptr, const void* col, int idx_bytes, const float* value,
                          const float* mat, int64_t M, int64_t K, int reduce, float* out, void* stream);
 
+/* spmm.spmm_max_fw / spmm_min_fw (spmm.cc:145-157, 195-208 -> spmm_cuda.cu:27-170 with REDUCE = MAX / MIN,
+ * reducer.cuh:43-85): out[r, c] = max (min) over the edges e of row r of value[e] * mat[col[e], c], and
+ * arg_out[r, c] = the first edge attaining it (same index type as rowptr / col); rows without edges give 0
+ * and arg = nnz.  The backward of these reductions (spmm.cc:159-193, 210-241) is index arithmetic on arg_out
+ * and stays library ops. */
+EXACT_API int exact_spmm_minmax(const void* rowptr, const void* col, int idx_bytes, const float* value,
+                                const float* mat, int64_t M, int64_t K, int64_t nnz, int is_max, float* out,
+                                void* arg_out, void* stream);
+
 /* Gradient with respect to the edge values, spmm_value_bw of spmm.cc:66-68, 125-126 (kernel
  * spmm_cuda.cu:172-209): out[e] = dot(mat[col[e], :], grad[row[e], :]), divided by max(length of row[e], 1)
  * for mean.  row [E] is the COO row of every edge, rowptr [M+1] is read for mean only.  Same lane-strided

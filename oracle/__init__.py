@@ -260,6 +260,20 @@ def spmm_value_bw(rowptr, col, mat, grad, reduce="sum"):
     return out
 
 
+def spmm_minmax(rowptr, col, val, mat, reduce):
+    """max / min aggregation -> (out [M, K] fp32, arg_out [M, K] int64; nnz where a row has no edge)."""
+    rowptr = np.ascontiguousarray(rowptr, np.int64)
+    col = np.ascontiguousarray(col, np.int64)
+    mat = _f32(mat)
+    M, K = rowptr.size - 1, mat.shape[1]
+    v = None if val is None else _f32(val)
+    out = np.zeros((M, K), np.float32)
+    arg = np.zeros((M, K), np.int64)
+    lib().orc_spmm_minmax(_p(rowptr), _p(col), _p(v) if v is not None else None, _p(mat), i64(M), i64(K), i64(col.size),
+                          ctypes.c_int(1 if reduce == "max" else 0), _p(out), _p(arg))
+    return out, arg
+
+
 def rows_compact(x):
     """Zero-compacted rows of x [n, K] fp32, K % 32 == 0 (the exchange format of the row-sharded
     aggregation; no counterpart in the reference): mask uint32 [n, K/32] (bit c % 32 of word c / 32 set

@@ -454,3 +454,25 @@ ORC_API void orc_spmm_value_bw(const int64_t *row, const int64_t *rowptr, const 
     out[e] = val;
   }
 }
+
+/* spmm_kernel with REDUCE = MAX / MIN.  spmm_cuda.cu:54-103 + reducer.cuh:43-85: val starts at lowest() / max(),
+ * an edge replaces it only when strictly greater / smaller (so the first edge of a tie wins), its position is
+ * kept in arg; rows without edges write 0 and arg = nnz (spmm_cuda.cu:152: arg_out is filled with col.numel()). */
+ORC_API void orc_spmm_minmax(const int64_t *rowptr, const int64_t *col, const float *val, const float *mat,
+                             int64_t M, int64_t K, int64_t nnz, int is_max, float *out, int64_t *arg_out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < M; r++) {
+    for (int64_t c = 0; c < K; c++) {
+      float best = is_max ? -3.402823466e+38f : 3.402823466e+38f;
+      int64_t arg = nnz;
+      for (int64_t e = rowptr[r]; e < rowptr[r + 1]; e++) {
+        float v = mat[col[e] * K + c];
+        if (val) v = val[e] * v;
+        if (is_max ? (v > best) : (v < best)) { best = v; arg = e; }
+      }
+      int has = rowptr[r + 1] > rowptr[r];
+      out[r * K + c] = has ? best : 0.0f;
+      arg_out[r * K + c] = has ? arg : nnz;
+    }
+  }
+}

@@ -105,3 +105,18 @@ def test_reference_value_gradient_equals_oracle(reduce):
     fn = rs.spmm_sum_bw if reduce == "sum" else rs.spmm_mean_bw
     grad_value = fn(*args)[0]
     assert np.array_equal(grad_value.cpu().numpy(), oracle.spmm_value_bw(rowptr, col, mat, g, reduce))
+
+
+@pytest.mark.parametrize("reduce", ["max", "min"])
+@pytest.mark.parametrize("with_values", [True, False])
+def test_reference_max_min_equal_oracle(reduce, with_values):
+    rs = _ref("ref_spmm")
+    rowptr, col, val = random_csr(4000, 4000, 20000, 3, with_values)
+    mat = normal(4000, 64, 4)
+    mat[:, 0] = 1.0     # ties: the first edge of a row must win
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    fn = rs.spmm_max_fw if reduce == "max" else rs.spmm_min_fw
+    out, arg = fn(t(rowptr), t(col), t(val) if with_values else None, t(mat))
+    ref_out, ref_arg = oracle.spmm_minmax(rowptr, col, val, mat, reduce)
+    assert np.array_equal(out.cpu().numpy(), ref_out)
+    assert np.array_equal(arg.cpu().numpy(), ref_arg)

@@ -183,3 +183,36 @@ def test_qmatmul_edge_value_gradient(reduce):
     out.backward(t(g))
     assert np.array_equal(v.grad.cpu().numpy(), oracle.spmm_value_bw(rowptr, col, mat, g, reduce))
     config.compress_activation = True
+
+
+@pytest.mark.parametrize("idx", [torch.int64, torch.int32])
+@pytest.mark.parametrize("reduce", ["max", "min"])
+@pytest.mark.parametrize("with_values", [True, False])
+@pytest.mark.parametrize("K", [128, 40, 13])
+def test_max_min_forward_and_grad(K, with_values, reduce, idx):
+    """spmm_max / spmm_min (test/test_op.py:506-562 asserts them against torch_sparse): values and the position
+    of the winning edge equal the oracle's (the first edge of a tie wins, empty rows give 0 and arg = nnz);
+    the gradient goes to the winning source rows (spmm.cc:159-193)."""
+    n = 3000
+    rowptr, col, val = random_csr(n, n, 15000, 3, with_values)     # average degree 5: some rows are empty
+    mat = normal(n, K, 4)
+    mat[:, 0] = 1.0                                                # ties in column 0
+    fn = S.spmm_max_fw if reduce == "max" else S.spmm_min_fw
+    out, arg = fn(t(rowptr, idx), t(col, idx), None if val is None else t(val), t(mat))
+    ref_out, ref_arg = oracle.spmm_minmax(rowptr, col, val, mat, reduce)
+    assert np.array_equal(out.cpu().numpy(), ref_out)
+    assert np.array_equal(arg.cpu().numpy().astype(np.int64), ref_arg)
+    # autograd through qmatmul with compression off: d out / d mat scatters g to the winners
+    config.compress_activation = False
+    row = np.repeat(np.arange(n), np.diff(rowptr))
+    adj = SparseTensor(row=t(row), col=t(col), value=None if val is None else t(val), sparse_sizes=(n, n), is_sorted=True)
+    x = t(mat).requires_grad_()
+    g = normal(n, K, 5)
+    qmatmul(adj, x, reduce).backward(t(g))
+    ref_g = np.zeros((n, K), np.float64)
+    valid = ref_arg < col.size
+    w = np.ones(col.size, np.float32) if val is None else val
+    rr, cc = np.nonzero(valid)
+    np.add.at(ref_g, (col[ref_arg[rr, cc]], cc), (w[ref_arg[rr, cc]] * g[rr, cc]).astype(np.float64))
+    np.testing.assert_allclose(x.grad.cpu().numpy(), ref_g, rtol=1e-5, atol=1e-5)
+    config.compress_activation = True
