@@ -214,6 +214,7 @@ def run_b200(args):
     config.compact_gather = not args.dense_gather
     config.compact_operand = not args.dense_gather
     config.peer_exchange = not args.no_peer_exchange
+    config.column_split_aggregation = not args.row_split
     config.cache_constant_gather = False   # every timed step exchanges its input features again
     net = cls(c["feats"], c["hidden"], c["classes"], c["layers"], dropout=c["dropout"], batch_norm=c["batch_norm"])
     net = (QModule(net) if c["use_qmodule"] else net).to(dev).train()
@@ -720,6 +721,9 @@ def main():
     ap.add_argument("--dense-gather", action="store_true", help="N > 1: exchange dense rows (no zero compaction)")
     ap.add_argument("--no-peer-exchange", action="store_true",
                     help="N > 1: exchange through the collective library only (no rank writes a peer's memory)")
+    ap.add_argument("--row-split", action="store_true",
+                    help="N > 1: aggregate on row shards of the adjacency (exchange whole operand rows) instead of "
+                         "switching to column slices around each aggregation")
     ap.add_argument("--cpu-reference", action="store_true",
                     help="--impl reference: time the CPU restatement even when the reference's CUDA kernels are built")
     # the reference drivers' knobs (mem_speed_bench/arxiv/train_full_batch.py:44-48)

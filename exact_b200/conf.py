@@ -53,6 +53,9 @@ class QuantizationConfig:
         # cores (tf32 inputs, fp32 accumulation: about 5e-4 relative, far below the quantisation noise of the
         # activation); False: unpack, then the library's fp32 GEMM.
         self.grad_weight_tensor_core = True
+        # qbatch_norm.backward reads the saved input in its packed form (two passes over the packed bytes) instead
+        # of dequantising it into an [N, D] tensor for ATen's backward.
+        self.bn_backward_from_packed = True
         # Row-sharded aggregation inside the one-node GraphSAGE layer: exchange the dense operand as compact
         # rows (kept columns + values per row) when at most this share of its entries is non-zero, as outputs
         # of ReLU + dropout and gradients that passed their masks are.  Same dense rows bit for bit.
@@ -62,6 +65,9 @@ class QuantizationConfig:
         # slice of the operand; two all-to-all exchanges written into the peers' buffers) instead of gathering
         # all rows of the operand on every rank.  Needs peer_exchange; per-row sums are then regrouped.
         self.column_split_aggregation = True
+        # ... and every rank's SpMM stores its result rows straight into their owners' buffers (the second
+        # exchange folded into the kernel); off: a local result followed by a scatter kernel.
+        self.routed_aggregation_output = True
         # Row shards write their compact rows straight into every peer's buffer (plain stores over NVLink,
         # buffers mapped with CUDA IPC) instead of going through a collective; off, or when the mapping
         # fails, the collective-library exchange is used.

@@ -144,3 +144,40 @@ def native_batch_norm_backward(grad_out, input, weight, running_mean, running_va
                                train, eps, output_mask):
     return torch.ops.aten.native_batch_norm_backward(grad_out, input, weight, running_mean, running_var,
                                                      save_mean, save_invstd, train, eps, output_mask)
+
+
+def batch_norm_backward_from_packed_supported(grad_out, quantized):
+    """Whether native_batch_norm_backward can read the saved input in its packed form (this library's kernels):
+    a compressed [N, D] fp32 activation with bf16 row statistics and D a multiple of 4."""
+    q_input, q_bits, q_scale, q_min = quantized
+    return (q_bits is not None and grad_out.is_cuda and grad_out.dtype == torch.float32 and grad_out.dim() == 2
+            and grad_out.size(1) % 4 == 0 and q_scale.dtype == torch.bfloat16 and q_input.is_cuda)
+
+
+def batch_norm_backward_from_packed(grad_out, quantized, weight, running_mean, running_var, save_mean, save_invstd,
+                                    train, eps, output_mask):
+    """native_batch_norm_backward (the call of ops.py:248-251) with the dequantisation of ops.py:238 folded into
+    both of its passes: the column sums and the element-wise pass read the packed bytes and the bf16 row
+    statistics, the [N, D] reconstruction is never written.  Returns (grad_input, grad_weight, grad_bias)."""
+    q_input, q_bits, q_scale, q_min = quantized
+    g = grad_out.contiguous()
+    N, D = g.shape
+    if train:
+        mean, invstd = save_mean, save_invstd
+    else:
+        mean, invstd = running_mean, torch.rsqrt(running_var + eps)
+    mean, invstd = mean.to(torch.float32).contiguous(), invstd.to(torch.float32).contiguous()
+    w = None if weight is None else weight.detach().to(torch.float32).contiguous()
+    lib = _lib.load()
+    ws_bytes = int(lib.exact_bn_backward_workspace_bytes(D))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=g.device)
+    grad_input = torch.empty_like(g) if output_mask[0] else None
+    grad_weight = torch.empty(D, dtype=torch.float32, device=g.device) if output_mask[1] else None
+    grad_bias = torch.empty(D, dtype=torch.float32, device=g.device) if output_mask[2] else None
+    wpt = 8 // q_bits
+    nbytes = (2 if (grad_input is not None and (train or grad_weight is not None or grad_bias is not None)) else 1) * (
+        N * D * 4 + (N + wpt - 1) // wpt * D + 4 * N) + (N * D * 4 if grad_input is not None else 0)
+    _lib.invoke("exact_bn_backward_from_packed", nbytes, _lib.ptr(g), N, D, _lib.ptr(q_input), q_bits, _lib.ptr(q_scale),
+                _lib.ptr(q_min), _lib.ptr(w), _lib.ptr(mean), _lib.ptr(invstd), 1 if train else 0, _lib.ptr(ws), ws_bytes,
+                _lib.ptr(grad_input), _lib.ptr(grad_weight), _lib.ptr(grad_bias), _lib.stream_ptr())
+    return grad_input, grad_weight, grad_bias

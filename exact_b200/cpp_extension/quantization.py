@@ -106,9 +106,10 @@ def rp_quantize_pack(data, R, bits, seed=None, offset=None, row_offset=None, wan
 
 
 def unpack_rp_supported(D, k):
-    """Shapes the fused unpack+transpose-projection kernel takes."""
-    Dpad, kpan = (D + 15) // 16 * 16, (k + 31) // 32
-    return Dpad <= 256 and Dpad * kpan * 128 + 2 * 128 * kpan * 128 + 4 * 4096 + 2048 <= 200 * 1024
+    """Shapes the fused unpack+transpose-projection kernels take: every configured one (sign(R) resident when it
+    fits beside the A tiles, streamed in panels otherwise)."""
+    Dpad, kpad = (D + 15) // 16 * 16, (k + 31) // 32 * 32
+    return D > 0 and k > 0 and Dpad * kpad < (1 << 28)
 
 
 def unpack_dequant_rp(packed, bits, scale, mn, N, R):

@@ -1,5 +1,6 @@
 """Stand-in for the reference's `exact.cpp_extension.spmm` module (exact/exact/cpp_extension/spmm.cc:243-252):
 spmm_{sum,mean}_{fw,bw} with the reference's argument lists, forwarded to the C ABI."""
+import ctypes
 import weakref
 
 import torch
@@ -57,9 +58,11 @@ def long_row_plan(rowptr, threshold, col=None):
 REGROUP = 0x100   # EXACT_SPMM_REGROUP
 
 
-def _spmm(rowptr, col, value, mat, reduce, regroup=False):
+def _spmm(rowptr, col, value, mat, reduce, regroup=False, route=None):
     """spmm.cc:12-18 -> spmm_cuda.cu:106-170.  `regroup`: the caller accepts a regrouped per-row fp32 sum
-    (narrow operands then gather two edges per load instruction)."""
+    (narrow operands then gather several edges per load instruction).  `route` = (shard, col0, ldd, addresses):
+    no local result; row r goes to columns col0 .. of row r % shard of the [shard, ldd] buffer at
+    addresses[r // shard] (the owners' buffers of a row-sharded run) and None is returned."""
     if not rowptr.is_cuda or not col.is_cuda or not mat.is_cuda:
         raise RuntimeError("rowptr, col and mat must be CUDA tensors")
     if rowptr.dim() != 1 or col.dim() != 1:
@@ -79,7 +82,7 @@ def _spmm(rowptr, col, value, mat, reduce, regroup=False):
         value = value.detach().to(torch.float32).contiguous()
     M = rowptr.numel() - 1
     K = mat.size(1)
-    out = torch.empty((M, K), dtype=mat.dtype, device=mat.device)
+    out = torch.empty((M, K), dtype=mat.dtype, device=mat.device) if route is None else None
     ib = 4 if col.dtype == torch.int32 else 8
     nnz = col.numel()
     index_bytes = nnz * (ib + (4 if value is not None else 0)) + (M + 1) * ib
@@ -90,6 +93,19 @@ def _spmm(rowptr, col, value, mat, reduce, regroup=False):
     thr = int(config.spmm_long_row)
     plan = long_row_plan(rowptr, thr, col) if thr > 0 else None
     red = _lib.REDUCE[reduce] | (REGROUP if regroup else 0)
+    if route is not None:
+        shard, col0, ldd, addresses = route
+        arr = (ctypes.c_void_p * len(addresses))(*addresses)
+        none = {"item_row": None, "item_begin": None, "item_end": None, "item_slot": None, "n_items": 0,
+                "long_row": None, "long_item_ptr": None, "n_long": 0}
+        pl = plan if plan is not None else none
+        scratch = torch.empty((pl["n_items"], K), dtype=torch.float32, device=mat.device) if plan is not None else None
+        _lib.invoke("exact_spmm_split_routed", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value),
+                    _lib.ptr(mat), M, K, red, thr if plan is not None else 0, _lib.ptr(pl["item_row"]),
+                    _lib.ptr(pl["item_begin"]), _lib.ptr(pl["item_end"]), _lib.ptr(pl["item_slot"]), pl["n_items"],
+                    _lib.ptr(pl["long_row"]), _lib.ptr(pl["long_item_ptr"]), pl["n_long"], _lib.ptr(scratch), shard,
+                    col0, ldd, arr, len(addresses), _lib.stream_ptr(), l2_bytes=l2_bytes, edge_columns=nnz * K)
+        return None
     if plan is None:
         _lib.invoke("exact_spmm", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), _lib.ptr(mat), M, K,
                     red, _lib.ptr(out), _lib.stream_ptr(), l2_bytes=l2_bytes, edge_columns=nnz * K)

@@ -17,6 +17,13 @@
 //              swizzled staging tile so that the fp32 reconstruction leaves in full 128-byte lines.
 // Two A buffers and two accumulator buffers overlap producer, MMA and epilogue of consecutive tiles.
 // All mbarrier waits are bounded; on expiry the CTA aborts cleanly and leaves a non-zero status word.
+//
+// Shapes whose sign(R) does not fit beside the A tiles (256 -> 128, every D = 602 shape) take
+// rp_unpack_stream_kernel: a work item is (128-row tile, block of up to 256 output columns), and the
+// contraction is streamed in panels of 32 projected columns through a ring of stages, each holding the
+// dequantised A panel (producer warps) and the matching panel of sign(R) (one TMA box, served by L2).  The
+// packed bytes of a tile are dequantised once per column block; that costs a few instructions per value
+// and the packed stream is a few per cent of the bytes written.
 #include "exact_b200.h"
 #include "tc.cuh"
 
@@ -257,6 +264,295 @@ rp_unpack_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Streaming variant: neither operand resident.
+constexpr int kStreamThreads = 448;  // 14 warps: MMA, 4 A producers, 4 epilogue, B loader, 4 more epilogue
+constexpr unsigned kStreamAPanel = kBwdTileM * 128;  // bytes of a [128 x 32] fp32 panel
+
+struct RpBwdStreamParams {
+  const uint8_t* packed;
+  const uint16_t* scale_bf16;
+  const uint16_t* min_bf16;
+  float* out;
+  int* status;
+  int* lib_status;
+  long long N;
+  int D, k, kpanels, kmma;
+  int DB, ndb;          // output columns per block (multiple of 16, <= 256), blocks per tile
+  long long num_tiles;
+  int stages;
+  unsigned stage_bytes;  // A panel + B panel
+  unsigned warp_bytes;   // shared memory per producer warp for the packed bytes of its 32 rows
+  float inv_sqrt_k;
+};
+
+template <int BITS>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+rp_unpack_stream_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ RpBwdStreamParams p) {
+  constexpr int WPT = 8 / BITS;
+  constexpr uint32_t MASK = (1u << BITS) - 1u;
+  constexpr int kMaxStages = 8;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) unsigned long long s_full[kMaxStages];
+  __shared__ __align__(8) unsigned long long s_empty[kMaxStages];
+  __shared__ __align__(8) unsigned long long s_tfull[2];
+  __shared__ __align__(8) unsigned long long s_tempty[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t stage_area = ring + (uint32_t)p.stages * p.stage_bytes;  // 8 x 4 KB epilogue staging tiles
+  const uint32_t bytes_area = stage_area + 8u * 4096u;                    // 4 x warp_bytes of packed bytes
+  volatile int* abort_flag = &s_abort;
+  const uint32_t b_bytes = (uint32_t)p.DB * 128u;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < p.stages; i++) {
+      mbar_init(smem_u32(&s_full[i]), 5);   // four producer warps + the loader's expect_tx arrival
+      mbar_init(smem_u32(&s_empty[i]), 1);  // tcgen05.commit
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(smem_u32(&s_tfull[b]), 1);
+      mbar_init(smem_u32(&s_tempty[b]), 8);   // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(smem_u32(&s_tmem_base), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 9) {
+    // ---------------- B loader: one [32 x DB] box of sign(R) per stage ----------------
+    if (lane == 0) {
+      long long g = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        for (int db = 0; db < p.ndb && ok; db++) {
+          for (int kp = 0; kp < p.kpanels; kp++, g++) {
+            const int st = (int)(g % p.stages);
+            const uint32_t ph = (uint32_t)(g / p.stages) & 1u;
+            if (!mbar_wait<64>(smem_u32(&s_empty[st]), ph ^ 1u, abort_flag)) { ok = false; break; }
+            const uint32_t full = smem_u32(&s_full[st]);
+            mbar_arrive_expect_tx(full, b_bytes);
+            tma_load_2d(ring + (uint32_t)st * p.stage_bytes + kStreamAPanel, &tm_r, kp * 32, db * p.DB, full);
+          }
+        }
+      }
+    }
+  } else if (warp == 0) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_tf32(kBwdTileM, p.DB);
+      long long g = 0;
+      int t = 0;
+      bool ok = true;
+      const long long my_tiles = p.num_tiles > blockIdx.x ? (p.num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      for (long long it = 0; it < my_tiles * p.ndb && ok; it++, t++) {
+        const int tb = t & 1;
+        const uint32_t tph = (uint32_t)(t >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&s_tempty[tb]), tph ^ 1u, abort_flag)) { ok = false; break; }
+        const uint32_t d_tmem = tmem_base + (uint32_t)(tb * 256);
+        for (int kp = 0; kp < p.kpanels; kp++, g++) {
+          const int st = (int)(g % p.stages);
+          const uint32_t ph = (uint32_t)(g / p.stages) & 1u;
+          if (!mbar_wait(smem_u32(&s_full[st]), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = ring + (uint32_t)st * p.stage_bytes;
+          const uint64_t a_desc = umma_desc_sw128(a_addr), b_desc = umma_desc_sw128(a_addr + kStreamAPanel);
+          for (int k4 = 0; k4 < 4 && kp * 4 + k4 < p.kmma; k4++)
+            umma_tf32(d_tmem, a_desc + (uint64_t)(k4 * 2), b_desc + (uint64_t)(k4 * 2), idesc, (kp | k4) != 0);
+          umma_commit(smem_u32(&s_empty[st]));
+        }
+        if (ok) umma_commit(smem_u32(&s_tfull[tb]));
+      }
+    }
+  } else if (warp <= 4) {
+    // ---------------- A producers: thread = row, one panel of 32 projected columns per stage ----------------
+    // The packed bytes of a warp's 32 rows (32 / WPT row groups, contiguous in the stream) are brought into
+    // shared memory once per tile with coalesced 16-byte loads and read from there for every column block and
+    // panel: no global-memory latency between the panels.
+    const int r = (warp - 1) * 32 + lane;
+    const uint32_t wbuf = bytes_area + (uint32_t)(warp - 1) * p.warp_bytes;
+    long long g = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      const long long n = tile * kBwdTileM + r;
+      const bool row_ok = n < p.N;
+      float s = 1.f, m = 0.f;
+      if (row_ok) {
+        s = bf16_bits_to_f32(__ldg(p.scale_bf16 + n));
+        m = bf16_bits_to_f32(__ldg(p.min_bf16 + n));
+      }
+      // this warp's bytes: row groups [grp0, grp1) of the stream
+      const long long n_w = tile * kBwdTileM + (warp - 1) * 32;
+      const long long rows_w = p.N - n_w < 32 ? p.N - n_w : 32;
+      uint32_t head = 0;
+      __syncwarp();   // the previous tile's reads of the buffer are done
+      if (rows_w > 0) {
+        const long long grp0 = n_w / WPT, grp1 = (n_w + rows_w + WPT - 1) / WPT;
+        const uint8_t* first = p.packed + grp0 * p.k;
+        const uint8_t* last = p.packed + grp1 * p.k;
+        head = (uint32_t)(reinterpret_cast<uintptr_t>(first) & 15u);
+        const uint8_t* base16 = first - head;
+        const long long words = (last - base16 + 15) / 16;
+        for (long long i = lane; i < words; i += 32) {
+          const uint8_t* src = base16 + i * 16;
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (src >= first && src + 16 <= last) {
+            v = __ldg(reinterpret_cast<const uint4*>(src));
+          } else {
+            uint32_t q[4] = {0u, 0u, 0u, 0u};
+            for (int b = 0; b < 16; b++)
+              if (src + b >= first && src + b < last) q[b >> 2] |= (uint32_t)__ldg(src + b) << (8 * (b & 3));
+            v = make_uint4(q[0], q[1], q[2], q[3]);
+          }
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(wbuf + (uint32_t)i * 16u), "r"(v.x), "r"(v.y),
+                       "r"(v.z), "r"(v.w)
+                       : "memory");
+        }
+      }
+      __syncwarp();
+      // code / s by the correctly rounded reciprocal sequence (see rp_unpack_kernel); other scales divide
+      const float rcp = __frcp_rn(s);
+      const uint32_t sexp = (__float_as_uint(s) >> 23) & 0xffu;
+      const bool tame = __all_sync(0xffffffffu, sexp >= 27u && sexp <= 227u);
+      const f32x2 r2 = f2_pack(rcp, rcp), ns2 = f2_pack(-s, -s), m2 = f2_pack(m, m);
+      const f32x2 neg_2p23 = f2_pack(-8388608.f, -8388608.f);
+      const uint32_t row_bytes = wbuf + head + (uint32_t)(lane / WPT) * (uint32_t)p.k;   // this row's group
+      const int sh = (lane % WPT) * BITS;   // n % WPT: tiles and warps start at multiples of 32 rows
+      for (int db = 0; db < p.ndb && ok; db++) {
+        for (int kp = 0; kp < p.kpanels; kp++, g++) {
+          const int st = (int)(g % p.stages);
+          const uint32_t ph = (uint32_t)(g / p.stages) & 1u;
+          if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_empty[st]), ph ^ 1u, abort_flag))) { ok = false; break; }
+          const uint32_t row_addr = ring + (uint32_t)st * p.stage_bytes + (uint32_t)r * 128u;
+#pragma unroll
+          for (int ci = 0; ci < 8; ci++) {
+            const int c = kp * 32 + ci * 4;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (row_ok && c < p.k) {
+              // four bytes at any alignment: two aligned words and a funnel shift (the buffer is padded)
+              const uint32_t a = row_bytes + (uint32_t)c;
+              uint32_t lo, hi;
+              asm volatile("ld.shared.b32 %0, [%1];" : "=r"(lo) : "r"(a & ~3u));
+              asm volatile("ld.shared.b32 %0, [%1];" : "=r"(hi) : "r"((a & ~3u) + 4u));
+              const uint32_t w = __funnelshift_r(lo, hi, 8u * (a & 3u));
+              if (tame && c + 4 <= p.k) {
+                const uint32_t t4 = (w >> sh) & (0x01010101u * MASK);
+                float cf[4];
+#pragma unroll
+                for (int b = 0; b < 4; b++) cf[b] = __uint_as_float(__byte_perm(t4, 0x4b000000u, 0x7540 | b));  // 2^23 + code
+#pragma unroll
+                for (int b = 0; b < 4; b += 2) {
+                  const f32x2 c2 = f2_add(f2_pack(cf[b], cf[b + 1]), neg_2p23);
+                  const f32x2 q0 = f2_mul(c2, r2);
+                  const f32x2 q = f2_fma(f2_fma(q0, ns2, c2), r2, q0);
+                  f2_unpack(f2_add(q, m2), v[b], v[b + 1]);
+                }
+              } else {
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                  if (c + b < p.k) {
+                    const uint32_t code = ((w >> (8 * b)) >> sh) & MASK;
+                    v[b] = __fadd_rn(__fdiv_rn((float)code, s), m);  // quantization_cuda_kernel.cu:182
+                  }
+                }
+              }
+            }
+            const uint32_t addr = row_addr + (((uint32_t)ci ^ ((uint32_t)r & 7u)) << 4);
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3])
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&s_full[st]));
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue: warps 5..8 and 10..13, thread = row; the two warps of a TMEM lane quadrant
+    // take alternate chunks of 32 columns ----------------
+    const int quad = warp & 3, half = warp >= 10 ? 1 : 0;
+    const bool vec4 = (p.D & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+    const bool vec2 = (p.D & 1) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7) == 0;
+    const uint32_t stage_addr = stage_area + (uint32_t)(quad + 4 * half) * 4096u;
+    int t = 0;
+    bool ok = true;
+    const long long my_tiles = p.num_tiles > blockIdx.x ? (p.num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    for (long long it = 0; it < my_tiles * p.ndb && ok; it++, t++) {
+      const long long tile = blockIdx.x + (it / p.ndb) * gridDim.x;
+      const int col_base = (int)(it % p.ndb) * p.DB;
+      const int buf = t & 1;
+      const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_tfull[buf]), ph, abort_flag))) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * 256);
+      const long long row_base = tile * kBwdTileM + quad * 32;
+      for (int c0 = half * 32; c0 < p.DB && col_base + c0 < p.D; c0 += 64) {
+        const int cols = (p.DB - c0) < 32 ? (p.DB - c0) : 32;   // 16 or 32
+        for (int h = 0; h * 16 < cols; h++) {
+          float v[16];
+          tmem_ld16(taddr + (uint32_t)(c0 + h * 16), v);
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const uint32_t ci = (uint32_t)(h * 4 + j);
+            const uint32_t addr = stage_addr + (uint32_t)lane * 128u + ((ci ^ ((uint32_t)lane & 7u)) << 4);
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(__fmul_rn(v[4 * j], p.inv_sqrt_k)),
+                         "f"(__fmul_rn(v[4 * j + 1], p.inv_sqrt_k)), "f"(__fmul_rn(v[4 * j + 2], p.inv_sqrt_k)),
+                         "f"(__fmul_rn(v[4 * j + 3], p.inv_sqrt_k))
+                         : "memory");
+          }
+        }
+        __syncwarp();
+        const uint32_t ci = (uint32_t)lane & 7u;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const int rr = 4 * i + (lane >> 3);
+          const long long nn = row_base + rr;
+          const int c = col_base + c0 + (int)ci * 4;
+          float4 o;
+          const uint32_t addr = stage_addr + (uint32_t)rr * 128u + ((ci ^ ((uint32_t)rr & 7u)) << 4);
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(o.x), "=f"(o.y), "=f"(o.z), "=f"(o.w) : "r"(addr));
+          if (nn < p.N && (int)ci * 4 < cols && c < p.D) {
+            float* __restrict__ d = p.out + nn * p.D + c;
+            if (vec4 && c + 4 <= p.D) {
+              __stcs(reinterpret_cast<float4*>(d), o);
+            } else if (vec2 && c + 4 <= p.D) {
+              __stcs(reinterpret_cast<float2*>(d), make_float2(o.x, o.y));
+              __stcs(reinterpret_cast<float2*>(d) + 1, make_float2(o.z, o.w));
+            } else {
+              const float ov[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+              for (int bb = 0; bb < 4; bb++)
+                if (c + bb < p.D) d[bb] = ov[bb];
+            }
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_tempty[buf]));
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && s_abort) {
+    atomicExch(p.status, 1);
+    if (p.lib_status) atomicOr(p.lib_status, EXB_STATUS_UNPACK_RP);
+  }
+}
+
 // sign(R), zero padded to [Dpad, kpad32]; also clears the status word.
 __global__ void rp_bwd_prepare_kernel(const float* __restrict__ R, int D, int k, int Dpad, int kpad32,
                                       float* __restrict__ rs, int* status) {
@@ -300,16 +596,58 @@ int exact_unpack_dequant_rp(const uint8_t* packed, int bits, const uint16_t* sca
   const int kpanels = kpad32 / 32;
   const long long a_bytes = (long long)kBwdTileM * kpanels * 128;
   const long long b_bytes = (long long)Dpad * kpanels * 128;
-  if (Dpad > 256 || b_bytes + 2 * a_bytes + 4 * 4096 + 2048 > 200 * 1024)
-    return fail(EXB_ERR_UNSUPPORTED, "unpack_dequant_rp: D = %lld, k = %lld exceed one resident B tile (D <= 256, small k)",
-                (long long)D, (long long)k);
+  const bool resident = Dpad <= 256 && b_bytes + 2 * a_bytes + 4 * 4096 + 2048 <= 200 * 1024;
+  EXB_REQUIRE((long long)Dpad * kpad32 < (1LL << 28), "unpack_dequant_rp: D x k out of range");
   EXB_REQUIRE((N + kBwdTileM - 1) / kBwdTileM < 2147483647LL / kBwdTileM, "unpack_dequant_rp: too many rows");
   if ((k & 3) == 0) EXB_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 3) == 0, "unpack_dequant_rp: packed must be 4-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   int* status = reinterpret_cast<int*>(workspace);
   float* rs = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 256);
-  rp_bwd_prepare_kernel<<<(Dpad * kpad32 + 255) / 256, 256, 0, st>>>(R, (int)D, (int)k, Dpad, kpad32, rs, status);
+  rp_bwd_prepare_kernel<<<(unsigned)(((long long)Dpad * kpad32 + 255) / 256), 256, 0, st>>>(R, (int)D, (int)k, Dpad, kpad32, rs,
+                                                                                         status);
   EXB_CUDA_OK(cudaGetLastError());
+
+  if (!resident) {
+    // column blocks of equal width (a multiple of 16, at most 256); rows of sign(R) past Dpad read as zeros
+    RpBwdStreamParams q{};
+    q.ndb = (Dpad + 255) / 256;
+    q.DB = ((Dpad + q.ndb - 1) / q.ndb + 15) / 16 * 16;
+    CUtensorMap tm_rs;
+    int rcs = make_tensor_map_2d_f32(&tm_rs, rs, (unsigned long long)kpad32, (unsigned long long)Dpad,
+                                     (unsigned long long)kpad32 * 4, 32, (unsigned)q.DB);
+    if (rcs) return rcs;
+    q.packed = packed; q.scale_bf16 = scale_bf16; q.min_bf16 = min_bf16; q.out = out; q.status = status;
+    q.lib_status = status_word_ptr();
+    q.N = N; q.D = (int)D; q.k = (int)k; q.kpanels = kpanels; q.kmma = (int)((k + 7) / 8);
+    q.num_tiles = (N + kBwdTileM - 1) / kBwdTileM;
+    q.stage_bytes = kStreamAPanel + (unsigned)q.DB * 128u;
+    // packed bytes of 32 rows (32 / wpt row groups of k bytes), 16 bytes of alignment slack at either end
+    q.warp_bytes = (unsigned)(((32 / (8 / bits)) * k + 15 + 16 + 15) / 16 * 16);
+    const long long ring_budget = 226ll * 1024 - 8 * 4096 - 1024 - 4ll * q.warp_bytes;
+    if (ring_budget < 2ll * q.stage_bytes)
+      return fail(EXB_ERR_UNSUPPORTED, "unpack_dequant_rp: k = %lld too large for the shared-memory ring", (long long)k);
+    q.stages = (int)(ring_budget / q.stage_bytes);
+    if (q.stages > 8) q.stages = 8;
+    q.inv_sqrt_k = (float)(1.0 / sqrt((double)k));
+    const size_t dyn_s = (size_t)q.stages * q.stage_bytes + 8 * 4096 + 4 * (size_t)q.warp_bytes + 1024;
+    long long grid_s = sm_count();
+    if (grid_s > q.num_tiles) grid_s = q.num_tiles;
+#define EXB_BWD_STREAM(BITS_)                                                                                          \
+  {                                                                                                                    \
+    EXB_CUDA_OK(cudaFuncSetAttribute(rp_unpack_stream_kernel<BITS_>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                     (int)dyn_s));                                                                     \
+    rp_unpack_stream_kernel<BITS_><<<(unsigned)grid_s, kStreamThreads, dyn_s, st>>>(tm_rs, q);                         \
+  }
+    switch (bits) {
+      case 1: EXB_BWD_STREAM(1) break;
+      case 2: EXB_BWD_STREAM(2) break;
+      case 4: EXB_BWD_STREAM(4) break;
+      default: EXB_BWD_STREAM(8) break;
+    }
+#undef EXB_BWD_STREAM
+    EXB_CUDA_OK(cudaGetLastError());
+    return EXB_OK;
+  }
 
   CUtensorMap tm_r;
   int rc = make_tensor_map_2d_f32(&tm_r, rs, (unsigned long long)kpad32, (unsigned long long)Dpad,

@@ -44,7 +44,19 @@ struct SpmmParams {
   const int* long_item_ptr;
   long long n_long;
   float* scratch;  // [n_items, K]
+  // Routed output (feature-parallel aggregation): row r is written to columns route_col0 .. + K - 1 of row
+  // r % route_shard of the [route_shard, route_ld] matrix at route_dst[r / route_shard], which may be another
+  // GPU's memory (plain stores).  route_n == 0: the rows go to `out`.
+  float* route_dst[8];
+  int route_n;
+  long long route_shard, route_ld, route_col0;
 };
+
+__device__ __forceinline__ float* output_row(const SpmmParams& p, long long row) {
+  if (p.route_n == 0) return p.out + row * p.K;
+  const long long owner = row / p.route_shard;
+  return p.route_dst[owner] + (row - owner * p.route_shard) * p.route_ld + p.route_col0;
+}
 
 constexpr int kSpmmWarps = 4;
 constexpr int kEdgeUnroll = 16;   // gathers in flight per lane (16 against 8: 3 % faster at 128 M edges x 256 columns)
@@ -178,7 +190,7 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_csr_kernel(const __grid_
     end = (long long)rowptr[unit + 1];
     count = end - begin;
     if (p.long_threshold > 0 && count > p.long_threshold) return;
-    dst = p.out + unit * K;
+    dst = output_row(p, unit);
   } else {
     if (unit >= p.n_items) return;
     begin = p.item_begin[unit];
@@ -209,10 +221,11 @@ __global__ void __launch_bounds__(128) spmm_long_reduce_kernel(const __grid_cons
   const int s0 = p.long_item_ptr[i], s1 = p.long_item_ptr[i + 1];
   const long long cnt = (long long)rowptr[row + 1] - (long long)rowptr[row];
   const float dv = (float)(cnt > 0 ? cnt : 1);
+  float* __restrict__ dst = output_row(p, row);
   for (long long c = threadIdx.x; c < p.K; c += blockDim.x) {
     float a = 0.f;
     for (int s = s0; s < s1; s++) a = __fadd_rn(a, p.scratch[(long long)s * p.K + c]);
-    p.out[row * p.K + c] = p.mean ? __fdiv_rn(a, dv) : a;
+    dst[c] = p.mean ? __fdiv_rn(a, dv) : a;
   }
 }
 
@@ -247,7 +260,7 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_csr_multi_kernel(const _
     end = (long long)rowptr[unit + 1];
     count = end - begin;
     if (p.long_threshold > 0 && count > p.long_threshold) return;
-    dst = p.out + unit * K;
+    dst = output_row(p, unit);
   } else {
     if (unit >= p.n_items) return;
     begin = p.item_begin[unit];
@@ -377,6 +390,8 @@ template <typename IdxT, bool HAS_VAL>
 static int launch_spmm_vec(const SpmmParams& p, cudaStream_t st) {
   uintptr_t a = reinterpret_cast<uintptr_t>(p.mat) | reinterpret_cast<uintptr_t>(p.out);
   if (p.scratch) a |= reinterpret_cast<uintptr_t>(p.scratch);
+  for (int i = 0; i < p.route_n; i++) a |= reinterpret_cast<uintptr_t>(p.route_dst[i]);
+  if (p.route_n) a |= (uintptr_t)(p.route_ld * 4) | (uintptr_t)(p.route_col0 * 4);
   if (p.regroup && p.K <= 64 && p.K % 4 == 0 && a % 16 == 0) return launch_spmm_pair<IdxT, HAS_VAL>(p, st);
   if (p.K % 4 == 0 && a % 16 == 0) return launch_spmm_kvt<IdxT, 4, HAS_VAL>(p, st);
   if (p.K % 2 == 0 && a % 8 == 0) return launch_spmm_kvt<IdxT, 2, HAS_VAL>(p, st);
@@ -390,7 +405,7 @@ static int spmm_common(SpmmParams& p, int idx_bytes, int reduce, cudaStream_t st
   EXB_REQUIRE(reduce == EXACT_REDUCE_SUM || reduce == EXACT_REDUCE_MEAN, "spmm: reduce must be sum or mean");
   EXB_REQUIRE(p.M >= 0 && p.K >= 0, "spmm: negative shape");
   if (p.M == 0 || p.K == 0) return EXB_OK;
-  EXB_REQUIRE(p.rowptr && p.mat && p.out, "spmm: null pointer");
+  EXB_REQUIRE(p.rowptr && p.mat && (p.out || p.route_n > 0), "spmm: null pointer");
   EXB_REQUIRE((p.M + kSpmmWarps - 1) / kSpmmWarps <= 2147483647LL, "spmm: too many rows");
   EXB_REQUIRE(p.K * 4 < (1LL << 32), "spmm: K too large");
   // Column indices are staged as 32-bit values (also on the int64 path): operands of 2^32 rows or more are
@@ -541,6 +556,37 @@ int exact_spmm_split(const void* rowptr, const void* col, int idx_bytes, const f
   p.item_row = item_row; p.item_begin = reinterpret_cast<const long long*>(item_begin);
   p.item_end = reinterpret_cast<const long long*>(item_end); p.item_slot = item_slot; p.n_items = n_items;
   p.long_row = long_row; p.long_item_ptr = long_item_ptr; p.n_long = n_long; p.scratch = scratch;
+  return spmm_common(p, idx_bytes, reduce, (cudaStream_t)stream);
+}
+
+int exact_spmm_split_routed(const void* rowptr, const void* col, int idx_bytes, const float* value, const float* mat,
+                            int64_t M, int64_t K, int reduce, int64_t long_threshold, const int32_t* item_row,
+                            const int64_t* item_begin, const int64_t* item_end, const int32_t* item_slot,
+                            int64_t n_items, const int32_t* long_row, const int32_t* long_item_ptr, int64_t n_long,
+                            float* scratch, int64_t shard, int64_t col0, int64_t ldd, void* const* dst, int n_dst,
+                            void* stream) {
+  EXB_REQUIRE(long_threshold >= 0 && n_items >= 0 && n_long >= 0, "spmm_split_routed: negative plan size");
+  EXB_REQUIRE(n_items <= 2147483647LL && n_long <= 2147483647LL, "spmm_split_routed: plan too large");
+  if (n_items > 0)
+    EXB_REQUIRE(long_threshold > 0 && item_row && item_begin && item_end && long_row && long_item_ptr && scratch &&
+                    n_long > 0,
+                "spmm_split_routed: null plan array or scratch");
+  EXB_REQUIRE(n_dst >= 1 && n_dst <= 8 && dst != nullptr, "spmm_split_routed: 1 to 8 destinations");
+  EXB_REQUIRE(shard > 0 && (int64_t)n_dst * shard >= M, "spmm_split_routed: %d destinations of %lld rows do not hold %lld rows",
+              n_dst, (long long)shard, (long long)M);
+  EXB_REQUIRE(col0 >= 0 && K >= 0 && ldd >= col0 + K, "spmm_split_routed: columns %lld .. %lld exceed the row pitch %lld",
+              (long long)col0, (long long)(col0 + K), (long long)ldd);
+  SpmmParams p{};
+  p.rowptr = rowptr; p.col = col; p.val = value; p.mat = mat; p.out = nullptr; p.M = M; p.K = K;
+  p.long_threshold = n_items > 0 ? long_threshold : 0;
+  p.item_row = item_row; p.item_begin = reinterpret_cast<const long long*>(item_begin);
+  p.item_end = reinterpret_cast<const long long*>(item_end); p.item_slot = item_slot; p.n_items = n_items;
+  p.long_row = long_row; p.long_item_ptr = long_item_ptr; p.n_long = n_long; p.scratch = scratch;
+  p.route_n = n_dst; p.route_shard = shard; p.route_ld = ldd; p.route_col0 = col0;
+  for (int i = 0; i < n_dst; i++) {
+    EXB_REQUIRE(dst[i] != nullptr, "spmm_split_routed: null destination %d", i);
+    p.route_dst[i] = static_cast<float*>(dst[i]);
+  }
   return spmm_common(p, idx_bytes, reduce, (cudaStream_t)stream);
 }
 

@@ -243,10 +243,15 @@ class ShardedSparseTensor:
             # rows already scaled by 1 / deg (here or by the caller): A_mean^T g = A^T (D^-1 g), no edge weights
             unweighted = unweighted or rowscale is not None
             t_ptr, t_col, t_w = self.full_t["sum" if (unweighted and "sum" in self.full_t) else self.reduce]
-            y = ext_spmm._spmm(t_ptr, t_col, None if unweighted else t_w, slice_all, "sum", regroup=True)
+            args = (t_ptr, t_col, None if unweighted else t_w, slice_all, "sum")
         else:
-            y = ext_spmm._spmm(self.full_rowptr, self.full_col, self.full_value, slice_all, reduce, regroup=True)
-        ext_rows.rows_scatter(y, S, self.rank * Kp, P * Kp, outb.ptrs)
+            args = (self.full_rowptr, self.full_col, self.full_value, slice_all, reduce)
+        if config.routed_aggregation_output and P <= 8:
+            # every result row goes from the warp that summed it straight into its owner's buffer
+            ext_spmm._spmm(*args, regroup=True, route=(S, self.rank * Kp, P * Kp, outb.ptrs))
+        else:
+            y = ext_spmm._spmm(*args, regroup=True)
+            ext_rows.rows_scatter(y, S, self.rank * Kp, P * Kp, outb.ptrs)
         self._order_peer_stores(dev)
         out = outb.local_tensor().view(torch.float32).view(S, P * Kp)[:n_loc]
         # the buffer is written again two aggregations of this width later: callers consume the result at once

@@ -257,6 +257,15 @@ class qbatch_norm(Function):
     def backward(ctx, grad_output):
         quantized, weight, running_mean, running_var, save_mean, save_var, training, eps = ctx.saved
         q_input_shape = ctx.other_args
+        mask = [ctx.needs_input_grad[0], ctx.needs_input_grad[3], ctx.needs_input_grad[4]]
+        if (config.compress_activation and not config.simulate and not config.swap and config.bn_backward_from_packed
+                and len(q_input_shape) == 2
+                and ext_backward_func.batch_norm_backward_from_packed_supported(grad_output, quantized)):
+            # both passes of the backward read the packed bytes: no [N, D] reconstruction (ops.py:238)
+            del ctx.saved
+            grad_input, grad_weight, grad_bias = ext_backward_func.batch_norm_backward_from_packed(
+                grad_output, quantized, weight, running_mean, running_var, save_mean, save_var, training, eps, mask)
+            return grad_input, None, None, grad_weight, grad_bias, None, None, None, None
         input = dequantize_activation(quantized, q_input_shape)
         del quantized, ctx.saved
         empty_cache(config.empty_cache_threshold)

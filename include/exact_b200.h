@@ -224,6 +224,39 @@ EXACT_API int exact_cols_scatter(const float* x, int64_t n, int64_t K, int64_t l
 EXACT_API int exact_rows_scatter(const float* y, int64_t n_total, int64_t Kp, int64_t shard, int64_t col0, int64_t ldd,
                                  void* const* dst, int n_dst, void* stream);
 
+/* Batch-norm backward straight from the packed input: native_batch_norm_backward as called by the reference's
+ * qbatch_norm.backward (exact/exact/ops.py:248-251) with the dequantize_activation of ops.py:238 folded into
+ * both of its passes, so the [N, D] reconstruction is never written.
+ *   grad_out [N, D] fp32 (16-byte aligned, D % 4 == 0, else code 3); packed / scale_bf16 / min_bf16: the saved
+ *   input as exact_quantize_pack wrote it; weight [D] or NULL (ones);
+ *   training != 0: mean = save_mean, invstd = save_invstd of the forward;
+ *       grad_input = (g - sum(g)/N - (x - mean) * invstd^2 * sum(g (x - mean))/N) * invstd * weight
+ *   training == 0: mean = running_mean, invstd = 1/sqrt(running_var + eps); grad_input = g * invstd * weight
+ *   grad_weight = invstd * sum_n g (x - mean), grad_bias = sum_n g; any of the three outputs may be NULL.
+ * Column sums are added in a fixed order (per-CTA partial rows, then CTA order): results are run-to-run
+ * identical and differ from ATen's by fp32 reassociation.  workspace: exact_bn_backward_workspace_bytes(D),
+ * 256-byte aligned. */
+EXACT_API int64_t exact_bn_backward_workspace_bytes(int64_t D);
+EXACT_API int exact_bn_backward_from_packed(const float* grad_out, int64_t N, int64_t D, const uint8_t* packed, int bits,
+                                            const uint16_t* scale_bf16, const uint16_t* min_bf16, const float* weight,
+                                            const float* mean, const float* invstd, int training, void* workspace,
+                                            int64_t workspace_bytes, float* grad_input, float* grad_weight,
+                                            float* grad_bias, void* stream);
+
+/* exact_spmm_split with the second exchange folded into it (no counterpart in the reference): instead of a local
+ * [M, K] result followed by exact_rows_scatter, every output row r is stored, by the warp that summed it,
+ * straight into its owner's buffer, dst[r / shard][(r % shard) * ldd + col0 + c], c < K (plain stores, peers'
+ * memory included), so the result slice is neither written to nor read back from local memory and the
+ * transfer overlaps the gathers.  n_dst * shard >= M; ldd >= col0 + K; for 16-byte stores dst, ldd and col0
+ * are 16-byte / 4-element aligned (else narrower stores).  A plan is optional (n_items = 0: every row is
+ * summed by one warp).  Ordering against the readers is the caller's, as for exact_rows_scatter. */
+EXACT_API int exact_spmm_split_routed(const void* rowptr, const void* col, int idx_bytes, const float* value,
+                                      const float* mat, int64_t M, int64_t K, int reduce, int64_t long_threshold,
+                                      const int32_t* item_row, const int64_t* item_begin, const int64_t* item_end,
+                                      const int32_t* item_slot, int64_t n_items, const int32_t* long_row,
+                                      const int32_t* long_item_ptr, int64_t n_long, float* scratch, int64_t shard,
+                                      int64_t col0, int64_t ldd, void* const* dst, int n_dst, void* stream);
+
 /* Buffers that the ranks of a row-sharded run write into each other (one process per GPU, one node).  No
  * counterpart in the reference.  These are the only entry points that allocate or free device memory:
  *   exact_peer_alloc   cudaMalloc of `bytes` on the current device;

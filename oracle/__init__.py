@@ -329,3 +329,21 @@ def crows_used_mask(buf, K):
     cnt = buf[:, 0:4].copy().view(np.uint32).reshape(n).astype(np.int64)
     pos = np.arange(slot)[None, :]
     return (pos < 4) | ((pos >= 16) & (pos < 16 + cnt[:, None])) | ((pos >= voff) & (pos < voff + 4 * cnt[:, None]))
+
+
+def bn_backward(grad_out, x, weight, mean, invstd, training):
+    """native_batch_norm_backward as the reference calls it on the dequantised input (exact/exact/ops.py:238,
+    248-251), in float64: (grad_input, grad_weight, grad_bias).  training: mean / invstd are the batch statistics
+    saved by the forward; otherwise the running mean and 1 / sqrt(running_var + eps)."""
+    g = np.asarray(grad_out, np.float64)
+    xc = np.asarray(x, np.float64) - np.asarray(mean, np.float64)[None, :]
+    invstd = np.asarray(invstd, np.float64)
+    w = np.ones_like(invstd) if weight is None else np.asarray(weight, np.float64)
+    n = g.shape[0]
+    sum_g = g.sum(0)
+    sum_gx = (g * xc).sum(0)
+    if training:
+        grad_in = (g - sum_g / n - xc * (invstd * invstd * sum_gx / n)) * (invstd * w)
+    else:
+        grad_in = g * (invstd * w)
+    return grad_in, sum_gx * invstd, sum_g

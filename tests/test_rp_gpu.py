@@ -83,7 +83,10 @@ def test_rows_of_a_view_that_is_not_16_byte_aligned():
 
 
 BWD_CASES = [(256, 128, 32, 2), (1000, 256, 32, 2), (1000, 100, 13, 2), (4096, 128, 16, 4), (513, 64, 8, 8),
-             (50000, 256, 32, 2), (130, 256, 64, 1), (9, 36, 5, 2), (3000, 200, 25, 2)]
+             (50000, 256, 32, 2), (130, 256, 64, 1), (9, 36, 5, 2), (3000, 200, 25, 2),
+             # sign(R) not resident: streamed in panels, output in column blocks
+             (20000, 256, 128, 2), (5000, 602, 76, 2), (3000, 602, 301, 2), (1000, 602, 76, 8), (700, 300, 37, 4),
+             (129, 1030, 33, 1), (40000, 602, 76, 4)]
 
 
 @pytest.mark.parametrize("N,D,k,bits", BWD_CASES)

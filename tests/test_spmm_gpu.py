@@ -129,6 +129,35 @@ def test_regrouped_sum_for_narrow_operands(K, with_values, reduce):
     assert np.array_equal(strict, flagged)
 
 
+@pytest.mark.parametrize("reduce", ["sum", "mean"])
+@pytest.mark.parametrize("K,regroup", [(32, True), (8, True), (64, True), (128, False), (100, False), (13, False)])
+def test_routed_output_equals_local_result_then_scatter(K, regroup, reduce):
+    """exact_spmm_split_routed: every result row goes straight into columns col0 .. of row r % shard of the buffer
+    of its owner r // shard (here three local buffers standing for three ranks).  Same bits as the local result
+    cut into row blocks; hub rows (pieces + ordered sum) and empty rows included; the other columns of the
+    buffers stay untouched."""
+    n, shard, col0, ldd = 4000, 1336, 4 * ((K + 3) // 4), 3 * 4 * ((K + 3) // 4) + 8
+    rng = np.random.default_rng(31)
+    hub = np.stack([np.full(1500, 1400, np.int64), rng.choice(n, 1500, replace=False)])
+    rest = rng.integers(0, n, (2, 30000))
+    rest = rest[:, rest[0] > 50]
+    e = np.concatenate([hub, rest], 1)
+    key = np.unique(e[0] * n + e[1])
+    row, col = key // n, key % n
+    rowptr = np.zeros(n + 1, np.int64)
+    np.cumsum(np.bincount(row, minlength=n), out=rowptr[1:])
+    mat = t(normal(n, K, 32))
+    local = S._spmm(t(rowptr), t(col), None, mat, reduce, regroup=regroup)
+    bufs = [torch.full((shard, ldd), -7.0, device="cuda") for _ in range(3)]
+    assert S._spmm(t(rowptr), t(col), None, mat, reduce, regroup=regroup,
+                   route=(shard, col0, ldd, [b.data_ptr() for b in bufs])) is None
+    for q, b in enumerate(bufs):
+        rows = local[q * shard:(q + 1) * shard]
+        assert torch.equal(b[:rows.size(0), col0:col0 + K], rows)
+        assert bool((b[:, :col0] == -7.0).all()) and bool((b[:, col0 + K:] == -7.0).all())
+        assert bool((b[rows.size(0):] == -7.0).all())
+
+
 @pytest.mark.parametrize("K", [256, 64])
 def test_power_law_graph_with_many_out_of_order_pieces(K):
     """An R-MAT graph of the benchmark's skew: 120,000 nodes, ~6 M edges, hub rows of 10^4 edges cut into dozens
