@@ -58,6 +58,16 @@ def long_row_plan(rowptr, threshold, col=None):
 REGROUP = 0x100   # EXACT_SPMM_REGROUP
 
 
+def row_order(rowptr):
+    """Rows sorted by length (longest first), int32, cached per row-pointer tensor: the order in which the
+    kernel for narrow operands takes the rows, so that the rows a warp works on together are equally long."""
+    per = _plans_of(rowptr)
+    if "row_order" not in per:
+        rp = rowptr.to(torch.int64)
+        per["row_order"] = torch.argsort(rp[1:] - rp[:-1], stable=True, descending=True).to(torch.int32).contiguous()
+    return per["row_order"]
+
+
 def _spmm(rowptr, col, value, mat, reduce, regroup=False, route=None):
     """spmm.cc:12-18 -> spmm_cuda.cu:106-170.  `regroup`: the caller accepts a regrouped per-row fp32 sum
     (narrow operands then gather several edges per load instruction).  `route` = (shard, col0, ldd, addresses):
@@ -93,9 +103,13 @@ def _spmm(rowptr, col, value, mat, reduce, regroup=False, route=None):
     thr = int(config.spmm_long_row)
     plan = long_row_plan(rowptr, thr, col) if thr > 0 else None
     red = _lib.REDUCE[reduce] | (REGROUP if regroup else 0)
+    narrow = K <= 64 and K % 4 == 0 and M > 0
+    if route is None and narrow:
+        route = (M, 0, K, [out.data_ptr()])   # the same entry point, one local destination: it takes a row order
     if route is not None:
         shard, col0, ldd, addresses = route
         arr = (ctypes.c_void_p * len(addresses))(*addresses)
+        order = row_order(rowptr) if narrow else None
         none = {"item_row": None, "item_begin": None, "item_end": None, "item_slot": None, "n_items": 0,
                 "long_row": None, "long_item_ptr": None, "n_long": 0}
         pl = plan if plan is not None else none
@@ -103,9 +117,10 @@ def _spmm(rowptr, col, value, mat, reduce, regroup=False, route=None):
         _lib.invoke("exact_spmm_split_routed", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value),
                     _lib.ptr(mat), M, K, red, thr if plan is not None else 0, _lib.ptr(pl["item_row"]),
                     _lib.ptr(pl["item_begin"]), _lib.ptr(pl["item_end"]), _lib.ptr(pl["item_slot"]), pl["n_items"],
-                    _lib.ptr(pl["long_row"]), _lib.ptr(pl["long_item_ptr"]), pl["n_long"], _lib.ptr(scratch), shard,
-                    col0, ldd, arr, len(addresses), _lib.stream_ptr(), l2_bytes=l2_bytes, edge_columns=nnz * K)
-        return None
+                    _lib.ptr(pl["long_row"]), _lib.ptr(pl["long_item_ptr"]), pl["n_long"], _lib.ptr(scratch),
+                    _lib.ptr(order), shard, col0, ldd, arr, len(addresses), _lib.stream_ptr(), device=mat.device,
+                    l2_bytes=l2_bytes, edge_columns=nnz * K)
+        return out
     if plan is None:
         _lib.invoke("exact_spmm", nbytes, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value), _lib.ptr(mat), M, K,
                     red, _lib.ptr(out), _lib.stream_ptr(), l2_bytes=l2_bytes, edge_columns=nnz * K)

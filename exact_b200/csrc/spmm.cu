@@ -49,6 +49,7 @@ struct SpmmParams {
   // GPU's memory (plain stores).  route_n == 0: the rows go to `out`.
   float* route_dst[8];
   int route_n;
+  const int* row_order;  // narrow operands: the order in which the rows are taken (a permutation), or null
   long long route_shard, route_ld, route_col0;
 };
 
@@ -229,110 +230,127 @@ __global__ void __launch_bounds__(128) spmm_long_reduce_kernel(const __grid_cons
   }
 }
 
-// Several edges per load instruction for narrow operands: a group of LPE lanes (16, 8 or 4) gathers 4 * LPE
-// columns (LPE x float4) of one edge, so the 32 / LPE groups of a warp take that many consecutive entries of
-// the staged edge list at once, each keeping its own partial sum; the partial sums are added at the end.  For
-// operands far larger than L2 the narrow column tile keeps more source rows cached per pass than a wide one,
-// and for K <= 64 it keeps the lanes busy (column slices of 16 to 64 columns are what a rank multiplies in
-// the feature-parallel aggregation).  The sum of a row is formed from interleaved partial sums, so it differs
-// from the strict edge order of spmm_csr_kernel by fp32 reassociation.
+// Narrow operands (K <= 64): a group of LPE = 4, 8 or 16 lanes (LPE x float4 = the whole row of the operand) owns
+// one row of the adjacency, so a warp works on 32 / LPE rows at once and keeps that many independent chains of
+// index load -> gathers in flight.  With one row per warp a narrow operand is bound by those chains, not by
+// bytes: at 128 M edges a pass over 16, 32 or 64 columns took 1.8, 2.0 and 2.8 ms against 4.4 ms for 128
+// columns.  A group walks its row eight edges at a time: its lanes load the eight column indices (the next
+// eight are requested before the gathers of the current ones are consumed), every lane gets each index by a
+// shuffle, gathers its float4 of that source row and adds the eight in edge order, so a row's sum is the
+// strict CSR-order sum (the pieces of long rows are still added separately).  The groups of a warp run until
+// the longest of their rows is done; callers that pass `row_order` (rows sorted by length) give every warp rows
+// of equal length.
 template <typename IdxT, bool HAS_VAL, int MODE, int LPE>
 __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_csr_multi_kernel(const __grid_constant__ SpmmParams p) {
-  __shared__ uint32_t s_idx[kSpmmWarps][32];
-  __shared__ float s_val[kSpmmWarps][32];
-  constexpr int kGroups = 32 / LPE;   // edges per load instruction
-  constexpr int kDepth = 8;           // load instructions in flight
+  constexpr int kRows = 32 / LPE;              // rows (or long-row pieces) per warp
+  constexpr int kBatch = 8;                    // edges per step and group
+  constexpr int NI = LPE >= kBatch ? 1 : kBatch / LPE;   // index registers per lane
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grp = lane / LPE, hl = lane % LPE;
-  const long long unit = (long long)blockIdx.x * kSpmmWarps + warp;
+  const long long unit = ((long long)blockIdx.x * kSpmmWarps + warp) * kRows + grp;
   const IdxT* __restrict__ rowptr = reinterpret_cast<const IdxT*>(p.rowptr);
   const IdxT* __restrict__ col = reinterpret_cast<const IdxT*>(p.col);
   const long long K = p.K;
   const long long coff = ((long long)blockIdx.y * LPE + hl) * 4;
   const bool cvalid = coff < K;
 
-  long long begin, end;
-  float* dst;
-  long long count = 0;
+  long long begin = 0, len = 0;
+  float* dst = nullptr;
+  bool live = false;
   if (MODE == MODE_ROWS) {
-    if (unit >= p.M) return;
-    begin = (long long)rowptr[unit];
-    end = (long long)rowptr[unit + 1];
-    count = end - begin;
-    if (p.long_threshold > 0 && count > p.long_threshold) return;
-    dst = output_row(p, unit);
+    if (unit < p.M) {
+      const long long row = p.row_order ? (long long)p.row_order[unit] : unit;
+      begin = (long long)rowptr[row];
+      len = (long long)rowptr[row + 1] - begin;
+      live = !(p.long_threshold > 0 && len > p.long_threshold);
+      dst = output_row(p, row);
+    }
   } else {
-    if (unit >= p.n_items) return;
-    begin = p.item_begin[unit];
-    end = p.item_end[unit];
-    dst = p.scratch + (long long)(p.item_slot ? p.item_slot[unit] : (int)unit) * K;
+    if (unit < p.n_items) {
+      begin = p.item_begin[unit];
+      len = p.item_end[unit] - begin;
+      live = true;
+      dst = p.scratch + (long long)(p.item_slot ? p.item_slot[unit] : (int)unit) * K;
+    }
   }
+  const long long count = len;
+  if (!live) len = 0;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   const unsigned long long row_bytes = (unsigned long long)K * 4ull;
   const char* __restrict__ mat0 = reinterpret_cast<const char*>(p.mat + (cvalid ? coff : 0));
-  uint32_t* sidx = s_idx[warp];
-  float* sval = s_val[warp];
-  for (long long base = begin; base < end; base += 32) {
-    const long long e = base + lane;
-    uint32_t idx = 0;
-    float v = 0.f;
-    if (e < end) {
-      idx = (uint32_t)col[e];
-      if (HAS_VAL) v = __ldg(p.val + e);
-    }
-    __syncwarp();
-    sidx[lane] = idx;
-    if (HAS_VAL) sval[lane] = v;
-    __syncwarp();
-    const int cnt = (end - base) < 32 ? (int)(end - base) : 32;
-    for (int t0 = 0; kGroups * t0 < cnt; t0 += kDepth) {
-      float4 m[kDepth];
-      float w[kDepth];
+  const IdxT* __restrict__ mycol = col + begin;
+  const float* __restrict__ myval = HAS_VAL ? p.val + begin : nullptr;
+
+  uint32_t idx[NI];
+  float val[NI];
 #pragma unroll
-      for (int u = 0; u < kDepth; u++) {
-        const int i = kGroups * (t0 + u) + grp;
-        m[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        w[u] = 0.f;
-        if (i < cnt) {
-          if (HAS_VAL) w[u] = sval[i];
-          if (cvalid) m[u] = __ldg(reinterpret_cast<const float4*>(mat0 + (unsigned long long)sidx[i] * row_bytes));
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kDepth; u++) {
-        if (HAS_VAL) {
-          acc[0] = __fmaf_rn(w[u], m[u].x, acc[0]); acc[1] = __fmaf_rn(w[u], m[u].y, acc[1]);
-          acc[2] = __fmaf_rn(w[u], m[u].z, acc[2]); acc[3] = __fmaf_rn(w[u], m[u].w, acc[3]);
-        } else {
-          acc[0] = __fadd_rn(acc[0], m[u].x); acc[1] = __fadd_rn(acc[1], m[u].y);
-          acc[2] = __fadd_rn(acc[2], m[u].z); acc[3] = __fadd_rn(acc[3], m[u].w);
-        }
-      }
+  for (int q = 0; q < NI; q++) {
+    const int pos = q * LPE + hl;
+    idx[q] = 0;
+    val[q] = 0.f;
+    if (pos < kBatch && pos < len) {
+      idx[q] = (uint32_t)mycol[pos];
+      if (HAS_VAL) val[q] = __ldg(myval + pos);
     }
   }
+  for (long long b = 0; __any_sync(0xffffffffu, b < len); b += kBatch) {
+    uint32_t nidx[NI];
+    float nval[NI];
 #pragma unroll
-  for (int off = 16; off >= LPE; off >>= 1) {
+    for (int q = 0; q < NI; q++) {
+      const int in_batch = q * LPE + hl;
+      const long long pos = b + kBatch + in_batch;
+      nidx[q] = 0;
+      nval[q] = 0.f;
+      if (in_batch < kBatch && pos < len) {
+        nidx[q] = (uint32_t)mycol[pos];
+        if (HAS_VAL) nval[q] = __ldg(myval + pos);
+      }
+    }
+    float4 m[kBatch];
+    float w[kBatch];
 #pragma unroll
-    for (int x = 0; x < 4; x++) acc[x] = __fadd_rn(acc[x], __shfl_xor_sync(0xffffffffu, acc[x], off));
+    for (int j = 0; j < kBatch; j++) {
+      const uint32_t ij = __shfl_sync(0xffffffffu, idx[j / LPE], j % LPE, LPE);
+      w[j] = HAS_VAL ? __shfl_sync(0xffffffffu, val[j / LPE], j % LPE, LPE) : 0.f;
+      m[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (b + j < len && cvalid) m[j] = __ldg(reinterpret_cast<const float4*>(mat0 + (unsigned long long)ij * row_bytes));
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; j++) {
+      if (HAS_VAL) {
+        acc[0] = __fmaf_rn(w[j], m[j].x, acc[0]); acc[1] = __fmaf_rn(w[j], m[j].y, acc[1]);
+        acc[2] = __fmaf_rn(w[j], m[j].z, acc[2]); acc[3] = __fmaf_rn(w[j], m[j].w, acc[3]);
+      } else {
+        acc[0] = __fadd_rn(acc[0], m[j].x); acc[1] = __fadd_rn(acc[1], m[j].y);
+        acc[2] = __fadd_rn(acc[2], m[j].z); acc[3] = __fadd_rn(acc[3], m[j].w);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < NI; q++) {
+      idx[q] = nidx[q];
+      val[q] = nval[q];
+    }
   }
   if (MODE == MODE_ROWS && p.mean) {
     const float dv = (float)(count > 0 ? count : 1);  // reducer.cuh:75-76
 #pragma unroll
     for (int x = 0; x < 4; x++) acc[x] = __fdiv_rn(acc[x], dv);
   }
-  if (grp == 0 && cvalid) *reinterpret_cast<float4*>(dst + coff) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  if (live && cvalid) *reinterpret_cast<float4*>(dst + coff) = make_float4(acc[0], acc[1], acc[2], acc[3]);
 }
 
 template <typename IdxT, bool HAS_VAL, int LPE>
 static int launch_spmm_multi(const SpmmParams& p, cudaStream_t st) {
   const unsigned gy = (unsigned)((p.K + 4 * LPE - 1) / (4 * LPE));
+  constexpr long long per_cta = (long long)kSpmmWarps * (32 / LPE);
   {
-    dim3 grid((unsigned)((p.M + kSpmmWarps - 1) / kSpmmWarps), gy);
+    dim3 grid((unsigned)((p.M + per_cta - 1) / per_cta), gy);
     spmm_csr_multi_kernel<IdxT, HAS_VAL, MODE_ROWS, LPE><<<grid, kSpmmWarps * 32, 0, st>>>(p);
     EXB_CUDA_OK(cudaGetLastError());
   }
   if (p.n_items > 0) {
-    dim3 grid((unsigned)((p.n_items + kSpmmWarps - 1) / kSpmmWarps), gy);
+    dim3 grid((unsigned)((p.n_items + per_cta - 1) / per_cta), gy);
     spmm_csr_multi_kernel<IdxT, HAS_VAL, MODE_ITEMS, LPE><<<grid, kSpmmWarps * 32, 0, st>>>(p);
     EXB_CUDA_OK(cudaGetLastError());
     spmm_long_reduce_kernel<IdxT><<<(unsigned)p.n_long, 128, 0, st>>>(p);
@@ -392,7 +410,7 @@ static int launch_spmm_vec(const SpmmParams& p, cudaStream_t st) {
   if (p.scratch) a |= reinterpret_cast<uintptr_t>(p.scratch);
   for (int i = 0; i < p.route_n; i++) a |= reinterpret_cast<uintptr_t>(p.route_dst[i]);
   if (p.route_n) a |= (uintptr_t)(p.route_ld * 4) | (uintptr_t)(p.route_col0 * 4);
-  if (p.regroup && p.K <= 64 && p.K % 4 == 0 && a % 16 == 0) return launch_spmm_pair<IdxT, HAS_VAL>(p, st);
+  if (p.K <= 64 && p.K % 4 == 0 && a % 16 == 0) return launch_spmm_pair<IdxT, HAS_VAL>(p, st);
   if (p.K % 4 == 0 && a % 16 == 0) return launch_spmm_kvt<IdxT, 4, HAS_VAL>(p, st);
   if (p.K % 2 == 0 && a % 8 == 0) return launch_spmm_kvt<IdxT, 2, HAS_VAL>(p, st);
   return launch_spmm_kvt<IdxT, 1, HAS_VAL>(p, st);
@@ -563,8 +581,8 @@ int exact_spmm_split_routed(const void* rowptr, const void* col, int idx_bytes, 
                             int64_t M, int64_t K, int reduce, int64_t long_threshold, const int32_t* item_row,
                             const int64_t* item_begin, const int64_t* item_end, const int32_t* item_slot,
                             int64_t n_items, const int32_t* long_row, const int32_t* long_item_ptr, int64_t n_long,
-                            float* scratch, int64_t shard, int64_t col0, int64_t ldd, void* const* dst, int n_dst,
-                            void* stream) {
+                            float* scratch, const int32_t* row_order, int64_t shard, int64_t col0, int64_t ldd,
+                            void* const* dst, int n_dst, void* stream) {
   EXB_REQUIRE(long_threshold >= 0 && n_items >= 0 && n_long >= 0, "spmm_split_routed: negative plan size");
   EXB_REQUIRE(n_items <= 2147483647LL && n_long <= 2147483647LL, "spmm_split_routed: plan too large");
   if (n_items > 0)
@@ -583,6 +601,7 @@ int exact_spmm_split_routed(const void* rowptr, const void* col, int idx_bytes, 
   p.item_end = reinterpret_cast<const long long*>(item_end); p.item_slot = item_slot; p.n_items = n_items;
   p.long_row = long_row; p.long_item_ptr = long_item_ptr; p.n_long = n_long; p.scratch = scratch;
   p.route_n = n_dst; p.route_shard = shard; p.route_ld = ldd; p.route_col0 = col0;
+  p.row_order = row_order;
   for (int i = 0; i < n_dst; i++) {
     EXB_REQUIRE(dst[i] != nullptr, "spmm_split_routed: null destination %d", i);
     p.route_dst[i] = static_cast<float*>(dst[i]);

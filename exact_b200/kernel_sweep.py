@@ -189,7 +189,7 @@ def run_mask(N, D, p, reps):
     return out
 
 
-def run_spmm(nodes, avg_deg, K, reps, reduce, density=None):
+def run_spmm(nodes, avg_deg, K, reps, reduce, density=None, regroup=False):
     """Mean / sum aggregation over an R-MAT graph.  `density`: the share of non-zero entries of the dense
     operand; below 1 the packing of the operand into compact rows and its expansion back (the two kernels
     around the peer exchange of a row-sharded run) are timed too."""
@@ -218,10 +218,10 @@ def run_spmm(nodes, avg_deg, K, reps, reduce, density=None):
             out.append({"op": name, "nodes": nodes, "K": K, "density": density, "ms": round(ms, 4),
                         "GB/s": round(nb / (ms * 1e-3) / 1e9, 1), "frac": round(nb / (ms * 1e-3) / 1e9 / peak, 4),
                         "peak": peak, "peak_kind": kind})
-    ms = _time(lambda: S._spmm(rowptr, col, None, x, reduce), reps, None)
+    ms = _time(lambda: S._spmm(rowptr, col, None, x, reduce, regroup=regroup), reps, None)
     must = nodes * K * 4 + nnz * 4 + (nodes + 1) * 4 + nodes * K * 4
     l2 = nnz * K * 4 + nnz * 4 + (nodes + 1) * 4 + nodes * K * 4
-    out.append({"op": "spmm_" + reduce, "nodes": nodes, "nnz": nnz, "K": K, "density": density,
+    out.append({"op": "spmm_" + reduce, "nodes": nodes, "nnz": nnz, "K": K, "density": density, "regroup": regroup,
                 "ms": round(ms, 4), "GB/s": round(must / (ms * 1e-3) / 1e9, 1),
                 "frac": round(must / (ms * 1e-3) / 1e9 / peak, 4), "l2_side_GB/s": round(l2 / (ms * 1e-3) / 1e9, 1),
                 "peak": peak, "peak_kind": kind})
@@ -334,6 +334,9 @@ def main():
     ap.add_argument("--nodes", type=int, default=1_000_000)
     ap.add_argument("--avg-deg", type=float, default=50.0)
     ap.add_argument("--K", type=int, nargs="*", default=[256])
+    ap.add_argument("--regroup", action="store_true",
+                    help="--op spmm: accept a regrouped per-row sum (operands of at most 64 columns then take "
+                         "several edges per load instruction, as the column slices of a row-sharded run do)")
     ap.add_argument("--density", type=float, default=None,
                     help="--op spmm: share of non-zero operand entries; below 1 the compact-rows pack / unpack are timed too")
     ap.add_argument("--max-bytes", type=float, default=12e9, help="skip cases whose input exceeds this")
@@ -346,7 +349,7 @@ def main():
         return
     if a.op == "spmm":
         for K in a.K:
-            for r in run_spmm(a.nodes, a.avg_deg, K, a.reps, "mean", a.density):
+            for r in run_spmm(a.nodes, a.avg_deg, K, a.reps, "mean", a.density, a.regroup):
                 print(json.dumps(r), flush=True)
         return
     if a.op == "grad_weight":

@@ -33,10 +33,9 @@ extern "C" {
 
 enum { EXACT_DTYPE_F32 = 0, EXACT_DTYPE_BF16 = 1 };
 enum { EXACT_REDUCE_SUM = 0, EXACT_REDUCE_MEAN = 1 };
-/* OR-ed into `reduce`: the caller accepts a per-row sum that is regrouped (2, 4 or 8 interleaved partial sums
- * for operands of at most 64, 32 or 16 columns instead of strict edge order; same terms, fp32 reassociation).
- * Lets narrow operands use a kernel that gathers several edges per load instruction.  Without it every row up
- * to the long-row threshold is summed in edge order, bit-identical to the reference kernel. */
+/* May be OR-ed into `reduce`; accepted and ignored.  (It used to let operands of at most 64 columns take a
+ * kernel that interleaved partial sums of a row; that kernel now gives several rows to a warp instead and sums
+ * every row up to the long-row threshold in edge order, bit-identical to the reference kernel, flag or not.) */
 enum { EXACT_SPMM_REGROUP = 0x100 };
 
 /* Library version (major * 100 + minor) and the last error message of the calling thread. */
@@ -249,13 +248,17 @@ EXACT_API int exact_bn_backward_from_packed(const float* grad_out, int64_t N, in
  * memory included), so the result slice is neither written to nor read back from local memory and the
  * transfer overlaps the gathers.  n_dst * shard >= M; ldd >= col0 + K; for 16-byte stores dst, ldd and col0
  * are 16-byte / 4-element aligned (else narrower stores).  A plan is optional (n_items = 0: every row is
- * summed by one warp).  Ordering against the readers is the caller's, as for exact_rows_scatter. */
+ * summed by one warp).  row_order (optional, [M] int32, a permutation of the rows): the order in which a narrow
+ * operand (EXACT_SPMM_REGROUP, K <= 64) takes the rows, several rows per warp; sorted by row length it gives
+ * every warp rows of equal length.  With n_dst = 1, shard = M, col0 = 0 and ldd = K this is exact_spmm_split
+ * with a row order.  Ordering against the readers is the caller's, as for exact_rows_scatter. */
 EXACT_API int exact_spmm_split_routed(const void* rowptr, const void* col, int idx_bytes, const float* value,
                                       const float* mat, int64_t M, int64_t K, int reduce, int64_t long_threshold,
                                       const int32_t* item_row, const int64_t* item_begin, const int64_t* item_end,
                                       const int32_t* item_slot, int64_t n_items, const int32_t* long_row,
-                                      const int32_t* long_item_ptr, int64_t n_long, float* scratch, int64_t shard,
-                                      int64_t col0, int64_t ldd, void* const* dst, int n_dst, void* stream);
+                                      const int32_t* long_item_ptr, int64_t n_long, float* scratch,
+                                      const int32_t* row_order, int64_t shard, int64_t col0, int64_t ldd,
+                                      void* const* dst, int n_dst, void* stream);
 
 /* Buffers that the ranks of a row-sharded run write into each other (one process per GPU, one node).  No
  * counterpart in the reference.  These are the only entry points that allocate or free device memory:
