@@ -48,6 +48,13 @@ SIGNATURES = {
     "exact_spmm_split_routed": (c_int, [c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_int, c_i64, c_ptr, c_ptr,
                                         c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_i64, c_i64,
                                         ctypes.POINTER(c_ptr), c_int, c_ptr]),
+    "exact_quantize_pack_f16": (c_int, [c_ptr, c_i64, c_i64, c_int, c_ptr, c_u64, c_u64, c_i64, c_ptr, c_ptr, c_ptr, c_ptr]),
+    "exact_pack_single_precision_f16": (c_int, [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_int, c_ptr, c_u64, c_u64, c_i64,
+                                                c_ptr, c_ptr]),
+    "exact_unpack_single_precision_f16": (c_int, [c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_ptr]),
+    "exact_act_quantized_forward_f16": (c_int, [c_int, c_ptr, c_i64, c_f32, c_ptr, c_u64, c_u64, c_i64, c_ptr, c_ptr,
+                                                c_ptr]),
+    "exact_act_quantized_backward_f16": (c_int, [c_int, c_ptr, c_ptr, c_i64, c_f32, c_ptr, c_ptr]),
     "exact_bn_backward_workspace_bytes": (c_i64, [c_i64]),
     "exact_bn_backward_from_packed": (c_int, [c_ptr, c_i64, c_i64, c_ptr, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int,
                                               c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr]),

@@ -32,7 +32,7 @@ def packed_numel(N, D, bits):
 def quantize_pack(data, bits, noise=None, seed=None, offset=None, row_offset=None, want_f32_stats=False):
     """Fused row statistics + stochastic quantise + bit-pack.  One kernel, one read of `data`.
     -> (packed int8 [G*D+1], scale bf16 [N], min bf16 [N][, scale f32, min f32])."""
-    _check_cuda_float(data, "data", 2, (torch.float32, torch.bfloat16))
+    _check_cuda_float(data, "data", 2, (torch.float32, torch.bfloat16, torch.float16))
     if bits not in (1, 2, 4, 8):
         raise RuntimeError("bits must be 1, 2, 4 or 8")
     N, D = data.shape
@@ -42,6 +42,22 @@ def quantize_pack(data, bits, noise=None, seed=None, offset=None, row_offset=Non
             raise RuntimeError("noise must have the shape of data")
     lib = _lib.load()
     packed = torch.empty(packed_numel(N, D, bits), dtype=torch.int8, device=data.device)
+    if data.dtype == torch.float16:
+        # half arithmetic of the reference's half kernels; the statistics stay fp16 (ops.py:82-83)
+        if want_f32_stats:
+            raise RuntimeError("fp16 activations have fp16 statistics only")
+        scale = torch.empty(N, dtype=torch.float16, device=data.device)
+        mn = torch.empty(N, dtype=torch.float16, device=data.device)
+        if noise is None:
+            seed = config.seed if seed is None else seed
+            offset = config.next_offset() if offset is None else offset
+        else:
+            seed = offset = 0
+        row_offset = config.row_offset if row_offset is None else row_offset
+        _lib.invoke("exact_quantize_pack_f16", 2 * N * D * 2 + packed.numel() - 1 + 4 * N, _lib.ptr(data), N, D, bits,
+                    _lib.ptr(noise), seed, offset, row_offset, _lib.ptr(packed), _lib.ptr(scale), _lib.ptr(mn),
+                    _lib.stream_ptr())
+        return packed, scale, mn
     scale = torch.empty(N, dtype=torch.bfloat16, device=data.device)
     mn = torch.empty(N, dtype=torch.bfloat16, device=data.device)
     sf = mf = None
@@ -143,10 +159,12 @@ def pack_single_precision(data, min, max, scale, bits, stochastic, noise=None, s
     """quantization.cc:37-48.  `max` is accepted and ignored, as in the reference kernel; `stochastic`
     must be true (quantization_cuda_kernel.cu:123).  `noise` (optional, [N,D] fp32) replaces the
     Philox draw."""
-    _check_cuda_float(data, "data", 2, (torch.float32, torch.bfloat16))
-    _check_cuda_float(min, "min", 1)
-    _check_cuda_float(max, "max", 1)
-    _check_cuda_float(scale, "scale", 1)
+    _check_cuda_float(data, "data", 2, (torch.float32, torch.bfloat16, torch.float16))
+    half = data.dtype == torch.float16   # the reference's half instantiation: statistics are halves too
+    stat_types = (torch.float16,) if half else (torch.float32,)
+    _check_cuda_float(min, "min", 1, stat_types)
+    _check_cuda_float(max, "max", 1, stat_types)
+    _check_cuda_float(scale, "scale", 1, stat_types)
     if 8 % bits != 0 or bits not in (1, 2, 4, 8):
         raise RuntimeError("bits must be 1, 2, 4 or 8")
     if not stochastic:
@@ -159,6 +177,11 @@ def pack_single_precision(data, min, max, scale, bits, stochastic, noise=None, s
     else:
         seed = offset = 0
     row_offset = config.row_offset if row_offset is None else row_offset
+    if half:
+        _lib.invoke("exact_pack_single_precision_f16", N * D * 2 + packed.numel() - 1 + 4 * N, _lib.ptr(data),
+                    _lib.ptr(min), _lib.ptr(scale), N, D, bits, _lib.ptr(noise), seed, offset, row_offset,
+                    _lib.ptr(packed), _lib.stream_ptr())
+        return packed
     nbytes = N * D * data.element_size() + packed.numel() - 1 + 8 * N
     _lib.invoke("exact_pack_single_precision", nbytes, _lib.ptr(data), _dt(data), _lib.ptr(min), _lib.ptr(scale),
                 N, D, bits, _lib.ptr(noise), seed, offset, row_offset, _lib.ptr(packed), _lib.stream_ptr())
@@ -166,12 +189,13 @@ def pack_single_precision(data, min, max, scale, bits, stochastic, noise=None, s
 
 
 def unpack_single_precision(data, bits, scale, min, N, group_size):
-    """quantization.cc:50-62.  scale/min may be fp32 (reference signature) or bf16 (the stored
-    statistics; widening happens in the kernel).  Returns fp32 [N, group_size]."""
+    """quantization.cc:50-62.  scale/min may be fp32 (reference signature), bf16 (the stored statistics of an
+    fp32 activation; widening happens in the kernel) or fp16 (an fp16 activation).  Returns [N, group_size] in
+    fp32, or in fp16 for fp16 statistics."""
     if not data.is_cuda or not data.is_contiguous() or data.dim() != 1 or data.dtype != torch.int8:
         raise RuntimeError("The type of data is not correct!")
-    _check_cuda_float(scale, "scale", 1, (torch.float32, torch.bfloat16))
-    _check_cuda_float(min, "min", 1, (torch.float32, torch.bfloat16))
+    _check_cuda_float(scale, "scale", 1, (torch.float32, torch.bfloat16, torch.float16))
+    _check_cuda_float(min, "min", 1, (torch.float32, torch.bfloat16, torch.float16))
     if scale.dtype != min.dtype:
         raise RuntimeError("scale and min must have the same dtype")
     if bits not in (1, 2, 4, 8):
@@ -180,11 +204,35 @@ def unpack_single_precision(data, bits, scale, min, N, group_size):
     need = int(lib.exact_packed_bytes(N, group_size, bits))
     if data.numel() < need or scale.numel() < N or min.numel() < N:
         raise RuntimeError("packed stream or statistics shorter than N x group_size requires")
+    if scale.dtype == torch.float16:
+        # the output has the statistics' dtype (quantization_cuda_kernel.cu:194-195): fp16, half arithmetic
+        out = torch.empty((N, group_size), dtype=torch.float16, device=data.device)
+        _lib.invoke("exact_unpack_single_precision_f16", need + 4 * N + 2 * N * group_size, _lib.ptr(data), bits,
+                    _lib.ptr(scale), _lib.ptr(min), N, group_size, _lib.ptr(out), _lib.stream_ptr())
+        return out
     out = torch.empty((N, group_size), dtype=torch.float32, device=data.device)
     nbytes = need + 2 * N * scale.element_size() + 4 * N * group_size
     _lib.invoke("exact_unpack_single_precision", nbytes, _lib.ptr(data), bits, _lib.ptr(scale), _lib.ptr(min),
                 _dt(scale), N, group_size, _lib.ptr(out), _lib.stream_ptr())
     return out
+
+
+ACT_RELU, ACT_DROPOUT, ACT_RELU_DROPOUT, ACT_LEAKY_RELU = 0, 1, 2, 3   # EXACT_ACT_*
+_ACT_DTYPES = (torch.float32, torch.float16)
+
+
+def _act_forward_f16(op, input, param, uniforms, seed, offset, index_offset, out, mask):
+    """fp16 tensors: the reference's half instantiations (fp32 arithmetic on widened values, one rounding on
+    the store)."""
+    n = input.numel()
+    _lib.invoke("exact_act_quantized_forward_f16", 4 * n + n // 8, op, _lib.ptr(input), n, param, _lib.ptr(uniforms),
+                seed, offset, index_offset, _lib.ptr(out), _lib.ptr(mask), _lib.stream_ptr())
+
+
+def _act_backward_f16(op, grad_output, mask, param, gin):
+    n = grad_output.numel()
+    _lib.invoke("exact_act_quantized_backward_f16", 4 * n + n // 8, op, _lib.ptr(grad_output), _lib.ptr(mask), n, param,
+                _lib.ptr(gin), _lib.stream_ptr())
 
 
 class _ActQuantizedReLU(torch.autograd.Function):
@@ -196,8 +244,11 @@ class _ActQuantizedReLU(torch.autograd.Function):
         n = input.numel()
         out = torch.empty_like(input)
         mask = torch.empty(int(lib.exact_mask_words(n)), dtype=torch.int32, device=input.device)
-        _lib.invoke("exact_act_quantized_relu_forward", 8 * n + n // 8, _lib.ptr(input), n, _lib.ptr(out),
-                    _lib.ptr(mask), _lib.stream_ptr())
+        if input.dtype == torch.float16:
+            _act_forward_f16(ACT_RELU, input, 0.0, None, 0, 0, 0, out, mask)
+        else:
+            _lib.invoke("exact_act_quantized_relu_forward", 8 * n + n // 8, _lib.ptr(input), n, _lib.ptr(out),
+                        _lib.ptr(mask), _lib.stream_ptr())
         ctx.save_for_backward(mask)
         return out
 
@@ -207,14 +258,17 @@ class _ActQuantizedReLU(torch.autograd.Function):
         grad_output = grad_output.contiguous()
         gin = torch.empty_like(grad_output)
         n = grad_output.numel()
-        _lib.invoke("exact_act_quantized_relu_backward", 8 * n + n // 8, _lib.ptr(grad_output), _lib.ptr(mask), n,
-                    _lib.ptr(gin), _lib.stream_ptr())
+        if grad_output.dtype == torch.float16:
+            _act_backward_f16(ACT_RELU, grad_output, mask, 0.0, gin)
+        else:
+            _lib.invoke("exact_act_quantized_relu_backward", 8 * n + n // 8, _lib.ptr(grad_output), _lib.ptr(mask), n,
+                        _lib.ptr(gin), _lib.stream_ptr())
         return gin
 
 
 def act_quantized_relu(input):
     """quantization.cc:81-84."""
-    _check_cuda_float(input, "input")
+    _check_cuda_float(input, "input", None, _ACT_DTYPES)
     return _ActQuantizedReLU.apply(input)
 
 
@@ -233,8 +287,12 @@ class _ActQuantizedDropout(torch.autograd.Function):
             seed = offset = 0
         # rows are the sharded dimension: element 0 of this shard is global element row_offset * row_len
         index_offset = config.row_offset * (n // input.shape[0]) if (input.dim() >= 2 and n) else 0
-        _lib.invoke("exact_act_quantized_dropout_forward", 8 * n + n // 8, _lib.ptr(input), n, p, _lib.ptr(uniforms),
-                    seed, offset, index_offset, _lib.ptr(out), _lib.ptr(mask), _lib.stream_ptr())
+        if input.dtype == torch.float16:
+            _act_forward_f16(ACT_DROPOUT, input, p, uniforms, seed, offset, index_offset, out, mask)
+        else:
+            _lib.invoke("exact_act_quantized_dropout_forward", 8 * n + n // 8, _lib.ptr(input), n, p,
+                        _lib.ptr(uniforms), seed, offset, index_offset, _lib.ptr(out), _lib.ptr(mask),
+                        _lib.stream_ptr())
         ctx.save_for_backward(mask)
         ctx.p = p
         return out
@@ -245,15 +303,18 @@ class _ActQuantizedDropout(torch.autograd.Function):
         grad_output = grad_output.contiguous()
         gin = torch.empty_like(grad_output)
         n = grad_output.numel()
-        _lib.invoke("exact_act_quantized_dropout_backward", 8 * n + n // 8, _lib.ptr(grad_output), _lib.ptr(mask),
-                    n, ctx.p, _lib.ptr(gin), _lib.stream_ptr())
+        if grad_output.dtype == torch.float16:
+            _act_backward_f16(ACT_DROPOUT, grad_output, mask, ctx.p, gin)
+        else:
+            _lib.invoke("exact_act_quantized_dropout_backward", 8 * n + n // 8, _lib.ptr(grad_output), _lib.ptr(mask),
+                        n, ctx.p, _lib.ptr(gin), _lib.stream_ptr())
         return gin, None, None
 
 
 def act_quantized_dropout(input, p, train, uniforms=None):
     """quantization.cc:131-134; eval mode returns the input tensor itself (quantization.cc:115-117).
     `uniforms` (optional, fp32, shape of input) replaces the Philox draw."""
-    _check_cuda_float(input, "input")
+    _check_cuda_float(input, "input", None, _ACT_DTYPES)
     if not train:
         return input
     if uniforms is not None:
@@ -277,8 +338,12 @@ class _ActQuantizedReLUDropout(_ActQuantizedDropout):
         else:
             seed = offset = 0
         index_offset = config.row_offset * (n // input.shape[0]) if (input.dim() >= 2 and n) else 0
-        _lib.invoke("exact_act_quantized_relu_dropout_forward", 8 * n + n // 8, _lib.ptr(input), n, p,
-                    _lib.ptr(uniforms), seed, offset, index_offset, _lib.ptr(out), _lib.ptr(mask), _lib.stream_ptr())
+        if input.dtype == torch.float16:
+            _act_forward_f16(ACT_RELU_DROPOUT, input, p, uniforms, seed, offset, index_offset, out, mask)
+        else:
+            _lib.invoke("exact_act_quantized_relu_dropout_forward", 8 * n + n // 8, _lib.ptr(input), n, p,
+                        _lib.ptr(uniforms), seed, offset, index_offset, _lib.ptr(out), _lib.ptr(mask),
+                        _lib.stream_ptr())
         ctx.save_for_backward(mask)
         ctx.p = p
         return out
@@ -287,7 +352,7 @@ class _ActQuantizedReLUDropout(_ActQuantizedDropout):
 def act_quantized_relu_dropout(input, p, train, uniforms=None):
     """dropout(relu(input)) as the two reference ops compute it (quantization.cc:66-84, 111-134), in one
     pass and with one saved mask.  Eval mode: relu only."""
-    _check_cuda_float(input, "input")
+    _check_cuda_float(input, "input", None, _ACT_DTYPES)
     if not train:
         return torch.relu(input)
     if uniforms is not None:
@@ -306,8 +371,11 @@ class _ActQuantizedLeakyReLU(torch.autograd.Function):
         n = input.numel()
         out = torch.empty_like(input)
         mask = torch.empty(int(lib.exact_mask_words(n)), dtype=torch.int32, device=input.device)
-        _lib.invoke("exact_act_quantized_leaky_relu_forward", 8 * n + n // 8, _lib.ptr(input), n, slope, _lib.ptr(out),
-                    _lib.ptr(mask), _lib.stream_ptr())
+        if input.dtype == torch.float16:
+            _act_forward_f16(ACT_LEAKY_RELU, input, slope, None, 0, 0, 0, out, mask)
+        else:
+            _lib.invoke("exact_act_quantized_leaky_relu_forward", 8 * n + n // 8, _lib.ptr(input), n, slope,
+                        _lib.ptr(out), _lib.ptr(mask), _lib.stream_ptr())
         ctx.save_for_backward(mask)
         ctx.slope = slope
         return out
@@ -318,12 +386,15 @@ class _ActQuantizedLeakyReLU(torch.autograd.Function):
         grad_output = grad_output.contiguous()
         gin = torch.empty_like(grad_output)
         n = grad_output.numel()
-        _lib.invoke("exact_act_quantized_leaky_relu_backward", 8 * n + n // 8, _lib.ptr(grad_output), _lib.ptr(mask), n,
-                    ctx.slope, _lib.ptr(gin), _lib.stream_ptr())
+        if grad_output.dtype == torch.float16:
+            _act_backward_f16(ACT_LEAKY_RELU, grad_output, mask, ctx.slope, gin)
+        else:
+            _lib.invoke("exact_act_quantized_leaky_relu_backward", 8 * n + n // 8, _lib.ptr(grad_output),
+                        _lib.ptr(mask), n, ctx.slope, _lib.ptr(gin), _lib.stream_ptr())
         return gin, None
 
 
 def act_quantized_leaky_relu(input, slope):
     """quantization.cc:104-107."""
-    _check_cuda_float(input, "input")
+    _check_cuda_float(input, "input", None, _ACT_DTYPES)
     return _ActQuantizedLeakyReLU.apply(input.contiguous(), float(slope))

@@ -9,6 +9,7 @@
 // either (quantization.cc:71,92,119), only outputs and gradients are observable.
 #include "common.cuh"
 #include <cmath>
+#include <cuda_fp16.h>
 
 #include "exact_b200.h"
 
@@ -17,9 +18,9 @@ namespace exb {
 enum MaskOp { OP_RELU = 0, OP_DROPOUT = 1, OP_RELU_DROPOUT = 2, OP_LEAKY_RELU = 3 };
 
 struct MaskParams {
-  const float* x;       // forward input or grad_out
+  const void* x;        // forward input or grad_out, fp32 or fp16 (the kernels' element type)
   const float* u;       // supplied uniforms (dropout forward) or null
-  float* out;           // output or grad_in
+  void* out;            // output or grad_in, same type as x
   uint32_t* mask;
   long long n;
   float p;              // dropout probability; the negative slope for LeakyReLU
@@ -51,8 +52,37 @@ __device__ __forceinline__ void store4(float* base, long long i, long long n, co
       if (i + j < n) __stcs(base + i + j, v[j]);
   }
 }
+// fp16 elements (the reference's half instantiations, quantization_cuda_kernel.cu:284, 324, 387, 428, 535, 586):
+// Half (op) float is computed in fp32 there and the result rounded once when it is stored, so the kernels
+// below do the same fp32 arithmetic on widened values and round on the store.
+template <bool ALIGNED>
+__device__ __forceinline__ void load4(const __half* base, long long i, long long n, float (&v)[4]) {
+  if (ALIGNED && i + 4 <= n) {
+    const uint2 t = __ldcs(reinterpret_cast<const uint2*>(base + i));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&t.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; j++) v[j] = (i + j < n) ? __half2float(base[i + j]) : 0.f;
+  }
+}
+template <bool ALIGNED>
+__device__ __forceinline__ void store4(__half* base, long long i, long long n, const float (&v)[4]) {
+  if (ALIGNED && i + 4 <= n) {
+    const __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<const uint32_t*>(&a);
+    t.y = *reinterpret_cast<const uint32_t*>(&b);
+    __stcs(reinterpret_cast<uint2*>(base + i), t);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+      if (i + j < n) base[i + j] = __float2half_rn(v[j]);
+  }
+}
 
-template <int OP, bool ALIGNED>
+template <int OP, bool ALIGNED, typename T>
 __global__ void __launch_bounds__(256) mask_forward_kernel(const __grid_constant__ MaskParams p) {
   const int lane = threadIdx.x & 31;
   const long long nchunks = (p.n + 127) >> 7;
@@ -62,7 +92,7 @@ __global__ void __launch_bounds__(256) mask_forward_kernel(const __grid_constant
     const long long i = (c << 7) + 4 * lane;
     float v[4], o[4];
     bool keep[4];
-    load4<ALIGNED>(p.x, i, p.n, v);
+    load4<ALIGNED>(static_cast<const T*>(p.x), i, p.n, v);
     if (OP == OP_RELU) {
 #pragma unroll
       for (int j = 0; j < 4; j++) {
@@ -100,7 +130,7 @@ __global__ void __launch_bounds__(256) mask_forward_kernel(const __grid_constant
         if (OP == OP_RELU_DROPOUT) keep[j] = keep[j] && v[j] > 0.f;
       }
     }
-    store4<ALIGNED>(p.out, i, p.n, o);
+    store4<ALIGNED>(static_cast<T*>(p.out), i, p.n, o);
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const uint32_t w = __ballot_sync(0xffffffffu, keep[j]);
@@ -109,7 +139,7 @@ __global__ void __launch_bounds__(256) mask_forward_kernel(const __grid_constant
   }
 }
 
-template <int OP, bool ALIGNED>
+template <int OP, bool ALIGNED, typename T>
 __global__ void __launch_bounds__(256) mask_backward_kernel(const __grid_constant__ MaskParams p) {
   const int lane = threadIdx.x & 31;
   const long long nchunks = (p.n + 127) >> 7;
@@ -118,7 +148,7 @@ __global__ void __launch_bounds__(256) mask_backward_kernel(const __grid_constan
   for (long long c = warp0; c < nchunks; c += nwarps) {
     const long long i = (c << 7) + 4 * lane;
     float g[4], o[4];
-    load4<ALIGNED>(p.x, i, p.n, g);
+    load4<ALIGNED>(static_cast<const T*>(p.x), i, p.n, g);
     const uint4 mw = __ldg(reinterpret_cast<const uint4*>(p.mask) + c);
     const uint32_t m[4] = {mw.x, mw.y, mw.z, mw.w};
 #pragma unroll
@@ -135,31 +165,43 @@ __global__ void __launch_bounds__(256) mask_backward_kernel(const __grid_constan
         o[j] = keep ? q : 0.f;
       }
     }
-    store4<ALIGNED>(p.out, i, p.n, o);
+    store4<ALIGNED>(static_cast<T*>(p.out), i, p.n, o);
   }
 }
 
 static bool aligned16(const void* a) { return (reinterpret_cast<uintptr_t>(a) & 15) == 0; }
 
-template <int OP>
+static bool aligned_to(const void* a, unsigned bytes) { return (reinterpret_cast<uintptr_t>(a) & (bytes - 1)) == 0; }
+
+template <int OP, typename T = float>
 static int launch_mask(bool forward, const MaskParams& p, cudaStream_t st) {
   if (p.n == 0) return EXB_OK;
   EXB_REQUIRE(p.x && p.out && p.mask, "mask activation: null pointer");
   EXB_REQUIRE(aligned16(p.mask), "mask activation: mask must be 16-byte aligned");
-  const bool al = aligned16(p.x) && aligned16(p.out) && (p.u == nullptr || aligned16(p.u));
+  const unsigned vb = 4 * sizeof(T);   // one 4-element vector access
+  const bool al = aligned_to(p.x, vb) && aligned_to(p.out, vb) && (p.u == nullptr || aligned16(p.u));
   const long long nchunks = (p.n + 127) >> 7;
   long long blocks = (nchunks + 7) / 8;
   const long long cap = (long long)sm_count() * 8;
   if (blocks > cap) blocks = cap;
   if (forward) {
-    if (al) mask_forward_kernel<OP, true><<<(int)blocks, 256, 0, st>>>(p);
-    else mask_forward_kernel<OP, false><<<(int)blocks, 256, 0, st>>>(p);
+    if (al) mask_forward_kernel<OP, true, T><<<(int)blocks, 256, 0, st>>>(p);
+    else mask_forward_kernel<OP, false, T><<<(int)blocks, 256, 0, st>>>(p);
   } else {
-    if (al) mask_backward_kernel<OP, true><<<(int)blocks, 256, 0, st>>>(p);
-    else mask_backward_kernel<OP, false><<<(int)blocks, 256, 0, st>>>(p);
+    if (al) mask_backward_kernel<OP, true, T><<<(int)blocks, 256, 0, st>>>(p);
+    else mask_backward_kernel<OP, false, T><<<(int)blocks, 256, 0, st>>>(p);
   }
   EXB_CUDA_OK(cudaGetLastError());
   return EXB_OK;
+}
+
+static void dropout_constants(MaskParams& p, float prob) {
+  p.p = prob;
+  p.pinv = (float)(1.0 / (1.0 - (double)prob));  // quantization_cuda_kernel.cu:455
+  p.p1m = (float)(1.0 - (double)prob);           // quantization.cc:120
+  int ex = 0;
+  const float mant = frexpf(p.p1m, &ex);   // p1m = mant * 2^ex, mant in [0.5, 1)
+  p.p1m_inv_exact = (p.p1m > 0.f && mant == 0.5f && ex > -120 && ex < 120) ? ldexpf(1.f, 1 - ex) : 0.f;
 }
 
 }  // namespace exb
@@ -248,6 +290,39 @@ int exact_act_quantized_dropout_backward(const float* grad_out, const uint32_t* 
     p.p1m_inv_exact = (p.p1m > 0.f && mant == 0.5f && ex > -120 && ex < 120) ? ldexpf(1.f, 1 - ex) : 0.f;
   }
   return launch_mask<OP_DROPOUT>(false, p, (cudaStream_t)stream);
+}
+
+int exact_act_quantized_forward_f16(int op, const void* x, int64_t n, float param, const float* uniforms, uint64_t seed,
+                                    uint64_t offset, int64_t index_offset, void* out, uint32_t* mask, void* stream) {
+  EXB_REQUIRE(n >= 0, "act_quantized_f16: negative size");
+  EXB_REQUIRE(op >= EXACT_ACT_RELU && op <= EXACT_ACT_LEAKY_RELU, "act_quantized_f16: unknown op %d", op);
+  MaskParams p{};
+  p.x = x; p.out = out; p.mask = mask; p.n = n; p.p = param;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (op == EXACT_ACT_RELU) return launch_mask<OP_RELU, __half>(true, p, st);
+  if (op == EXACT_ACT_LEAKY_RELU) return launch_mask<OP_LEAKY_RELU, __half>(true, p, st);
+  EXB_REQUIRE(index_offset >= 0 && index_offset % 4 == 0, "dropout: index_offset must be a non-negative multiple of 4");
+  EXB_REQUIRE(param >= 0.f && param <= 1.f, "dropout: p must be in [0, 1] (got %f)", (double)param);
+  p.u = uniforms;
+  dropout_constants(p, param);
+  p.off_lo = (uint32_t)offset; p.off_hi = (uint32_t)(offset >> 32);
+  p.q0 = (unsigned long long)index_offset >> 2;
+  p.key = make_philox_key(seed);
+  if (op == EXACT_ACT_DROPOUT) return launch_mask<OP_DROPOUT, __half>(true, p, st);
+  return launch_mask<OP_RELU_DROPOUT, __half>(true, p, st);
+}
+
+int exact_act_quantized_backward_f16(int op, const void* grad_out, const uint32_t* mask, int64_t n, float param,
+                                     void* grad_in, void* stream) {
+  EXB_REQUIRE(n >= 0, "act_quantized_f16: negative size");
+  EXB_REQUIRE(op >= EXACT_ACT_RELU && op <= EXACT_ACT_LEAKY_RELU, "act_quantized_f16: unknown op %d", op);
+  MaskParams p{};
+  p.x = grad_out; p.out = grad_in; p.mask = const_cast<uint32_t*>(mask); p.n = n; p.p = param;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (op == EXACT_ACT_RELU) return launch_mask<OP_RELU, __half>(false, p, st);
+  if (op == EXACT_ACT_LEAKY_RELU) return launch_mask<OP_LEAKY_RELU, __half>(false, p, st);
+  dropout_constants(p, param);
+  return launch_mask<OP_DROPOUT, __half>(false, p, st);   // also the backward of ReLU + dropout (one mask)
 }
 
 }  // extern "C"

@@ -59,7 +59,8 @@ def no_scheme_compute_quantization_bits(input):
 
 def quantize_activation(input, scheme, noise=None):
     """ops.py:69-83 -> (q_input int8 [ceil(N/(8/b))*D + 1], q_bits, q_scale bf16 [N], q_min bf16 [N]), or
-    (input, None, None, None) when compression is off.
+    (input, None, None, None) when compression is off.  An fp16 activation (AMP: ops.py:130) keeps fp16
+    statistics (ops.py:82-83) and is quantised with the half arithmetic of the reference's half kernels.
 
     The row min/max, the scale, the stochastic quantise + pack and the bf16 rounding of the
     statistics run as ONE kernel that reads `input` once.  `noise` ([N, D] fp32 in [0,1)) replaces
@@ -75,8 +76,8 @@ def quantize_activation(input, scheme, noise=None):
             input_groups, q_bits, q_min, mx = no_scheme_compute_quantization_bits(input)
         q_input, q_scale = quantize_and_pack(input_groups, q_bits, q_min, mx, noise)
         return q_input, q_bits, q_scale.to(torch.bfloat16), q_min.to(torch.bfloat16)
-    if input.dtype not in (torch.float32, torch.bfloat16):
-        raise NotImplementedError("quantize_activation: fp32 and bf16 activations are supported")
+    if input.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+        raise NotImplementedError("quantize_activation: fp32, bf16 and fp16 activations are supported")
     if not config.stochastic:
         raise RuntimeError("stochastic must be true")  # quantization_cuda_kernel.cu:123
     q_bits = config.activation_compression_bits[0]

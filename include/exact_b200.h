@@ -93,6 +93,37 @@ EXACT_API int exact_unpack_single_precision(const uint8_t* packed, int bits, con
                                             const void* min, int stats_dtype, int64_t N, int64_t D,
                                             float* out, void* stream);
 
+/* fp16 activations: the half instantiations of the reference's pack / unpack kernels
+ * (quantization_cuda_kernel.cu:132, 209; AMP runs cast the inputs of the quantised ops to fp16,
+ * exact/exact/ops.py:130) and the fp16 row statistics that go with them (ops.py:82-83: the statistics of an
+ * fp16 activation stay fp16).  Every Half (op) Half is computed in fp32 and rounded back to half, as c10::Half
+ * does: pack  code = rint(max(float(half(half(x - min) * scale)) + noise - 0.5, 0));
+ *       unpack out = half(half(float(code) / scale) + min);
+ *       statistics min = min_d x, scale = half(float(half(1 / float(half(max - min)))) * (2^bits - 1)).
+ * data / x / out [N, D] and min / scale [N] are fp16 bit patterns; packed layout and noise as in the fp32 entry
+ * points. */
+EXACT_API int exact_quantize_pack_f16(const void* x, int64_t N, int64_t D, int bits, const float* noise, uint64_t seed,
+                                      uint64_t offset, int64_t row_offset, uint8_t* packed, uint16_t* scale_f16,
+                                      uint16_t* min_f16, void* stream);
+EXACT_API int exact_pack_single_precision_f16(const void* data, const void* min, const void* scale, int64_t N, int64_t D,
+                                              int bits, const float* noise, uint64_t seed, uint64_t offset,
+                                              int64_t row_offset, uint8_t* packed, void* stream);
+EXACT_API int exact_unpack_single_precision_f16(const uint8_t* packed, int bits, const void* scale, const void* min,
+                                                int64_t N, int64_t D, void* out, void* stream);
+
+/* The 1-bit-mask activations on fp16 tensors (the reference's half instantiations,
+ * quantization_cuda_kernel.cu:284, 324, 387, 428, 535, 586): the arithmetic of the fp32 entry points on widened
+ * values, rounded to half once on the store (Half (op) float is a float in the reference).  op: EXACT_ACT_*;
+ * param: the dropout probability or the negative slope (ignored by ReLU); uniforms / seed / offset / index_offset
+ * as in exact_act_quantized_dropout_forward.  The backward of EXACT_ACT_RELU_DROPOUT is that of
+ * EXACT_ACT_DROPOUT with the saved mask.  x / out / grad_out / grad_in: n fp16 bit patterns. */
+enum { EXACT_ACT_RELU = 0, EXACT_ACT_DROPOUT = 1, EXACT_ACT_RELU_DROPOUT = 2, EXACT_ACT_LEAKY_RELU = 3 };
+EXACT_API int exact_act_quantized_forward_f16(int op, const void* x, int64_t n, float param, const float* uniforms,
+                                              uint64_t seed, uint64_t offset, int64_t index_offset, void* out,
+                                              uint32_t* mask, void* stream);
+EXACT_API int exact_act_quantized_backward_f16(int op, const void* grad_out, const uint32_t* mask, int64_t n, float param,
+                                               void* grad_in, void* stream);
+
 /* Number of 32-bit mask words the 1-bit-mask activations need for n elements. */
 EXACT_API int64_t exact_mask_words(int64_t n);
 
@@ -300,9 +331,10 @@ EXACT_API int exact_spmm_split_static(const void* rowptr, const void* col, int i
  * exact/exact/ops.py:142-149 (torch.matmul(input, rand_matrix), ops.py:117, then ops.py:61-83) as one
  * TMA-fed tcgen05 (tf32) GEMM whose epilogue computes the row statistics and packs, so the [N, k]
  * product never reaches HBM.
- *   x [N, D] fp32 (D % 4 == 0, 16-byte aligned; packed 4-byte aligned when k % 4 == 0);  R [D, k] fp32 with entries +-1/sqrt(k) (only the
- *   signs are read; 1/sqrt(k) is applied in fp32);  k <= 256.  Other shapes return code 3 and the
- *   caller uses the unfused chain.
+ *   x [N, D] fp32, rows of any length (rows a tensor map cannot describe, D % 4 != 0 or a base that is not
+ *   16-byte aligned, are brought in by cp.async instead of TMA); packed 4-byte aligned when k % 4 == 0;  R [D, k]
+ *   fp32 with entries +-1/sqrt(k) (only the signs are read; 1/sqrt(k) is applied in fp32);  k up to 512 after
+ *   padding to 16.  Other shapes return code 3 and the caller uses the unfused chain.
  *   workspace: exact_rp_workspace_bytes(D, k) bytes, 256-byte aligned, caller-owned.  Its first int32
  *   is a status word the kernels clear and set non-zero only if a bounded on-chip wait expired.
  *   Noise: Philox4x32-10 keyed by (seed, offset); one call per (global row, block of 8 columns).
@@ -320,8 +352,8 @@ EXACT_API int exact_rp_quantize_pack(const float* x, int64_t N, int64_t D, const
  * dequantised straight into shared memory, so the [N, k] dequantised projection never reaches HBM.
  *   packed / scale_bf16 / min_bf16: a packed [N, k] activation as exact_quantize_pack or
  *   exact_rp_quantize_pack produce it;  R [D, k] fp32 (+-1/sqrt(k));  out [N, D] fp32.
- *   D <= 256 and k small enough for sign(R) to stay resident in shared memory; other shapes return
- *   code 3 and the caller uses the unfused chain.  workspace: exact_unpack_rp_workspace_bytes(D, k)
+ *   sign(R) stays resident in shared memory when it fits beside the A tiles (D <= 256, small k); otherwise it is
+ *   streamed in panels and the output is produced in blocks of up to 256 columns.  workspace: exact_unpack_rp_workspace_bytes(D, k)
  *   bytes, 256-byte aligned; its first int32 is the status word (see exact_rp_quantize_pack). */
 EXACT_API int64_t exact_unpack_rp_workspace_bytes(int64_t D, int64_t k);
 EXACT_API int exact_unpack_dequant_rp(const uint8_t* packed, int bits, const uint16_t* scale_bf16,

@@ -347,3 +347,39 @@ def bn_backward(grad_out, x, weight, mean, invstd, training):
     else:
         grad_in = g * (invstd * w)
     return grad_in, sum_gx * invstd, sum_g
+
+
+def _u16(a):
+    a = np.asarray(a)
+    if a.dtype == np.float16:
+        a = a.view(np.uint16)
+    return np.ascontiguousarray(a, dtype=np.uint16)
+
+
+def quantize_activation_f16(x, noise, bits):
+    """ops.py:69-83 for an fp16 activation (statistics stay fp16, ops.py:82-83) -> (packed u8, scale f16, min f16),
+    with the half arithmetic of the reference's half kernels and of torch's half tensor ops."""
+    xb, noise = _u16(x), _f32(noise)
+    N, D = xb.shape
+    mn, sc = np.empty(N, np.uint16), np.empty(N, np.uint16)
+    lib().orc_row_stats_f16(_p(xb), i64(N), i64(D), cint(bits), _p(mn), _p(sc))
+    packed = np.empty(packed_nbytes(N, D, bits), np.uint8)
+    lib().orc_pack_f16(_p(xb), _p(mn), _p(sc), _p(noise), i64(N), i64(D), cint(bits), _p(packed))
+    return packed, sc.view(np.float16), mn.view(np.float16)
+
+
+def pack_f16(x, mn, scale, noise, bits):
+    """pack_single_precision on halves (quantization_cuda_kernel.cu:73-93, scalar_t = Half)."""
+    xb, noise = _u16(x), _f32(noise)
+    N, D = xb.shape
+    packed = np.empty(packed_nbytes(N, D, bits), np.uint8)
+    lib().orc_pack_f16(_p(xb), _p(_u16(mn)), _p(_u16(scale)), _p(noise), i64(N), i64(D), cint(bits), _p(packed))
+    return packed
+
+
+def unpack_f16(packed, scale, mn, N, D, bits):
+    """unpack_single_precision with half statistics (quantization_cuda_kernel.cu:167-184) -> fp16 [N, D]."""
+    packed = np.ascontiguousarray(packed).view(np.uint8)
+    out = np.empty((N, D), np.uint16)
+    lib().orc_unpack_f16(_p(packed), _p(_u16(scale)), _p(_u16(mn)), i64(N), i64(D), cint(bits), _p(out))
+    return out.view(np.float16)

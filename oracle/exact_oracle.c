@@ -174,6 +174,95 @@ ORC_API void orc_quantize_activation(const float *x, const float *noise, int64_t
   free(sc);
 }
 
+/* ------------------------------------------------------------------------------------------------
+ * fp16 activations: the half instantiations of the same kernels (dispatch at
+ * quantization_cuda_kernel.cu:132, 209).  With scalar_t = c10::Half every Half (op) Half is computed in
+ * fp32 and rounded back to half (c10/util/Half-inl.h), Half + float is a float, so
+ *   pack    (quantization_cuda_kernel.cu:89)   t = half(half(x - min) * scale);
+ *                                              code = rint(max(float(t) + noise - 0.5, 0))
+ *   unpack  (quantization_cuda_kernel.cu:182)  out = half(half(float(code) / scale) + min)
+ * and the statistics of an fp16 activation stay fp16 (exact/exact/ops.py:82-83) and come from half tensor
+ * ops (ops.py:63, 39): mn = min_d x; scale = half(float(half(1 / float(half(mx - mn)))) * (2^bits - 1)).
+ * Halves travel as their bit patterns (uint16).
+ * ---------------------------------------------------------------------------------------------- */
+static inline float h2f(uint16_t b) {
+  _Float16 h;
+  memcpy(&h, &b, 2);
+  return (float)h;
+}
+static inline uint16_t f2h(float f) {
+  _Float16 h = (_Float16)f; /* round to nearest even */
+  uint16_t b;
+  memcpy(&b, &h, 2);
+  return b;
+}
+
+ORC_API void orc_row_stats_f16(const uint16_t *x, int64_t N, int64_t D, int bits, uint16_t *mn,
+                               uint16_t *scale) {
+  const float B = (float)((1 << bits) - 1);
+#pragma omp parallel for schedule(static)
+  for (int64_t n = 0; n < N; n++) {
+    const uint16_t *r = x + n * D;
+    float lo = h2f(r[0]), hi = lo;
+    int nan = isnan(lo);
+    for (int64_t d = 1; d < D; d++) {
+      float v = h2f(r[d]);
+      if (isnan(v)) nan = 1;
+      if (v < lo) lo = v;
+      if (v > hi) hi = v;
+    }
+    if (nan) lo = hi = NAN;
+    float diff = h2f(f2h(hi - lo));
+    float rcp = h2f(f2h(1.0f / diff));
+    mn[n] = f2h(lo);
+    scale[n] = f2h(rcp * B);
+  }
+}
+
+ORC_API void orc_pack_f16(const uint16_t *x, const uint16_t *mn, const uint16_t *scale, const float *noise,
+                          int64_t N, int64_t D, int bits, uint8_t *packed) {
+  const int wpt = 8 / bits;
+  const int64_t G = (N + wpt - 1) / wpt;
+#pragma omp parallel for schedule(static)
+  for (int64_t g = 0; g < G; g++) {
+    for (int64_t d = 0; d < D; d++) {
+      uint8_t acc = 0;
+      for (int ni = 0; ni < wpt; ni++) {
+        int64_t n = g * wpt + ni;
+        if (n >= N) break;
+        int64_t id = n * D + d;
+        float t1 = h2f(f2h(h2f(x[id]) - h2f(mn[n])));
+        float t2 = h2f(f2h(t1 * h2f(scale[n])));
+        double t = (double)(t2 + noise[id]) - 0.5;
+        float tf = (float)fmax(t, 0.0); /* fmax(NaN, 0) = 0 */
+        int32_t v = float2int_rn(tf);
+        acc |= (uint8_t)((uint32_t)v << (ni * bits));
+      }
+      packed[g * D + d] = acc;
+    }
+  }
+}
+
+ORC_API void orc_unpack_f16(const uint8_t *packed, const uint16_t *scale, const uint16_t *mn, int64_t N,
+                            int64_t D, int bits, uint16_t *out) {
+  const int wpt = 8 / bits;
+  const int mask = (1 << bits) - 1;
+  const int64_t G = (N + wpt - 1) / wpt;
+#pragma omp parallel for schedule(static)
+  for (int64_t g = 0; g < G; g++) {
+    for (int ni = 0; ni < wpt; ni++) {
+      int64_t n = g * wpt + ni;
+      if (n >= N) break;
+      const float s = h2f(scale[n]), m = h2f(mn[n]);
+      for (int64_t d = 0; d < D; d++) {
+        int v = (packed[g * D + d] >> (ni * bits)) & mask;
+        float q = h2f(f2h((float)v / s));
+        out[n * D + d] = f2h(q + m);
+      }
+    }
+  }
+}
+
 ORC_API void orc_dequantize_activation(const uint8_t *packed, const uint16_t *scale_bf16,
                                        const uint16_t *min_bf16, int64_t N, int64_t D, int bits,
                                        float *out) {

@@ -184,3 +184,36 @@ def test_oracle_reproduces_reference_kernels():
                 out = oracle.spmm(rowptr, col, val if hv else None, mat, red)
                 assert hashlib.sha256(out.tobytes()).digest() == z[f"spmm{i}_{red}_{hv}"].tobytes(), \
                     f"spmm case {i} {red} {hv}"
+
+
+def test_fp16_oracle_equals_torch_half_ops():
+    """The fp16 restatement (quantize_activation_f16 / unpack_f16) against the same chain written with torch's
+    half tensor ops on CPU, which round every Half (op) Half through fp32 like c10::Half in the reference's
+    half kernels: statistics (ops.py:63, 39), codes (quantization_cuda_kernel.cu:89) and the reconstruction
+    (quantization_cuda_kernel.cu:182), bit for bit."""
+    import torch
+    rng = np.random.default_rng(0)
+    N, D = 3001, 37
+    x = (rng.standard_normal((N, D)) * 3).astype(np.float16)
+    u = rng.random((N, D), dtype=np.float32)
+    for bits in (1, 2, 4, 8):
+        p, s, m = oracle.quantize_activation_f16(x, u, bits)
+        xt = torch.from_numpy(x)
+        mn, mx = xt.min(1)[0], xt.max(1)[0]
+        sc = (2 ** bits - 1) / (mx - mn)
+        assert np.array_equal(sc.numpy().view(np.uint16), s.view(np.uint16))
+        assert np.array_equal(mn.numpy().view(np.uint16), m.view(np.uint16))
+        t = ((xt - mn[:, None]) * sc[:, None]).float() + torch.from_numpy(u)
+        code = torch.clamp((t.double() - 0.5).float(), min=0).round().to(torch.int64).numpy()
+        wpt = 8 // bits
+        G = (N + wpt - 1) // wpt
+        pad = np.zeros((G * wpt, D), np.int64)
+        pad[:N] = code
+        ref = np.zeros((G, D), np.int64)
+        for i in range(wpt):
+            ref |= pad[i::wpt] << (i * bits)
+        assert np.array_equal((ref & 255).astype(np.uint8).ravel(), p)
+        codes = np.stack([(p.reshape(G, D) >> (i * bits)) & ((1 << bits) - 1) for i in range(wpt)], 1)
+        codes = codes.reshape(G * wpt, D)[:N]
+        ref_un = torch.from_numpy(codes.astype(np.float32)).half() / sc[:, None] + mn[:, None]
+        assert np.array_equal(ref_un.numpy().view(np.uint16), oracle.unpack_f16(p, s, m, N, D, bits).view(np.uint16))

@@ -48,6 +48,31 @@ def test_reference_pack_unpack_equal_oracle(shape, bits):
     assert np.array_equal(up.cpu().numpy(), ref_up)
 
 
+@pytest.mark.parametrize("bits", [1, 2, 4, 8])
+@pytest.mark.parametrize("shape", [(4096, 128), (37, 13), (131, 76), (1000, 256)])
+def test_reference_half_pack_unpack_equal_oracle(shape, bits):
+    """The half instantiations of the reference's kernels (quantization_cuda_kernel.cu:132, 209) and torch's
+    half tensor ops for the statistics (ops.py:63, 39) against the fp16 oracle, bit for bit."""
+    rq = _ref("ref_quantization")
+    N, D = shape
+    x = (normal(N, D, 303) * 2.5).astype(np.float16)
+    xt = torch.from_numpy(x).cuda()
+    mn, mx = xt.min(1)[0], xt.max(1)[0]
+    scale = (2 ** bits - 1) / (mx - mn)
+    torch.manual_seed(4321 + bits)
+    offset = int(torch.cuda.default_generators[torch.cuda.current_device()].get_offset())
+    packed = rq.pack_single_precision(xt, mn, mx, scale, bits, True)
+    torch.cuda.synchronize()
+    noise = oracle.noise_reference_pack(4321 + bits, offset, N, D, bits)
+    op, osc, omn = oracle.quantize_activation_f16(x, noise, bits)
+    assert np.array_equal(scale.cpu().numpy().view(np.uint16), osc.view(np.uint16))
+    assert np.array_equal(mn.cpu().numpy().view(np.uint16), omn.view(np.uint16))
+    assert np.array_equal(packed.cpu().numpy().view(np.uint8)[:-1], op)
+    up = rq.unpack_single_precision(packed, bits, scale, mn, N, D)
+    assert up.dtype == torch.float16
+    assert np.array_equal(up.cpu().numpy().view(np.uint16), oracle.unpack_f16(op, osc, omn, N, D, bits).view(np.uint16))
+
+
 def test_fma_contraction_in_reference_pack():
     """quantization_cuda_kernel.cu:89 is compiled with nvcc's default -fmad=true.  On an input large
     enough for the two variants to differ, the reference's binary must match the FMA variant of the
