@@ -55,6 +55,7 @@ SIGNATURES = {
     "exact_act_quantized_forward_f16": (c_int, [c_int, c_ptr, c_i64, c_f32, c_ptr, c_u64, c_u64, c_i64, c_ptr, c_ptr,
                                                 c_ptr]),
     "exact_act_quantized_backward_f16": (c_int, [c_int, c_ptr, c_ptr, c_i64, c_f32, c_ptr, c_ptr]),
+    "exact_spmm_f16": (c_int, [c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_int, c_ptr, c_ptr]),
     "exact_bn_backward_workspace_bytes": (c_i64, [c_i64]),
     "exact_bn_backward_from_packed": (c_int, [c_ptr, c_i64, c_i64, c_ptr, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int,
                                               c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr]),

@@ -81,13 +81,26 @@ def _spmm(rowptr, col, value, mat, reduce, regroup=False, route=None):
         raise RuntimeError("Input mismatch")
     if mat.dim() != 2:
         raise RuntimeError("mat must be [N, K] (batched operands are not used by the GCN/SAGE layers)")
-    if mat.dtype != torch.float32:
-        raise RuntimeError("mat must be float32")
+    if mat.dtype not in (torch.float32, torch.float16):
+        raise RuntimeError("mat must be float32 or float16")
     if rowptr.dtype != col.dtype or col.dtype not in (torch.int32, torch.int64):
         raise RuntimeError("rowptr and col must both be int32 or both int64")
     mat = mat.contiguous()
     rowptr = rowptr.contiguous()
     col = col.contiguous()
+    if mat.dtype == torch.float16:
+        # the reference's half instantiation (spmm_cuda.cu:142): every step rounded to half, rows in CSR order
+        if route is not None:
+            raise RuntimeError("fp16 operands have no routed output")
+        if value is not None:
+            value = value.detach().to(torch.float16).contiguous()
+        M, K = rowptr.numel() - 1, mat.size(1)
+        out = torch.empty((M, K), dtype=torch.float16, device=mat.device)
+        ib = 4 if col.dtype == torch.int32 else 8
+        nnz = col.numel()
+        _lib.invoke("exact_spmm_f16", nnz * (2 * K + ib) + 2 * M * K, _lib.ptr(rowptr), _lib.ptr(col), ib, _lib.ptr(value),
+                    _lib.ptr(mat), M, K, _lib.REDUCE[reduce], _lib.ptr(out), _lib.stream_ptr())
+        return out
     if value is not None:
         value = value.detach().to(torch.float32).contiguous()
     M = rowptr.numel() - 1

@@ -3,6 +3,7 @@ return values of the reference's exact/exact/ops.py.  Arithmetic runs in libexac
 GEMMs and batch norm stay library calls, as in the reference."""
 import numpy as np
 import torch
+from torch.amp import custom_bwd, custom_fwd
 import torch.nn.functional as F
 from torch.autograd.function import Function
 
@@ -165,6 +166,7 @@ class qlinear(Function):
     """ops.py:128-178."""
 
     @staticmethod
+    @custom_fwd(device_type="cuda", cast_inputs=torch.float16)
     def forward(ctx, input, weight, bias=None, quantized=None, randmat=None, scheme=None, rp=True):
         if quantized is not None:
             if randmat is None:
@@ -185,6 +187,7 @@ class qlinear(Function):
         return F.linear(input, weight, bias)
 
     @staticmethod
+    @custom_bwd(device_type="cuda")
     def backward(ctx, grad_output):
         quantized, weight, bias, randmat = ctx.saved
         ori_input_shape, q_input_shape, rp = ctx.other_args
@@ -293,6 +296,7 @@ class qspmm_sum(Function):
     given, the transposed structure for backward comes from its cache."""
 
     @staticmethod
+    @custom_fwd(device_type="cuda", cast_inputs=torch.float16)
     def forward(ctx, row, rowptr, col, value, colptr, csr2csc, has_value, other, quantized=None, randmat=None,
                 scheme=None, storage=None):
         result = spmm.spmm_sum_fw(row, rowptr, col, value, colptr, csr2csc, other)
@@ -312,6 +316,7 @@ class qspmm_sum(Function):
         return result
 
     @staticmethod
+    @custom_bwd(device_type="cuda")
     def backward(ctx, grad_outputs):
         row, rowptr, col, value, colptr, csr2csc, quantized, randmat = ctx.saved
         has_value, ori_input_shape, q_input_shape, value_requires_grad, mat_requires_grad = ctx.other_args
@@ -335,6 +340,7 @@ class qspmm_mean(Function):
     """ops.py:310-371."""
 
     @staticmethod
+    @custom_fwd(device_type="cuda", cast_inputs=torch.float16)
     def forward(ctx, row, rowptr, col, value, rowcount, colptr, csr2csc, has_value, other, quantized=None,
                 randmat=None, scheme=None, storage=None):
         result = spmm.spmm_mean_fw(row, rowptr, col, value, rowcount, colptr, csr2csc, other)
@@ -354,6 +360,7 @@ class qspmm_mean(Function):
         return result
 
     @staticmethod
+    @custom_bwd(device_type="cuda")
     def backward(ctx, grad_outputs):
         row, rowptr, col, value, rowcount, colptr, csr2csc, quantized, randmat = ctx.saved
         has_value, ori_input_shape, q_input_shape, value_requires_grad, mat_requires_grad = ctx.other_args
@@ -403,10 +410,12 @@ class qspmm_max(Function):
     """ops.py:374-403."""
 
     @staticmethod
+    @custom_fwd(device_type="cuda", cast_inputs=torch.float16)
     def forward(ctx, rowptr, col, value, has_value, other, quantized=None, randmat=None, scheme=None):
         return _minmax_forward(ctx, True, rowptr, col, value, has_value, other, quantized, scheme)
 
     @staticmethod
+    @custom_bwd(device_type="cuda")
     def backward(ctx, grad_outputs):
         return _minmax_backward(ctx, grad_outputs)
 
@@ -415,9 +424,11 @@ class qspmm_min(Function):
     """ops.py:406-436."""
 
     @staticmethod
+    @custom_fwd(device_type="cuda", cast_inputs=torch.float16)
     def forward(ctx, rowptr, col, value, has_value, other, quantized=None, randmat=None, scheme=None):
         return _minmax_forward(ctx, False, rowptr, col, value, has_value, other, quantized, scheme)
 
     @staticmethod
+    @custom_bwd(device_type="cuda")
     def backward(ctx, grad_outputs):
         return _minmax_backward(ctx, grad_outputs)

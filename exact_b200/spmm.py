@@ -1,6 +1,7 @@
 """QMatmul / qmatmul: sparse-adjacency x dense aggregation that saves its dense operand compressed.
 Mirrors exact/exact/spmm.py:7-89 for reduce in {sum, add, mean}."""
 import torch
+from torch.amp import custom_bwd, custom_fwd
 import torch.nn.functional as F
 from torch.autograd.function import Function
 
@@ -140,6 +141,7 @@ class qsage_layer(Function):
     Results differ from the separate nodes by fp32 reassociation only."""
 
     @staticmethod
+    @custom_fwd(device_type="cuda", cast_inputs=torch.float16)
     def forward(ctx, src, x, w_l, b_l, w_r, reduce, scheme_x, scheme_l):
         # the input, compressed once (layers.py:153-159)
         q_x, randmat_x, proj_x = project_and_quantize(x, scheme_x, True)
@@ -154,6 +156,7 @@ class qsage_layer(Function):
         return ext_backward_func.linear_forward(agg, w_l, b_l, a2=x if w_r is not None else None, weight2=w_r)
 
     @staticmethod
+    @custom_bwd(device_type="cuda")
     def backward(ctx, grad_output):
         q_x, randmat_x, q_agg, randmat_agg, w_l, b_l, w_r = ctx.saved
         x_shape, proj_x, proj_agg = ctx.other_args
@@ -216,6 +219,8 @@ def sage_layer_applies(src):
     from .dist import ShardedSparseTensor
     if not (config.fuse_sage_layer and config.skip_dead_saves):
         return False
+    if torch.is_autocast_enabled("cuda"):
+        return False   # fp16 operands take the reference's three nodes (half arithmetic of its half kernels)
     if isinstance(src, ShardedSparseTensor):
         return True
     value = src.storage.value()

@@ -273,6 +273,15 @@ EXACT_API int exact_bn_backward_from_packed(const float* grad_out, int64_t N, in
                                             int64_t workspace_bytes, float* grad_input, float* grad_weight,
                                             float* grad_bias, void* stream);
 
+/* CSR SpMM on fp16 operands with the arithmetic of the reference's half instantiation (spmm_cuda.cu:142; AMP runs
+ * cast the operands to fp16, exact/exact/ops.py:260, 313): term = half(value[e] * mat[col[e], c]) (the bare operand
+ * without values), result = half(result + term) in CSR order, mean = half(result / half(max(count, 1))); every
+ * Half (op) Half an fp32 operation on the widened values.  value (or NULL), mat [N, K], out [M, K]: fp16 bit
+ * patterns.  Rounding after every edge makes the order part of the result: one warp sums a row in CSR order
+ * whatever its length. */
+EXACT_API int exact_spmm_f16(const void* rowptr, const void* col, int idx_bytes, const void* value, const void* mat,
+                             int64_t M, int64_t K, int reduce, void* out, void* stream);
+
 /* exact_spmm_split with the second exchange folded into it (no counterpart in the reference): instead of a local
  * [M, K] result followed by exact_rows_scatter, every output row r is stored, by the warp that summed it,
  * straight into its owner's buffer, dst[r / shard][(r % shard) * ldd + col0 + c], c < K (plain stores, peers'

@@ -383,3 +383,16 @@ def unpack_f16(packed, scale, mn, N, D, bits):
     out = np.empty((N, D), np.uint16)
     lib().orc_unpack_f16(_p(packed), _p(_u16(scale)), _p(_u16(mn)), i64(N), i64(D), cint(bits), _p(out))
     return out.view(np.float16)
+
+
+def spmm_f16(rowptr, col, val, mat, reduce="sum"):
+    """CSR x dense on halves with the half arithmetic of the reference's half instantiation (spmm_cuda.cu:142,
+    83-92; reducer.cuh:53-77): every product, every partial sum and the mean's divisor rounded to half."""
+    rowptr = np.ascontiguousarray(rowptr, dtype=np.int64)
+    col = np.ascontiguousarray(col, dtype=np.int64)
+    val = None if val is None else _u16(val)
+    mat = _u16(mat)
+    M, K = rowptr.size - 1, mat.shape[1]
+    out = np.empty((M, K), np.uint16)
+    lib().orc_spmm_f16(_p(rowptr), _p(col), _p(val), _p(mat), i64(M), i64(K), cint({"sum": 0, "mean": 1}[reduce]), _p(out))
+    return out.view(np.float16)

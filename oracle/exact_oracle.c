@@ -518,6 +518,30 @@ ORC_API void orc_spmm(const int64_t *rowptr, const int64_t *col, const float *va
   }
 }
 
+/* CSR SpMM on halves: the reference's half instantiation (spmm_cuda.cu:142; operands cast to fp16 by
+ * exact/exact/ops.py:260, 313 under AMP).  Every Half (op) Half is an fp32 operation rounded back to half
+ * (spmm_cuda.cu:83-92, reducer.cuh:53-60, 72-77):
+ *   term = half(val[e] * mat[col[e], c]) (the bare operand without edge values);
+ *   result = half(result + term) in CSR order from 0;  mean: out = half(result / half(max(count, 1))). */
+ORC_API void orc_spmm_f16(const int64_t *rowptr, const int64_t *col, const uint16_t *val, const uint16_t *mat,
+                          int64_t M, int64_t K, int reduce, uint16_t *out) {
+#pragma omp parallel for schedule(dynamic, 64)
+  for (int64_t r = 0; r < M; r++) {
+    int64_t cnt = rowptr[r + 1] - rowptr[r];
+    float dv = h2f(f2h((float)(cnt > 0 ? cnt : 1)));
+    for (int64_t c = 0; c < K; c++) {
+      float acc = 0.0f;
+      for (int64_t e = rowptr[r]; e < rowptr[r + 1]; e++) {
+        float m = h2f(mat[col[e] * K + c]);
+        if (val) m = h2f(f2h(h2f(val[e]) * m));
+        acc = h2f(f2h(acc + m));
+      }
+      if (reduce == 1) acc = h2f(f2h(acc / dv));
+      out[r * K + c] = f2h(acc);
+    }
+  }
+}
+
 /* spmm_value_bw.  spmm_cuda.cu:172-209: one warp per edge; lane l accumulates val += mat[col, k] * grad[row, k]
  * for k = l, l + 32, ... (one FMA each: nvcc contracts the mul+add), then the lanes are added by
  * val += shfl_down(val, i) for i = 16, 8, 4, 2, 1 (lane 0 holds the result; lanes beyond 31 - i add the value

@@ -106,3 +106,34 @@ def test_mask_activations_on_fp16():
     assert np.array_equal(y.detach().cpu().numpy().view(np.uint16), out.astype(np.float16).view(np.uint16))
     refg = oracle.mask_bw(oracle.dropout_bw(gf, keep, p), rk).astype(np.float16)
     assert np.array_equal(gx.cpu().numpy().view(np.uint16), refg.view(np.uint16))
+
+
+@pytest.mark.parametrize("idx", [torch.int64, torch.int32])
+@pytest.mark.parametrize("reduce", ["sum", "mean"])
+@pytest.mark.parametrize("with_values", [True, False])
+@pytest.mark.parametrize("K", [128, 100, 13, 256])
+def test_spmm_f16_bit_exact(K, with_values, reduce, idx):
+    """SpMM on halves: every product and partial sum rounded to half in CSR order, the mean's divisor rounded to
+    half first (a hub row of 3000 edges: half(3000) = 3000, of 5001: 5000), against the fp16 oracle."""
+    from exact_b200.cpp_extension import spmm as S
+    from helpers import random_csr
+    n = 6000
+    rowptr, col, val = random_csr(n, n, 60000, 21, with_values=True)
+    rng = np.random.default_rng(22)
+    hub = np.sort(rng.choice(n, 5001, replace=False))
+    # replace row 7 by a hub row whose length half precision cannot represent
+    keep = np.repeat(np.arange(n), np.diff(rowptr)) != 7
+    row = np.concatenate([np.repeat(np.arange(n), np.diff(rowptr))[keep], np.full(5001, 7)])
+    colx = np.concatenate([col[keep], hub])
+    valx = np.concatenate([val[keep], rng.standard_normal(5001).astype(np.float32)])
+    order = np.argsort(row * n + colx, kind="stable")
+    row, colx, valx = row[order], colx[order], valx[order]
+    rowptr = np.zeros(n + 1, np.int64)
+    np.cumsum(np.bincount(row, minlength=n), out=rowptr[1:])
+    valh = (valx * 0.5).astype(np.float16) if with_values else None
+    mat = (normal(n, K, 23)).astype(np.float16)
+    ref = oracle.spmm_f16(rowptr, colx, valh, mat, reduce)
+    out = S._spmm(torch.from_numpy(rowptr).to(idx).cuda(), torch.from_numpy(colx).to(idx).cuda(),
+                  None if valh is None else torch.from_numpy(valh).cuda(), torch.from_numpy(mat).cuda(), reduce)
+    assert out.dtype == torch.float16
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), ref.view(np.uint16))

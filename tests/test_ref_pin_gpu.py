@@ -73,6 +73,25 @@ def test_reference_half_pack_unpack_equal_oracle(shape, bits):
     assert np.array_equal(up.cpu().numpy().view(np.uint16), oracle.unpack_f16(op, osc, omn, N, D, bits).view(np.uint16))
 
 
+@pytest.mark.parametrize("reduce", ["sum", "mean"])
+@pytest.mark.parametrize("with_values", [True, False])
+def test_reference_half_spmm_equals_oracle(with_values, reduce):
+    """The half instantiation of the reference's SpMM kernel (spmm_cuda.cu:142) against the fp16 oracle."""
+    rs = _ref("ref_spmm")
+    n, K = 3000, 72
+    rowptr, col, val = random_csr(n, n, 40000, 31, with_values=True)
+    valh = (val * 0.5).astype(np.float16) if with_values else None
+    mat = normal(n, K, 32).astype(np.float16)
+    t = lambda a: torch.from_numpy(a).cuda()
+    v = None if valh is None else t(valh)
+    if reduce == "sum":
+        out = rs.spmm_sum_fw(None, t(rowptr), t(col), v, None, None, t(mat))
+    else:
+        out = rs.spmm_mean_fw(None, t(rowptr), t(col), v, None, None, None, t(mat))
+    ref = oracle.spmm_f16(rowptr, col, valh, mat, reduce)
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), ref.view(np.uint16))
+
+
 def test_fma_contraction_in_reference_pack():
     """quantization_cuda_kernel.cu:89 is compiled with nvcc's default -fmad=true.  On an input large
     enough for the two variants to differ, the reference's binary must match the FMA variant of the
