@@ -96,12 +96,15 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per edge and operand column that one ncu capture of
-# each SpMM entry point moved on a case a few GB small (the kernel sweep's R-MAT graph of 1,200,000 nodes / 60 M
-# edges, operand 20x larger than L2 as in the workload; K = 256; compact rows at 25 % density).  `traffic` of the
-# roofline block is this figure times the edges x columns of an average launch of the run: an estimate that
-# assumes DRAM bytes grow with the gathered volume once the operand is far larger than L2.  None: not captured.
-SPMM_DRAM_BYTES_PER_EDGE_COLUMN = {"exact_spmm_split": None, "exact_spmm_crows": None, "exact_spmm": None}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per edge and operand column, from one ncu capture of
+# each SpMM entry point on a case a few GB small: the kernel sweep's R-MAT graph of 1,200,000 nodes / 62.9 M edges
+# (operand 10x larger than L2), all launches of one call added (row kernel, long-row pieces, their reduction).
+#   K = 256 (128-column tiles):              9.98 GB per call  -> 0.62 bytes per edge and column
+#   K = 32 (narrow-operand kernel, routed):  0.80 GB per call  -> 0.40 bytes per edge and column
+# `traffic` of the roofline block is this figure times the edges x columns of an average launch of the run: an
+# estimate that assumes DRAM bytes grow with the gathered volume once the operand is far larger than L2 (a
+# capture of the full 2.45 M-node graph gave 0.64 for K = 256).
+SPMM_DRAM_BYTES_PER_EDGE_COLUMN = {"exact_spmm_split": 0.62, "exact_spmm": 0.62, "exact_spmm_split_routed": 0.40}
 
 
 def apply_knobs(c, args):

@@ -169,6 +169,34 @@ def run_grad_weight(N, O, k, bits, reps):
             "peak": peak, "peak_kind": kind}
 
 
+def run_bn_bwd(N, D, bits, reps):
+    """Batch-norm backward read from the packed input (two passes over g and the packed bytes, one write) against
+    the route it replaces: unpack to fp32, then ATen's backward on the reconstruction."""
+    from .cpp_extension import backward_func as B
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(N, D, device=dev, generator=gen)
+    g = torch.randn(N, D, device=dev, generator=gen)
+    w = torch.randn(D, device=dev, generator=gen)
+    rm, rv = torch.zeros(D, device=dev), torch.ones(D, device=dev)
+    _, mean, invstd = torch.ops.aten.native_batch_norm(x, w, None, rm, rv, True, 0.1, 1e-5)
+    pk, sb, mb = Q.quantize_pack(x, bits, seed=1, offset=0)
+    q = (pk, bits, sb, mb)
+    del x
+    ms = _time(lambda: B.batch_norm_backward_from_packed(g, q, w, rm, rv, mean, invstd, True, 1e-5, [True, True, True]),
+               reps, None)
+
+    def old():
+        xh = Q.unpack_single_precision(pk, bits, sb, mb, N, D)
+        torch.ops.aten.native_batch_norm_backward(g, xh, w, rm, rv, mean, invstd, True, 1e-5, [True, True, True])
+    ms_old = _time(old, reps, None)
+    nbytes = 12 * N * D + 2 * (N * D * bits // 8 + 4 * N)
+    peak, kind = _peak()
+    return {"op": "bn_backward_from_packed", "N": N, "D": D, "bits": bits, "ms": round(ms, 4),
+            "unpack_plus_aten_ms": round(ms_old, 4), "GB/s": round(nbytes / (ms * 1e-3) / 1e9, 1),
+            "frac": round(nbytes / (ms * 1e-3) / 1e9 / peak, 4), "peak": peak, "peak_kind": kind}
+
+
 def run_mask(N, D, p, reps):
     """ReLU + dropout of a hidden layer in one pass (forward) and its backward: GB/s on 8 bytes + 1 bit per element."""
     dev = torch.device("cuda")
@@ -323,7 +351,7 @@ def main_sharded(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp", "linear", "mask", "grad_weight"])
+    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp", "linear", "mask", "grad_weight", "bn_bwd"])
     ap.add_argument("--kept-frac", type=float, nargs="*", default=[0.5, 0.125])
     ap.add_argument("--N", type=int, nargs="*", default=[100_000, 1_000_000, 10_000_000])
     ap.add_argument("--D", type=int, nargs="*", default=[64, 128, 256, 602])
@@ -356,6 +384,14 @@ def main():
         for N in a.N:
             for bits in a.bits:
                 print(json.dumps(run_grad_weight(N, 256, 32, bits, a.reps)), flush=True)
+        return
+    if a.op == "bn_bwd":
+        for N in a.N:
+            for D in a.D:
+                if N * D * 4 > a.max_bytes or D % 4:
+                    continue
+                for bits in a.bits:
+                    print(json.dumps(run_bn_bwd(N, D, bits, a.reps)), flush=True)
         return
     if a.op == "mask":
         for N in a.N:

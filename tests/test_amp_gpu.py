@@ -46,8 +46,9 @@ def _run(cfg_name, amp, seed=3, nodes=3000):
 def test_autocast_runs_the_half_kernels_and_matches_fp32(cfg_name):
     loss32, out32, g32, calls32 = _run(cfg_name, False)
     loss16, out16, g16, calls16 = _run(cfg_name, True)
-    assert {"exact_quantize_pack_f16", "exact_spmm_f16", "exact_act_quantized_forward_f16",
-            "exact_act_quantized_backward_f16", "exact_unpack_single_precision_f16"} <= calls16
+    assert {"exact_quantize_pack_f16", "exact_spmm_f16", "exact_unpack_single_precision_f16"} <= calls16
+    if cfg_name == "cfg4":   # in configuration 2 the activations follow a batch norm, which autocast keeps in fp32
+        assert {"exact_act_quantized_forward_f16", "exact_act_quantized_backward_f16"} <= calls16
     assert not any(name.endswith("_f16") for name in calls32)
     assert abs(loss16 - loss32) < 2e-2 * abs(loss32)
     assert float((out16 - out32).norm() / out32.norm()) < 3e-2

@@ -58,13 +58,15 @@ def test_quantize_and_dequantize_activation_keep_fp16():
     """ops.py:69-98 on an fp16 activation: fp16 statistics in, fp16 reconstruction out, error within one
     quantisation step."""
     config.manual_seed(3)
+    config.compress_activation, config.simulate, config.activation_compression_bits = True, False, [2]
     x = torch.from_numpy(_half(2000, 64, 9)).cuda()
     q = ops.quantize_activation(x, None)
     assert q[2].dtype == torch.float16 and q[3].dtype == torch.float16
     xh = ops.dequantize_activation(q, x.shape)
     assert xh.dtype == torch.float16 and xh.shape == x.shape
     step = (x.float().max(1)[0] - x.float().min(1)[0]) / (2 ** config.activation_compression_bits[0] - 1)
-    assert bool(((xh.float() - x.float()).abs() <= 1.02 * step[:, None] + 2e-2).all())
+    # one quantisation step plus the half roundings of x - min, code / scale and + min (values up to 16: 2^-6 each)
+    assert bool(((xh.float() - x.float()).abs() <= 1.02 * step[:, None] + 5e-2).all())
 
 
 def test_mask_activations_on_fp16():
