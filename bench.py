@@ -218,6 +218,7 @@ def run_b200(args):
     config.compact_operand = not args.dense_gather
     config.peer_exchange = not args.no_peer_exchange
     config.column_split_aggregation = not args.row_split
+    config.routed_aggregation_output = bool(args.routed_output)
     config.cache_constant_gather = False   # every timed step exchanges its input features again
     net = cls(c["feats"], c["hidden"], c["classes"], c["layers"], dropout=c["dropout"], batch_norm=c["batch_norm"])
     net = (QModule(net) if c["use_qmodule"] else net).to(dev).train()
@@ -727,6 +728,9 @@ def main():
     ap.add_argument("--row-split", action="store_true",
                     help="N > 1: aggregate on row shards of the adjacency (exchange whole operand rows) instead of "
                          "switching to column slices around each aggregation")
+    ap.add_argument("--routed-output", action="store_true",
+                    help="N > 1: the SpMM of the feature-parallel aggregation stores its result rows straight into "
+                         "their owners' buffers instead of a local result followed by a scatter kernel")
     ap.add_argument("--cpu-reference", action="store_true",
                     help="--impl reference: time the CPU restatement even when the reference's CUDA kernels are built")
     # the reference drivers' knobs (mem_speed_bench/arxiv/train_full_batch.py:44-48)

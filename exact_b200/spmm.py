@@ -7,8 +7,9 @@ from torch.autograd.function import Function
 
 from .conf import config
 from .cpp_extension import backward_func as ext_backward_func
+from .cpp_extension import quantization as ext_quantization
 from .cpp_extension import spmm as ext_spmm
-from .ops import (linear_backward_from_compressed, project_and_quantize, qspmm_max, qspmm_mean, qspmm_min,
+from .ops import (_rademacher, linear_backward_from_compressed, project_and_quantize, qspmm_max, qspmm_mean, qspmm_min,
                   qspmm_sum)
 from .qscheme import QScheme
 from .utils import empty_cache
@@ -147,6 +148,39 @@ class qsage_layer(Function):
         q_x, randmat_x, proj_x = project_and_quantize(x, scheme_x, True)
         if w_r is None:
             q_x = randmat_x = None   # drawn (the noise stream stays that of the separate nodes), read by nothing
+        out_f, in_f = w_l.shape
+        k_agg = int(config.kept_frac * in_f + 0.999)
+        kp, op = (k_agg + 3) // 4 * 4, (out_f + 3) // 4 * 4
+        if (config.aggregate_projected_first and config.kept_frac < 1.0 and config.compress_activation
+                and not config.simulate and not config.swap and x.dtype == torch.float32
+                and kp + op < in_f):
+            # Few outputs (the last layer): the aggregation is linear, so reduce(A, x) R = reduce(A, x R) and
+            # reduce(A, x) W_l^T = reduce(A, x W_l^T).  One GEMM forms [x R | x W_l^T], the SpMM (and, row-
+            # sharded, both exchanges) then works on k + out_features columns instead of in_features, and its
+            # result holds the projected aggregate that lin_l saves (ops.py:142-149) and lin_l's output.  R and
+            # the rounding noise are drawn where the separate nodes draw them.
+            with torch.no_grad():
+                off_r, off_n = config.next_offset(), config.next_offset()
+                randmat_agg = _rademacher(in_f, k_agg, x.device, x.dtype, offset=off_r)
+                wcat = x.new_zeros((kp + op, in_f))
+                wcat[:k_agg].copy_(randmat_agg.t())
+                wcat[kp:kp + out_f].copy_(w_l)
+                t = _aggregate(src, ext_backward_func.linear_forward(x, wcat), reduce, tag="fw%d" % (kp + op))
+                q_bits = config.activation_compression_bits[0]
+                q_in, q_scale, q_min = ext_quantization.quantize_pack(t[:, :k_agg].contiguous(), q_bits, offset=off_n)
+                q_agg = (q_in, q_bits, q_scale, q_min)
+                if config.quantized_hook is not None:
+                    config.quantized_hook(q_agg, randmat_agg)
+                y = t[:, kp:kp + out_f].contiguous()
+                if b_l is not None:
+                    y += b_l
+                if w_r is not None:
+                    y = ext_backward_func.linear_forward(x, w_r, None, out=y, accumulate=True)
+            empty_cache(config.empty_cache_threshold)
+            ctx.src, ctx.reduce = src, reduce
+            ctx.saved = q_x, randmat_x, q_agg, randmat_agg, w_l, b_l, w_r
+            ctx.other_args = x.shape, proj_x, torch.Size([x.shape[0], k_agg])
+            return y
         agg = _aggregate(src, x, reduce, tag="fw%d" % x.size(1))
         q_agg, randmat_agg, proj_agg = project_and_quantize(agg, scheme_l, True)
         empty_cache(config.empty_cache_threshold)

@@ -47,8 +47,9 @@ def _np(t):
     return t.detach().contiguous().numpy()
 
 
-def compress(cfg, x, rp=True):
-    """(input2rp ->) quantize_activation: exact/exact/ops.py:142-149 -> saved tuple."""
+def compress(cfg, x, rp=True, fused=None):
+    """(input2rp ->) quantize_activation: exact/exact/ops.py:142-149 -> saved tuple.  `fused` = False: the CUDA
+    side quantises this tensor with the plain pack kernel (its noise stream) whatever the shape."""
     x = _np(x)
     N, D = x.shape
     R = None
@@ -57,7 +58,7 @@ def compress(cfg, x, rp=True):
         k = int(cfg.kept_frac * D + 0.999)
         R = oracle.rademacher(cfg.noise.seed, cfg.noise.next(), D, k)
         x = oracle.input2rp(x, R)
-        rows_keyed = _rp_fused(cfg, D, k) and cfg.compress
+        rows_keyed = _rp_fused(cfg, D, k) and cfg.compress and fused is not False
     if not cfg.compress:
         return ("raw", x.copy(), R, (N, D))
     if rows_keyed:
@@ -185,7 +186,15 @@ def sage_forward(cfg, params, x, adj, n_layers, dropout):
     for i in range(n_layers):
         shared = compress(cfg, x)
         agg = OSpmm.apply(adj, x, "mean")
-        h = OQLinear.apply(cfg, agg, params[f"convs.{i}.lin_l.weight"], params[f"convs.{i}.lin_l.bias"], None)
+        # The CUDA layer with few outputs aggregates [x R | x W_l^T] (the same numbers up to fp32 reassociation) and
+        # then packs the projected aggregate with the plain pack kernel: same values, that kernel's noise stream.
+        w_l = params[f"convs.{i}.lin_l.weight"]
+        k = int(cfg.kept_frac * w_l.shape[1] + 0.999)
+        pad4 = lambda v: (v + 3) // 4 * 4
+        reordered = (getattr(cfg, "reorder_sage", True) and cfg.kept_frac < 1.0 and cfg.compress
+                     and pad4(k) + pad4(w_l.shape[0]) < w_l.shape[1])
+        saved_agg = compress(cfg, agg, fused=False) if reordered else None
+        h = OQLinear.apply(cfg, agg, w_l, params[f"convs.{i}.lin_l.bias"], saved_agg)
         h = h + OQLinear.apply(cfg, x, params[f"convs.{i}.lin_r.weight"], None, shared)
         if i == n_layers - 1:
             return h

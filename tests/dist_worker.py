@@ -25,6 +25,7 @@ def main():
     ap.add_argument("--peer", type=int, default=1)
     ap.add_argument("--compact", type=int, default=1)
     ap.add_argument("--colsplit", type=int, default=1)
+    ap.add_argument("--routed", type=int, default=0)
     a = ap.parse_args()
 
     import torch
@@ -46,6 +47,7 @@ def main():
     config.peer_exchange = bool(a.peer)
     config.compact_operand = bool(a.compact)
     config.column_split_aggregation = bool(a.colsplit)
+    config.routed_aggregation_output = bool(a.routed)
     config.cache_constant_gather = False
     if a.world > 1:
         adj = xdist.shard_graph(full, "mean", a.rank, a.world)

@@ -52,7 +52,9 @@ def test_autocast_runs_the_half_kernels_and_matches_fp32(cfg_name):
     assert not any(name.endswith("_f16") for name in calls32)
     assert abs(loss16 - loss32) < 2e-2 * abs(loss32)
     assert float((out16 - out32).norm() / out32.norm()) < 3e-2
+    # a bias in front of a batch norm has a gradient of rounding noise only: compare against the layer's scale
+    scale = max(float(v.norm()) for v in g32.values())
     for k, g in g16.items():
         assert g.dtype == torch.float32 and bool(torch.isfinite(g).all()), k
-        rel = float((g - g32[k]).norm() / (g32[k].norm() + 1e-30))
-        assert rel < 0.1, (k, rel)
+        err = float((g - g32[k]).norm())
+        assert err < 0.1 * float(g32[k].norm()) + 2e-3 * scale, (k, err, float(g32[k].norm()))

@@ -83,11 +83,13 @@ def _compare_with_single(parts, single, regrouped=False):
             assert torch.equal(a, b)                          # replicas stay in step
 
 
+@pytest.mark.parametrize("routed", [0, 1])
 @pytest.mark.parametrize("world", [2, 8])
-def test_sharded_run_with_feature_parallel_aggregation(world, single, tmp_path):
+def test_sharded_run_with_feature_parallel_aggregation(world, routed, single, tmp_path):
     """The default route: column slices of every row to every rank, the whole adjacency times the slice, row
-    blocks of the result back to their owners (per-row sums regrouped: several edges per load instruction)."""
-    parts = _run(world, tmp_path, "cols", peer=1, colsplit=1)
+    blocks of the result back to their owners, by a scatter kernel (default) or stored by the SpMM itself
+    (routed).  The pieces of long rows are summed separately, so sums are regrouped."""
+    parts = _run(world, tmp_path, "cols%d" % routed, peer=1, colsplit=1, routed=routed)
     assert all(p["peers_used"] for p in parts), "the ranks could not map each other's buffers"
     assert all(p["exchange"].startswith("feature-parallel") for p in parts)
     _compare_with_single(parts, single, regrouped=True)

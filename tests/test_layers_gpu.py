@@ -179,10 +179,13 @@ def test_one_node_sage_layer_is_a_reassociation(cfg_name, nodes):
     runs = []
     for fuse, first in ((True, True), (True, False), (False, True)):
         config.fuse_sage_layer, config.aggregate_gradient_first = fuse, first
+        # the separate nodes pack the last layer's aggregate with the fused projection kernel's noise stream
+        config.aggregate_projected_first = False
         try:
             loss, out, grads, _, _, _ = run_model(cfg_name, nodes, seed=6, fused_rp=True)
         finally:
             config.fuse_sage_layer, config.aggregate_gradient_first = True, True
+            config.aggregate_projected_first = True
         runs.append((loss, out, grads))
     # inside the node the order of the backward products does not touch the forward pass
     assert runs[0][0] == runs[1][0] and torch.equal(runs[0][1], runs[1][1])
@@ -191,6 +194,40 @@ def test_one_node_sage_layer_is_a_reassociation(cfg_name, nodes):
     assert abs(runs[0][0] - runs[2][0]) < 1e-5 * abs(runs[2][0]) and relfro(runs[0][1], runs[2][1]) < 1e-5
     for k, g in runs[0][2].items():
         assert relfro(g, runs[2][2][k]) < 3e-2, (k, relfro(g, runs[2][2][k]))
+
+
+@pytest.mark.parametrize("cfg_name,nodes", [("cfg3", 2000), ("cfg4", 3000)])
+def test_last_layer_aggregates_projected_first(cfg_name, nodes):
+    """A SAGE layer with few outputs aggregates [x R | x W_l^T] instead of x (aggregation is linear): the model's
+    output and loss equal those of the plain order up to fp32 reassociation, and so do the gradients up to the
+    different rounding noise of the one saved tensor that is packed by another kernel (the last layer's projected
+    aggregate, which only lin_l's weight gradient reads)."""
+    runs = []
+    for flag in (True, False):
+        config.aggregate_projected_first = flag
+        try:
+            loss, out, grads, oloss, oout, ograds = run_model(cfg_name, nodes, seed=9, fused_rp=True)
+        finally:
+            config.aggregate_projected_first = True
+        runs.append((loss, out, grads))
+        if flag:   # the CPU restatement (reference order) with the same noise
+            assert abs(loss - oloss) < 1e-4 * abs(oloss) and relfro(out, oout) < 1e-4
+            for k, g in grads.items():
+                assert relfro(g, ograds[k]) < 0.15, k
+    assert abs(runs[0][0] - runs[1][0]) < 1e-5 * abs(runs[1][0]) and relfro(runs[0][1], runs[1][1]) < 1e-5
+    c = graphs.CONFIGS[cfg_name]
+    pad4 = lambda v: (v + 3) // 4 * 4
+    reordered = set()
+    for i in range(c["layers"]):
+        in_f = c["feats"] if i == 0 else c["hidden"]
+        out_f = c["classes"] if i == c["layers"] - 1 else c["hidden"]
+        if pad4(int(c["kept_frac"] * in_f + 0.999)) + pad4(out_f) < in_f:
+            reordered.add(f"convs.{i}.lin_l.weight")
+    assert reordered
+    for k, g in runs[0][2].items():
+        if k in reordered:
+            continue    # read from the differently rounded saved tensor: equal within the quantisation noise only
+        assert relfro(g, runs[1][2][k]) < 3e-2, (k, relfro(g, runs[1][2][k]))
 
 
 @pytest.mark.parametrize("cfg_name,nodes", [("cfg2", 3000), ("cfg4", 3000)])
