@@ -70,6 +70,9 @@ class QuantizationConfig:
         # kernel takes the rows in length-sorted order, and rows of 48 - 256 bytes stored over NVLink in that order
         # moved at about 100 GB/s (26.6 ms of SpMM per epoch at 4 GPUs against 10.4 ms + 2 ms for result + scatter).
         self.routed_aggregation_output = False
+        # The first exchange of the feature-parallel aggregation runs on a side stream while the layer's work that
+        # does not need the aggregate (compressing x, x W_r^T, the weight gradients) runs on the main stream.
+        self.overlap_exchange = True
         # Row shards write their compact rows straight into every peer's buffer (plain stores over NVLink,
         # buffers mapped with CUDA IPC) instead of going through a collective; off, or when the mapping
         # fails, the collective-library exchange is used.

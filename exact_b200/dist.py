@@ -213,7 +213,7 @@ class ShardedSparseTensor:
             self._sync = torch.zeros(1, dtype=torch.int32, device=device)
         all_reduce(self._sync, group=self.group)
 
-    def aggregate(self, x_local, reduce, transposed=False, rowscale=None, unweighted=False):
+    def aggregate(self, x_local, reduce, transposed=False, rowscale=None, unweighted=False, meanwhile=None):
         """reduce(A, x) (or A^T x when `transposed`: spmm.cc:70-77, 128-137) for this rank's rows, with x given
         by rows: [local_rows, K] on every rank.  Feature-parallel: every rank receives a slice of Kp = ceil(K / P)
         columns of ALL rows (each rank stores its rows' slices into the peers' buffers), multiplies the whole
@@ -221,7 +221,9 @@ class ShardedSparseTensor:
         all-to-all exchanges of N K / P elements per rank instead of an all-gather of N K (P - 1) / P, equal work
         on every rank whatever the degree distribution, and gathers over a P times narrower operand.  Per-row
         sums are regrouped (several edges per load instruction on the narrow slices).  Returns None when the
-        ranks cannot write each other's memory (the caller takes the row-split route)."""
+        ranks cannot write each other's memory (the caller takes the row-split route; `meanwhile` has then not
+        been called).  `meanwhile`: work of the caller that does not depend on the result; it is enqueued on the
+        current stream while the first exchange (NVLink-bound stores, issued on a side stream) is in flight."""
         n_loc, K = x_local.shape
         dev = x_local.device
         P, S, N = self.world, self.shard, self.n_global
@@ -236,7 +238,18 @@ class ShardedSparseTensor:
             return None
         x_local = x_local if (x_local.stride(1) == 1 and x_local.stride(0) % 4 == 0 and x_local.data_ptr() % 16 == 0) \
             else x_local.contiguous()
-        ext_rows.cols_scatter(x_local, rowscale, self.row_start, Kp, inb.ptrs)
+        if meanwhile is not None and config.overlap_exchange:
+            main = torch.cuda.current_stream(dev)
+            side = self._side_stream(dev)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                ext_rows.cols_scatter(x_local, rowscale, self.row_start, Kp, inb.ptrs)
+            meanwhile()
+            main.wait_stream(side)      # x_local and rowscale stay alive in this frame until both streams have joined
+        else:
+            ext_rows.cols_scatter(x_local, rowscale, self.row_start, Kp, inb.ptrs)
+            if meanwhile is not None:
+                meanwhile()
         self._order_peer_stores(dev)
         slice_all = inb.local_tensor().view(torch.float32).view(P * S, Kp)[:N]
         if transposed:
@@ -256,6 +269,12 @@ class ShardedSparseTensor:
         out = outb.local_tensor().view(torch.float32).view(S, P * Kp)[:n_loc]
         # the buffer is written again two aggregations of this width later: callers consume the result at once
         return out if K == P * Kp else out[:, :K].contiguous()
+
+    def _side_stream(self, dev):
+        st = getattr(self, "_side", None)
+        if st is None:
+            st = self._side = torch.cuda.Stream(device=dev)
+        return st
 
     def describe_exchange(self):
         if self._col_bufs:

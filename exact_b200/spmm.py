@@ -74,13 +74,16 @@ def _operand(src, x, tag, rowscale=None):
     return x if rowscale is None else x * rowscale.unsqueeze(1)
 
 
-def _aggregate(src, other, reduce, tag="fw"):
-    """reduce(A, other) with nothing recorded for backward."""
+def _aggregate(src, other, reduce, tag="fw", meanwhile=None):
+    """reduce(A, other) with nothing recorded for backward.  `meanwhile` (optional): work of the caller that does
+    not need the result; a row-sharded source runs it while its first exchange is in flight."""
     from .dist import ShardedSparseTensor
     if isinstance(src, ShardedSparseTensor):
-        out = src.aggregate(other, reduce)
+        out = src.aggregate(other, reduce, meanwhile=meanwhile)
         if out is not None:
             return out
+    if meanwhile is not None:
+        meanwhile()
     operand = _operand(src, other, tag)
     if isinstance(src, ShardedSparseTensor):
         return ext_spmm._spmm(src.rowptr, src.col, src.value, operand, reduce)
@@ -88,7 +91,7 @@ def _aggregate(src, other, reduce, tag="fw"):
     return ext_spmm._spmm(rowptr, col, value, operand, reduce)
 
 
-def _aggregate_transposed(src, grad, reduce, rowscale=None, prescaled=False, tag="bw"):
+def _aggregate_transposed(src, grad, reduce, rowscale=None, prescaled=False, tag="bw", meanwhile=None):
     """Gradient of reduce(A, other) with respect to `other` (spmm.cc:70-77, 128-137).  Inside the one-node
     layer the result is an fp32 regrouping of the separate nodes' anyway, so the SpMM may regroup too.
     With `rowscale` = 1 / max(deg, 1) the caller asks for A_mean^T g as A^T (D^-1 g): the rows of `grad` are
@@ -96,9 +99,11 @@ def _aggregate_transposed(src, grad, reduce, rowscale=None, prescaled=False, tag
     less: 10.0 against 12.0 ms at 125.8 M edges x 256 columns).  `prescaled`: `grad` already holds D^-1 g."""
     from .dist import ShardedSparseTensor
     if isinstance(src, ShardedSparseTensor):
-        out = src.aggregate(grad, reduce, transposed=True, rowscale=rowscale, unweighted=prescaled)
+        out = src.aggregate(grad, reduce, transposed=True, rowscale=rowscale, unweighted=prescaled, meanwhile=meanwhile)
         if out is not None:
             return out
+    if meanwhile is not None:
+        meanwhile()
     operand = _operand(src, grad, tag, rowscale)
     unweighted = rowscale is not None or prescaled
     if isinstance(src, ShardedSparseTensor):
@@ -144,16 +149,44 @@ class qsage_layer(Function):
     @staticmethod
     @custom_fwd(device_type="cuda", cast_inputs=torch.float16)
     def forward(ctx, src, x, w_l, b_l, w_r, reduce, scheme_x, scheme_l):
+        from .dist import ShardedSparseTensor
+        # Row-sharded: what does not need the aggregate (compressing x, x W_r^T + b) is enqueued while the first
+        # exchange of the aggregation is in flight; lin_l's product is then added to it.
+        overlap = (isinstance(src, ShardedSparseTensor) and config.overlap_exchange
+                   and config.column_split_aggregation)
+        early = {}
+
+        def lin_r_early():
+            if w_r is not None:
+                early["y"] = ext_backward_func.linear_forward(x, w_r, b_l)
+
+        def compress_x_and_lin_r():
+            early["q"] = project_and_quantize(x, scheme_x, True)
+            lin_r_early()
+
+        out_f, in_f = w_l.shape
+        k_agg = int(config.kept_frac * in_f + 0.999)
+        kp, op = (k_agg + 3) // 4 * 4, (out_f + 3) // 4 * 4
+        reorder = (config.aggregate_projected_first and config.kept_frac < 1.0 and config.compress_activation
+                   and not config.simulate and not config.swap and x.dtype == torch.float32 and kp + op < in_f)
+        if overlap and not reorder:
+            agg = _aggregate(src, x, reduce, tag="fw%d" % x.size(1), meanwhile=compress_x_and_lin_r)
+            q_x, randmat_x, proj_x = early["q"]
+            if w_r is None:
+                q_x = randmat_x = None
+            q_agg, randmat_agg, proj_agg = project_and_quantize(agg, scheme_l, True)
+            empty_cache(config.empty_cache_threshold)
+            ctx.src, ctx.reduce = src, reduce
+            ctx.saved = q_x, randmat_x, q_agg, randmat_agg, w_l, b_l, w_r
+            ctx.other_args = x.shape, proj_x, proj_agg
+            if w_r is None:
+                return ext_backward_func.linear_forward(agg, w_l, b_l)
+            return ext_backward_func.linear_forward(agg, w_l, None, out=early["y"], accumulate=True)
         # the input, compressed once (layers.py:153-159)
         q_x, randmat_x, proj_x = project_and_quantize(x, scheme_x, True)
         if w_r is None:
             q_x = randmat_x = None   # drawn (the noise stream stays that of the separate nodes), read by nothing
-        out_f, in_f = w_l.shape
-        k_agg = int(config.kept_frac * in_f + 0.999)
-        kp, op = (k_agg + 3) // 4 * 4, (out_f + 3) // 4 * 4
-        if (config.aggregate_projected_first and config.kept_frac < 1.0 and config.compress_activation
-                and not config.simulate and not config.swap and x.dtype == torch.float32
-                and kp + op < in_f):
+        if reorder:
             # Few outputs (the last layer): the aggregation is linear, so reduce(A, x) R = reduce(A, x R) and
             # reduce(A, x) W_l^T = reduce(A, x W_l^T).  One GEMM forms [x R | x W_l^T], the SpMM (and, row-
             # sharded, both exchanges) then works on k + out_features columns instead of in_features, and its
@@ -165,17 +198,21 @@ class qsage_layer(Function):
                 wcat = x.new_zeros((kp + op, in_f))
                 wcat[:k_agg].copy_(randmat_agg.t())
                 wcat[kp:kp + out_f].copy_(w_l)
-                t = _aggregate(src, ext_backward_func.linear_forward(x, wcat), reduce, tag="fw%d" % (kp + op))
+                t = _aggregate(src, ext_backward_func.linear_forward(x, wcat), reduce, tag="fw%d" % (kp + op),
+                               meanwhile=lin_r_early if overlap else None)
                 q_bits = config.activation_compression_bits[0]
                 q_in, q_scale, q_min = ext_quantization.quantize_pack(t[:, :k_agg].contiguous(), q_bits, offset=off_n)
                 q_agg = (q_in, q_bits, q_scale, q_min)
                 if config.quantized_hook is not None:
                     config.quantized_hook(q_agg, randmat_agg)
-                y = t[:, kp:kp + out_f].contiguous()
-                if b_l is not None:
-                    y += b_l
-                if w_r is not None:
-                    y = ext_backward_func.linear_forward(x, w_r, None, out=y, accumulate=True)
+                if "y" in early:
+                    y = early["y"].add_(t[:, kp:kp + out_f])
+                else:
+                    y = t[:, kp:kp + out_f].contiguous()
+                    if b_l is not None:
+                        y += b_l
+                    if w_r is not None:
+                        y = ext_backward_func.linear_forward(x, w_r, None, out=y, accumulate=True)
             empty_cache(config.empty_cache_threshold)
             ctx.src, ctx.reduce = src, reduce
             ctx.saved = q_x, randmat_x, q_agg, randmat_agg, w_l, b_l, w_r
@@ -196,28 +233,38 @@ class qsage_layer(Function):
         x_shape, proj_x, proj_agg = ctx.other_args
         del ctx.saved
         g = grad_output.contiguous()
-        grad_w_r = None
         k_agg, k_x = proj_agg[1], proj_x[1]
         both_projected = randmat_agg is not None and (w_r is None or randmat_x is not None)
-        if (config.compress_activation and not config.simulate and not config.swap and q_agg[1] is not None
-                and config.grad_weight_in_projected_space and both_projected
-                and ext_backward_func.grad_weight_supported(g, k_agg, k_x if w_r is not None else 0, q_agg[1])):
-            # both weight gradients in one pass over g: g^T [Xq_agg | Xq_x] on the tensor cores, dequantised
-            # on the way in, then the two small transposed projections
-            ga, gx = ext_backward_func.grad_weight_from_packed(g, q_agg, k_agg, q_x if w_r is not None else None, k_x)
-            grad_w_l = ga.mm(randmat_agg.t())
-            grad_b = g.sum(0) if b_l is not None else None
-            if w_r is not None:
-                grad_w_r = gx.mm(randmat_x.t())
-        else:
-            _, grad_w_l, grad_b = linear_backward_from_compressed(q_agg, w_l, b_l, randmat_agg, x_shape, proj_agg, True,
-                                                                  g, False)
-            if w_r is not None:
-                _, grad_w_r, _ = linear_backward_from_compressed(q_x, w_r, None, randmat_x, x_shape, proj_x, True, g,
-                                                                 False)
+        wg = {}
+
+        def weight_grads():
+            grad_w_r = None
+            if (config.compress_activation and not config.simulate and not config.swap and q_agg[1] is not None
+                    and config.grad_weight_in_projected_space and both_projected
+                    and ext_backward_func.grad_weight_supported(g, k_agg, k_x if w_r is not None else 0, q_agg[1])):
+                # both weight gradients in one pass over g: g^T [Xq_agg | Xq_x] on the tensor cores, dequantised
+                # on the way in, then the two small transposed projections
+                ga, gx = ext_backward_func.grad_weight_from_packed(g, q_agg, k_agg, q_x if w_r is not None else None,
+                                                                   k_x)
+                grad_w_l = ga.mm(randmat_agg.t())
+                grad_b = g.sum(0) if b_l is not None else None
+                if w_r is not None:
+                    grad_w_r = gx.mm(randmat_x.t())
+            else:
+                _, grad_w_l, grad_b = linear_backward_from_compressed(q_agg, w_l, b_l, randmat_agg, x_shape, proj_agg,
+                                                                      True, g, False)
+                if w_r is not None:
+                    _, grad_w_r, _ = linear_backward_from_compressed(q_x, w_r, None, randmat_x, x_shape, proj_x, True,
+                                                                     g, False)
+            wg["l"], wg["b"], wg["r"] = grad_w_l, grad_b, grad_w_r
+
+        out_f, in_f = w_l.shape
+        # row-sharded: the weight gradients are enqueued while the first exchange of the aggregation is in flight
+        aggregated_first = ctx.needs_input_grad[1] and config.aggregate_gradient_first and out_f <= in_f
+        if not aggregated_first:
+            weight_grads()
         grad_x = None
         if ctx.needs_input_grad[1]:
-            out_f, in_f = w_l.shape
             # With out_features <= in_features the transposed aggregation runs on g itself: fewer (or as
             # many) columns for the SpMM, one GEMM over [A^T g | g] instead of two, and, row-sharded, a
             # gathered operand that has passed the ReLU / dropout masks (mostly zeros, sent compacted)
@@ -237,14 +284,14 @@ class qsage_layer(Function):
                     wp = w_l.new_zeros((out_f + pad, in_f))
                     wp[:out_f].copy_(w_l)
                 t = _aggregate_transposed(ctx.src, gp, ctx.reduce, rowscale=inv, prescaled=prescaled,
-                                          tag="bw%d" % gp.size(1))
+                                          tag="bw%d" % gp.size(1), meanwhile=weight_grads)
                 grad_x = ext_backward_func.linear_forward(t, wp.t(), None, a2=g if w_r is not None else None,
                                                           weight2=w_r.t() if w_r is not None else None)
             else:
                 grad_x = _aggregate_transposed(ctx.src, ext_backward_func.linear_forward(g, w_l.t()), ctx.reduce)
                 if w_r is not None:
                     grad_x = ext_backward_func.linear_forward(g, w_r.t(), None, out=grad_x, accumulate=True)
-        return None, grad_x, grad_w_l, grad_b, grad_w_r, None, None, None
+        return None, grad_x, wg["l"], wg["b"], wg["r"], None, None, None
 
 
 def sage_layer_applies(src):
