@@ -217,7 +217,7 @@ def run_b200(args):
     config.compact_gather = not args.dense_gather
     config.compact_operand = not args.dense_gather
     config.peer_exchange = not args.no_peer_exchange
-    config.column_split_aggregation = not args.row_split
+    config.column_split_aggregation = False if args.row_split else (True if args.column_split else None)
     config.routed_aggregation_output = bool(args.routed_output)
     config.cache_constant_gather = False   # every timed step exchanges its input features again
     net = cls(c["feats"], c["hidden"], c["classes"], c["layers"], dropout=c["dropout"], batch_norm=c["batch_norm"])
@@ -725,6 +725,8 @@ def main():
     ap.add_argument("--dense-gather", action="store_true", help="N > 1: exchange dense rows (no zero compaction)")
     ap.add_argument("--no-peer-exchange", action="store_true",
                     help="N > 1: exchange through the collective library only (no rank writes a peer's memory)")
+    ap.add_argument("--column-split", action="store_true",
+                    help="N > 1: feature-parallel aggregation at every N (default: from 8 ranks on)")
     ap.add_argument("--row-split", action="store_true",
                     help="N > 1: aggregate on row shards of the adjacency (exchange whole operand rows) instead of "
                          "switching to column slices around each aggregation")

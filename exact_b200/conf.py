@@ -63,8 +63,11 @@ class QuantizationConfig:
         self.compact_operand_max_density = 0.5
         # Row-sharded runs: aggregate feature-parallel (every rank multiplies the whole adjacency with a column
         # slice of the operand; two all-to-all exchanges written into the peers' buffers) instead of gathering
-        # all rows of the operand on every rank.  Needs peer_exchange; per-row sums are then regrouped.
-        self.column_split_aggregation = True
+        # all rows of the operand on every rank.  Needs peer_exchange; the pieces of long rows are then summed
+        # separately.  None: from 8 ranks on (measured per epoch of the 2.45 M-node benchmark: 37.9 against 36.5 ms
+        # at 2 ranks, 23.1 against 21.4 ms at 4; the gathered volume of the row split grows with the ranks, the
+        # two exchanges of the column split shrink).  True / False: always / never.
+        self.column_split_aggregation = None
         # ... on: every rank's SpMM stores its result rows straight into their owners' buffers (the second exchange
         # folded into the kernel); off: a local result followed by a scatter kernel.  Off by default: the narrow
         # kernel takes the rows in length-sorted order, and rows of 48 - 256 bytes stored over NVLink in that order
@@ -72,7 +75,8 @@ class QuantizationConfig:
         self.routed_aggregation_output = False
         # The first exchange of the feature-parallel aggregation runs on a side stream while the layer's work that
         # does not need the aggregate (compressing x, x W_r^T, the weight gradients) runs on the main stream.
-        self.overlap_exchange = True
+        self.overlap_exchange = False   # measured at 4 ranks: 25.1 ms per epoch against 23.1 without (the overlapped
+        #                                 kernels share SMs and HBM with the exchange and slow down by more than it hides)
         # Row shards write their compact rows straight into every peer's buffer (plain stores over NVLink,
         # buffers mapped with CUDA IPC) instead of going through a collective; off, or when the mapping
         # fails, the collective-library exchange is used.

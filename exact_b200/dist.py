@@ -44,6 +44,13 @@ def all_reduce(t, op=dist.ReduceOp.SUM, group=None):
         dist.all_reduce(t, op=op, group=group)
 
 
+def column_split_active(world):
+    """Whether a run of `world` ranks aggregates feature-parallel (config.column_split_aggregation; None: from 8
+    ranks on)."""
+    flag = config.column_split_aggregation
+    return world >= 8 if flag is None else bool(flag)
+
+
 def shard_rows(n, world):
     """Rows per shard: ceil(n / world) rounded up to a multiple of 8."""
     return ((n + world - 1) // world + 7) // 8 * 8
@@ -227,7 +234,7 @@ class ShardedSparseTensor:
         n_loc, K = x_local.shape
         dev = x_local.device
         P, S, N = self.world, self.shard, self.n_global
-        if not (config.column_split_aggregation and x_local.dtype == torch.float32 and K % 4 == 0):
+        if not (column_split_active(self.world) and x_local.dtype == torch.float32 and K % 4 == 0):
             return None
         Kp = ((K + P - 1) // P + 3) // 4 * 4
         inb = self._column_buffers("in", Kp, P * S * Kp * 4, dev)

@@ -152,8 +152,9 @@ class qsage_layer(Function):
         from .dist import ShardedSparseTensor
         # Row-sharded: what does not need the aggregate (compressing x, x W_r^T + b) is enqueued while the first
         # exchange of the aggregation is in flight; lin_l's product is then added to it.
+        from .dist import column_split_active
         overlap = (isinstance(src, ShardedSparseTensor) and config.overlap_exchange
-                   and config.column_split_aggregation)
+                   and column_split_active(src.world))
         early = {}
 
         def lin_r_early():

@@ -26,6 +26,7 @@ def main():
     ap.add_argument("--compact", type=int, default=1)
     ap.add_argument("--colsplit", type=int, default=1)
     ap.add_argument("--routed", type=int, default=0)
+    ap.add_argument("--overlap", type=int, default=0)
     a = ap.parse_args()
 
     import torch
@@ -48,6 +49,7 @@ def main():
     config.compact_operand = bool(a.compact)
     config.column_split_aggregation = bool(a.colsplit)
     config.routed_aggregation_output = bool(a.routed)
+    config.overlap_exchange = bool(a.overlap)
     config.cache_constant_gather = False
     if a.world > 1:
         adj = xdist.shard_graph(full, "mean", a.rank, a.world)

@@ -95,6 +95,15 @@ def test_sharded_run_with_feature_parallel_aggregation(world, routed, single, tm
     _compare_with_single(parts, single, regrouped=True)
 
 
+def test_feature_parallel_aggregation_with_overlapped_first_exchange(single, tmp_path):
+    """config.overlap_exchange: the first exchange on a side stream while the layer's independent work (compressing
+    x, x W_r^T, the weight gradients) runs on the main stream; the GEMM of a layer is then split in two, so the
+    numbers are a reassociation of the default order."""
+    parts = _run(2, tmp_path, "ovl", peer=1, colsplit=1, overlap=1)
+    assert all(p["exchange"].startswith("feature-parallel") for p in parts)
+    _compare_with_single(parts, single, regrouped=True)
+
+
 @pytest.mark.parametrize("world", [2, 8])
 def test_sharded_run_with_peer_written_compact_rows(world, single, tmp_path):
     parts = _run(world, tmp_path, "peer", peer=1, colsplit=0)
