@@ -124,6 +124,35 @@ def test_argument_checks_added_later_reject_before_any_launch():
     assert rc == 1 and b"2^32" in lib.exact_last_error()
 
 
+def test_entry_points_added_for_routing_batch_norm_and_fp16_reject_bad_arguments():
+    lib = _lib.load()
+    one = ctypes.c_void_p(256)
+    dst = (ctypes.c_void_p * 2)(256, 512)
+    # routed SpMM: the destinations must hold all rows, the columns must fit the row pitch
+    rc = lib.exact_spmm_split_routed(one, one, 4, None, one, 100, 32, 0, 0, None, None, None, None, 0, None, None, 0, None,
+                                     None, 40, 0, 32, dst, 2, None)
+    assert rc == 1 and b"do not hold" in lib.exact_last_error()
+    rc = lib.exact_spmm_split_routed(one, one, 4, None, one, 100, 32, 0, 0, None, None, None, None, 0, None, None, 0, None,
+                                     None, 50, 16, 32, dst, 2, None)
+    assert rc == 1 and b"row pitch" in lib.exact_last_error()
+    rc = lib.exact_spmm_split_routed(one, one, 4, None, one, 100, 32, 0, 0, None, None, None, None, 0, None, None, 0, None,
+                                     None, 50, 0, 32, dst, 9, None)
+    assert rc == 1
+    # batch-norm backward from the packed input: D % 4 != 0 is "unsupported" (the caller unpacks), a short
+    # workspace an argument error
+    assert lib.exact_bn_backward_from_packed(one, 8, 13, one, 2, one, one, None, one, one, 1, one, 1 << 20, one, one, one,
+                                             None) == 3
+    rc = lib.exact_bn_backward_from_packed(one, 8, 16, one, 2, one, one, None, one, one, 1, one, 16, one, one, one, None)
+    assert rc == 1 and b"workspace" in lib.exact_last_error()
+    # fp16 entry points
+    assert lib.exact_quantize_pack_f16(one, 8, 16, 3, None, 0, 0, 0, one, one, one, None) == 1
+    assert lib.exact_quantize_pack_f16(one, 8, 16, 2, None, 0, 0, 4, one, one, one, None) == 1   # row_offset % 8
+    assert lib.exact_unpack_single_precision_f16(None, 2, one, one, 8, 16, one, None) == 1
+    assert lib.exact_act_quantized_forward_f16(7, one, 8, 0.0, None, 0, 0, 0, one, one, None) == 1
+    assert lib.exact_act_quantized_forward_f16(1, one, 8, 1.5, None, 0, 0, 0, one, one, None) == 1   # p > 1
+    assert lib.exact_spmm_f16(one, one, 2, None, one, 8, 16, 0, one, None) == 1
+
+
 def test_device_of_a_call_comes_from_its_tensors():
     """invoke() launches on the device its tensor arguments live on and refuses mixed devices."""
     import pytest
