@@ -282,6 +282,7 @@ def run_b200(args):
     if rank == 0:
         sampler.start()
     launches0 = _lib.LAUNCHES
+    _lib.LIBRARY_CALLS.clear()
     _lib.TIMER = _lib.KernelTimer()
     torch.cuda.reset_peak_memory_stats(dev)
     timed_losses = []
@@ -295,6 +296,7 @@ def run_b200(args):
     ksum = _lib.TIMER.summary()
     _lib.TIMER = None
     launches = _lib.LAUNCHES - launches0
+    library_calls = {k: round(v / args.steps, 2) for k, v in sorted(_lib.LIBRARY_CALLS.items())}
 
     # ---- end-to-end leg: features come from pinned host memory, the loss goes back to the host ------
     # Every step copies its features host -> device and reads its loss back.  The copy of step i+1 runs on a
@@ -363,6 +365,7 @@ def run_b200(args):
         "loss_first": loss_first, "loss_last": loss_last, "loss_step0": loss0, "packed_stream_sha256": stream_sha,
         "peak_device_memory_GB": round(peak_mem / 1e9, 2),   # rank 0, device-resident leg (graph, features, training state)
         "kernel_ms_per_step": {k: round(v["ms"] / args.steps, 3) for k, v in sorted(ksum.items())},
+        "library_gemm_calls_per_step": library_calls,
         "roofline": roofline, "kernels": kern, "cpu_baseline": cpu, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

@@ -237,6 +237,15 @@ LAUNCHES = 0      # kernels of this library launched so far (each kernel-launchi
 TIMER = None      # a KernelTimer while a benchmark wants per-kernel device times
 
 
+LIBRARY_CALLS = {}   # name -> calls: dense work of the path handed to a library kernel (torch) instead of this library's
+
+
+def note_library_call(name):
+    """Counts a dense operation of the path that went to a library GEMM (shape or dtype outside this library's
+    tensor-core kernels); bench.py reports the counts per step next to its own launches."""
+    LIBRARY_CALLS[name] = LIBRARY_CALLS.get(name, 0) + 1
+
+
 class KernelTimer:
     """Brackets every library call with CUDA events on the launching stream.  summary() synchronises
     and returns, per entry point: launches, total ms, algorithmic bytes (what must move at least once) and,

@@ -27,6 +27,7 @@ def linear_forward(a, weight, bias=None, a2=None, weight2=None, out=None, accumu
     """a @ weight.T (+ a2 @ weight2.T) (+ bias), optionally added to `out`: F.linear of ops.py:150 and the
     g W product of backward_func.cc:86 (pass weight.t()).  fp32 in and out."""
     if not _tc_ok(a) or (a2 is not None and not _tc_ok(a2)):
+        _lib.note_library_call("F.linear (rows < 1024, not fp32 or not CUDA)")
         r = torch.nn.functional.linear(a, weight, bias)
         if a2 is not None:
             r = r.addmm_(a2, weight2.t())
@@ -72,6 +73,7 @@ def rows_reduce_mm(g, x, batches=512):
     joins (a single GEMM call leaves most SMs idle on this shape: 2.0 ms against 0.76 ms at
     2.45M x 256 x 32).  Same fp32 arithmetic, pairwise-style summation."""
     M = g.size(0)
+    _lib.note_library_call("g^T x on the unpacked activation (library GEMM)")
     if not (g.is_cuda and g.dim() == 2 and M >= 64 * batches and g.is_contiguous() and x.is_contiguous()):
         return g.t().mm(x)
     rows = M // batches * batches

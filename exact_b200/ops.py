@@ -124,6 +124,7 @@ def input2rp(input, kept_acts):
     """ops.py:107-118 -> (input @ R, R)."""
     assert len(input.size()) == 2
     rand_matrix = _rademacher(input.shape[1], kept_acts, input.device, input.dtype)
+    _lib.note_library_call("input2rp as torch.matmul (unfused projection)")
     dim_reduced_input = torch.matmul(input, rand_matrix)
     return dim_reduced_input, rand_matrix
 
@@ -132,6 +133,7 @@ def input2rp(input, kept_acts):
 def rp2input(dim_reduced_input, input_shape, rand_matrix):
     """ops.py:121-125."""
     assert len(dim_reduced_input.size()) == 2
+    _lib.note_library_call("rp2input as torch.matmul (unfused transpose projection)")
     input = torch.matmul(dim_reduced_input, rand_matrix.t())
     return input.view(input_shape)
 
