@@ -11,7 +11,8 @@
 // Both exchanges are plain stores into the peers' buffers (mapped with CUDA IPC, see peer.cu): a rank writes
 // its piece to all ranks in one kernel; the caller orders the stores before the readers with a one-word
 // all-reduce.  Pieces are moved as 16-byte vectors; consecutive threads write consecutive addresses of one
-// destination, so the stores cross NVLink as full lines.
+// destination, so the stores cross NVLink as full lines (the result slices are laid out slice-major in the
+// owner's buffer for the same reason; the owner regroups them locally).
 //
 // The reference is single-GPU and has no counterpart.
 #include "common.cuh"
@@ -31,12 +32,17 @@ __global__ void __launch_bounds__(256)
 cols_scatter_kernel(const float* __restrict__ x, long long n, int K, long long ldx, const float* __restrict__ rowscale,
                     long long row0, int Kp, const __grid_constant__ ColDst dst) {
   const int kp4 = Kp >> 2;
-  const long long per_row = (long long)dst.n * kp4;
-  const long long total = n * per_row;
+  const long long per_dst = n * kp4;              // 16-byte pieces one destination receives: a contiguous block
+  const long long total = per_dst * dst.n;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / per_row;
-    const int c4 = (int)(i - r * per_row);       // 16-byte piece of the padded row: source column 4 * c4
-    const int q = c4 / kp4, cc = c4 - q * kp4;
+    // destination-major: consecutive threads write consecutive addresses of ONE destination across rows (its
+    // [n, Kp] block is dense), so every warp store is 512 contiguous bytes whatever Kp; the reads are strided
+    // pieces of Kp * 4 bytes, which local memory serves well
+    const int q = (int)(i / per_dst);
+    const long long rem = i - (long long)q * per_dst;
+    const long long r = rem / kp4;
+    const int cc = (int)(rem - r * kp4);
+    const int c4 = q * kp4 + cc;                  // 16-byte piece of the padded row: source column 4 * c4
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (4 * c4 < K) {
       v = __ldcs(reinterpret_cast<const float4*>(x + r * ldx + 4 * c4));

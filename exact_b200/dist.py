@@ -266,13 +266,24 @@ class ShardedSparseTensor:
             args = (t_ptr, t_col, None if unweighted else t_w, slice_all, "sum")
         else:
             args = (self.full_rowptr, self.full_col, self.full_value, slice_all, reduce)
+        if config.slice_major_result:
+            # the owner's buffer holds P dense [S, Kp] slices, one per source rank: every store of the second
+            # exchange is contiguous whatever Kp (row-major, a rank's pieces are Kp * 4 bytes at a pitch of K * 4:
+            # 32 - 128 bytes at 8 ranks); the owner interleaves the slices locally afterwards
+            col0, ldd = 0, Kp
+            ptrs = [p + self.rank * S * Kp * 4 for p in outb.ptrs]
+        else:
+            col0, ldd, ptrs = self.rank * Kp, P * Kp, outb.ptrs
         if config.routed_aggregation_output and P <= 8:
             # every result row goes from the warp that summed it straight into its owner's buffer
-            ext_spmm._spmm(*args, regroup=True, route=(S, self.rank * Kp, P * Kp, outb.ptrs))
+            ext_spmm._spmm(*args, regroup=True, route=(S, col0, ldd, ptrs))
         else:
             y = ext_spmm._spmm(*args, regroup=True)
-            ext_rows.rows_scatter(y, S, self.rank * Kp, P * Kp, outb.ptrs)
+            ext_rows.rows_scatter(y, S, col0, ldd, ptrs)
         self._order_peer_stores(dev)
+        if config.slice_major_result:
+            out = outb.local_tensor().view(torch.float32).view(P, S, Kp)[:, :n_loc].permute(1, 0, 2).reshape(n_loc, P * Kp)
+            return out if K == P * Kp else out[:, :K].contiguous()
         out = outb.local_tensor().view(torch.float32).view(S, P * Kp)[:n_loc]
         # the buffer is written again two aggregations of this width later: callers consume the result at once
         return out if K == P * Kp else out[:, :K].contiguous()

@@ -27,6 +27,7 @@ def main():
     ap.add_argument("--colsplit", type=int, default=1)
     ap.add_argument("--routed", type=int, default=0)
     ap.add_argument("--overlap", type=int, default=0)
+    ap.add_argument("--slicemajor", type=int, default=1)
     a = ap.parse_args()
 
     import torch
@@ -50,6 +51,7 @@ def main():
     config.column_split_aggregation = bool(a.colsplit)
     config.routed_aggregation_output = bool(a.routed)
     config.overlap_exchange = bool(a.overlap)
+    config.slice_major_result = bool(a.slicemajor)
     config.cache_constant_gather = False
     if a.world > 1:
         adj = xdist.shard_graph(full, "mean", a.rank, a.world)

@@ -95,6 +95,12 @@ def test_sharded_run_with_feature_parallel_aggregation(world, routed, single, tm
     _compare_with_single(parts, single, regrouped=True)
 
 
+def test_feature_parallel_aggregation_with_row_major_result_buffers(single, tmp_path):
+    """config.slice_major_result = False: the second exchange writes row-major into the owners' buffers."""
+    parts = _run(2, tmp_path, "rowmajor", peer=1, colsplit=1, slicemajor=0)
+    _compare_with_single(parts, single, regrouped=True)
+
+
 def test_feature_parallel_aggregation_with_overlapped_first_exchange(single, tmp_path):
     """config.overlap_exchange: the first exchange on a side stream while the layer's independent work (compressing
     x, x W_r^T, the weight gradients) runs on the main stream; the GEMM of a layer is then split in two, so the
