@@ -11,8 +11,7 @@
 // Both exchanges are plain stores into the peers' buffers (mapped with CUDA IPC, see peer.cu): a rank writes
 // its piece to all ranks in one kernel; the caller orders the stores before the readers with a one-word
 // all-reduce.  Pieces are moved as 16-byte vectors; consecutive threads write consecutive addresses of one
-// destination, so the stores cross NVLink as full lines (the result slices are laid out slice-major in the
-// owner's buffer for the same reason; the owner regroups them locally).
+// destination, so the stores cross NVLink as full lines.
 //
 // The reference is single-GPU and has no counterpart.
 #include "common.cuh"

@@ -27,7 +27,7 @@ def main():
     ap.add_argument("--colsplit", type=int, default=1)
     ap.add_argument("--routed", type=int, default=0)
     ap.add_argument("--overlap", type=int, default=0)
-    ap.add_argument("--slicemajor", type=int, default=1)
+    ap.add_argument("--slicemajor", type=int, default=0)
     a = ap.parse_args()
 
     import torch

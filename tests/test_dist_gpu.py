@@ -95,9 +95,10 @@ def test_sharded_run_with_feature_parallel_aggregation(world, routed, single, tm
     _compare_with_single(parts, single, regrouped=True)
 
 
-def test_feature_parallel_aggregation_with_row_major_result_buffers(single, tmp_path):
-    """config.slice_major_result = False: the second exchange writes row-major into the owners' buffers."""
-    parts = _run(2, tmp_path, "rowmajor", peer=1, colsplit=1, slicemajor=0)
+def test_feature_parallel_aggregation_with_slice_major_result_buffers(single, tmp_path):
+    """config.slice_major_result: the second exchange writes dense per-source slices into the owners' buffers,
+    interleaved into rows locally."""
+    parts = _run(2, tmp_path, "slicemajor", peer=1, colsplit=1, slicemajor=1)
     _compare_with_single(parts, single, regrouped=True)
 
 
