@@ -124,8 +124,12 @@ def input2rp(input, kept_acts):
     """ops.py:107-118 -> (input @ R, R)."""
     assert len(input.size()) == 2
     rand_matrix = _rademacher(input.shape[1], kept_acts, input.device, input.dtype)
-    _lib.note_library_call("input2rp as torch.matmul (unfused projection)")
-    dim_reduced_input = torch.matmul(input, rand_matrix)
+    if ext_backward_func._tc_ok(input):
+        # the dense product on this library's tensor-core GEMM (fp32 operands split into tf32 head and tail)
+        dim_reduced_input = ext_backward_func.linear_forward(input, rand_matrix.t().contiguous())
+    else:
+        _lib.note_library_call("input2rp as torch.matmul (fewer than 1024 rows, not fp32 or not CUDA)")
+        dim_reduced_input = torch.matmul(input, rand_matrix)
     return dim_reduced_input, rand_matrix
 
 
@@ -133,8 +137,11 @@ def input2rp(input, kept_acts):
 def rp2input(dim_reduced_input, input_shape, rand_matrix):
     """ops.py:121-125."""
     assert len(dim_reduced_input.size()) == 2
-    _lib.note_library_call("rp2input as torch.matmul (unfused transpose projection)")
-    input = torch.matmul(dim_reduced_input, rand_matrix.t())
+    if ext_backward_func._tc_ok(dim_reduced_input) and rand_matrix.dtype == torch.float32:
+        input = ext_backward_func.linear_forward(dim_reduced_input, rand_matrix)   # xq R^T on the tensor cores
+    else:
+        _lib.note_library_call("rp2input as torch.matmul (fewer than 1024 rows, not fp32 or not CUDA)")
+        input = torch.matmul(dim_reduced_input, rand_matrix.t())
     return input.view(input_shape)
 
 

@@ -107,3 +107,19 @@ def test_fused_unpack_transpose_projection(N, D, k, bits):
     assert rel_fro(out, ref) < 1e-2
     assert rel_fro(out, ref) < 3e-3
     config.check_device_status = False
+
+
+@pytest.mark.parametrize("N,D,k", [(5000, 256, 32), (3000, 602, 76), (2000, 100, 13), (500, 128, 16)])
+def test_public_input2rp_and_rp2input_against_the_oracle(N, D, k):
+    """ops.input2rp / ops.rp2input (exact/exact/ops.py:107-125), the unfused projection pair: dense products on this
+    library's tensor-core GEMM from 1,024 rows on (tf32 head/tail split: fp32-class accuracy), the library's
+    otherwise; against the oracle's double-accumulated products."""
+    from exact_b200 import ops
+    config.manual_seed(21)
+    x = normal(N, D, 41)
+    y, R = ops.input2rp(torch.from_numpy(x).cuda(), k)
+    Rn = R.cpu().numpy()
+    assert np.array_equal(np.abs(Rn), np.full_like(Rn, 1.0 / np.sqrt(np.float32(k))))
+    assert rel_fro(y.cpu().numpy(), oracle.input2rp(x, Rn)) < 1e-5
+    back = ops.rp2input(y, torch.Size([N, D]), R)
+    assert rel_fro(back.cpu().numpy(), oracle.rp2input(y.cpu().numpy(), Rn)) < 1e-5
