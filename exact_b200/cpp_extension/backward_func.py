@@ -84,15 +84,16 @@ def rows_reduce_mm(g, x, batches=512):
 
 
 def grad_weight_supported(g, k0, k1, bits):
-    """Shapes exact_grad_weight_from_packed takes: fp32 g [N, O] with O % 4 == 0, O <= 256, at least 4,096 rows
+    """Shapes exact_grad_weight_from_packed takes: fp32 g [N, O] with O <= 256 (padded to a multiple of 4), at least 4,096 rows
     (below that the library GEMM on the unpacked activation is as fast), and few enough activation columns for
     four producer warps (k0 + k1 <= 1024 * bits / 256)."""
     if not (config.grad_weight_tensor_core and g.is_cuda and g.dtype == torch.float32 and g.dim() == 2):
         return False
     N, O = g.shape
     kpad = (k0 + 15) // 16 * 16 + ((k1 + 15) // 16 * 16 if k1 else 0)
-    return (N >= 4096 and O % 4 == 0 and O <= 256 and kpad <= 256 and (k0 + k1) * (32 // (8 // bits)) <= 1024
-            and g.is_contiguous() and g.data_ptr() % 16 == 0)
+    # a width that is not a multiple of 4 (47 classes) goes in as a zero-padded copy of g
+    return (N >= 4096 and (O + 3) // 4 * 4 <= 256 and kpad <= 256 and (k0 + k1) * (32 // (8 // bits)) <= 1024
+            and g.is_contiguous() and (g.data_ptr() % 16 == 0 or O % 4 != 0))
 
 
 _SM_COUNT = {}
@@ -102,6 +103,11 @@ def grad_weight_from_packed(g, q0, k0, q1=None, k1=0):
     """(g^T Xq0 [O, k0], g^T Xq1 [O, k1] or None) for packed activations q = (packed, bits, scale_bf16, min_bf16)
     of N rows: backward_func.cc:87 with the dequantisation of ops.py:164 folded in, one pass over g."""
     lib = _lib.load()
+    N, O_true = g.shape
+    if O_true % 4:
+        gp = g.new_zeros((N, (O_true + 3) // 4 * 4))
+        gp[:, :O_true].copy_(g)
+        g = gp
     N, O = g.shape
     bits = q0[1]
     k0pad = (k0 + 15) // 16 * 16
@@ -122,7 +128,7 @@ def grad_weight_from_packed(g, q0, k0, q1=None, k1=0):
         status = int(ws[:4].view(torch.int32).item())
         if status != 0:
             raise _lib.ExactB200Error(f"grad_weight_from_packed: device status {status} (a bounded on-chip wait expired)")
-    return out[:, :k0], (out[:, k0pad:k0pad + k1] if q1 is not None else None)
+    return out[:O_true, :k0], (out[:O_true, k0pad:k0pad + k1] if q1 is not None else None)
 
 
 def linear_backward(grad_output, input, weight, bias=None, need_grad_input=True):

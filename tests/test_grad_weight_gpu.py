@@ -49,9 +49,19 @@ def test_grad_weight_from_packed(N, O, k0, k1, bits):
     config.check_device_status = False
 
 
+def test_width_that_is_not_a_multiple_of_four_goes_in_padded():
+    """47 classes: rows of 188 bytes cannot be described by a tensor map; g goes in as a zero-padded copy."""
+    from exact_b200.cpp_extension import quantization as Q
+    g = torch.randn(5000, 47, device="cuda")
+    assert B.grad_weight_supported(g, 32, 32, 2)
+    x = torch.randn(5000, 32, device="cuda")
+    pk, sb, mb = Q.quantize_pack(x, 2, seed=3, offset=0)
+    a, _ = B.grad_weight_from_packed(g, (pk, 2, sb, mb), 32)
+    ref = g.t().double() @ Q.unpack_single_precision(pk, 2, sb, mb, 5000, 32).double()
+    assert a.shape == (47, 32) and float((a.double() - ref).norm() / ref.norm()) < 2e-3
+
+
 def test_unsupported_shapes_use_the_library_route():
-    g = torch.randn(5000, 47, device="cuda")           # 188-byte rows: no tensor map
-    assert not B.grad_weight_supported(g, 32, 32, 2)
     g = torch.randn(1000, 256, device="cuda")          # too few rows to be worth it
     assert not B.grad_weight_supported(g, 32, 32, 2)
     g = torch.randn(5000, 256, device="cuda")
