@@ -3,10 +3,9 @@
 // Replaces quantization.act_quantized_relu / act_quantized_leaky_relu / act_quantized_dropout
 // (exact/exact/cpp_extension/quantization.cc:66-134; kernels quantization_cuda_kernel.cu:237-594).
 //
-// A warp handles 128 consecutive elements per step: each lane loads one float4, and four
-// __ballot_sync calls turn the 128 predicates into four mask words.  Word 4*c + j, bit l holds
-// element 128*c + 4*l + j.  The layout is private: the reference's mask never leaves its extension
-// either (quantization.cc:71,92,119), only outputs and gradients are observable.
+// One bit per element, 32-bit words: word 8c + j, bit l holds element 256c + 8l + j (see the forward kernel).  The
+// layout is private: the reference's mask never leaves its extension either (quantization.cc:71,92,119), only
+// outputs and gradients are observable.
 #include "common.cuh"
 #include <cmath>
 #include <cuda_fp16.h>
@@ -28,7 +27,7 @@ struct MaskParams {
   float p1m;            // float(1 - p)
   float p1m_inv_exact;  // 1 / p1m when p1m is a power of two (then g / p1m == g * that, bit for bit), else 0
   uint32_t off_lo, off_hi;
-  unsigned long long q0;  // Philox block index of element 0 (global element index / 4)
+  unsigned long long q0;  // Philox block index of element 0 (global element index / 8)
   PhiloxKey key;
 };
 
@@ -82,46 +81,64 @@ __device__ __forceinline__ void store4(__half* base, long long i, long long n, c
   }
 }
 
+// Forward: a warp handles 256 consecutive elements per step, a lane eight of them (two 4-element vector loads);
+// eight __ballot_sync calls turn the 256 predicates into eight mask words: word 8c + j, bit l = element 256c + 8l + j.
+// Dropout draws one Philox4x32-10 block per lane and step: 128 bits = eight 16-bit uniforms (h + 0.5) / 65536, keyed
+// by the global index of the lane's first element / 8.  (32-bit uniforms, one block per four elements, made the
+// Philox rounds the largest share of the instructions: 66 % of the copy peak for ReLU + dropout.)
 template <int OP, bool ALIGNED, typename T>
 __global__ void __launch_bounds__(256) mask_forward_kernel(const __grid_constant__ MaskParams p) {
   const int lane = threadIdx.x & 31;
-  const long long nchunks = (p.n + 127) >> 7;
+  const long long nchunks = (p.n + 255) >> 8;
   const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long c = warp0; c < nchunks; c += nwarps) {
-    const long long i = (c << 7) + 4 * lane;
-    float v[4], o[4];
-    bool keep[4];
-    load4<ALIGNED>(static_cast<const T*>(p.x), i, p.n, v);
+    const long long i = (c << 8) + 8 * lane;
+    float v[8], o[8];
+    bool keep[8];
+    {
+      float a[4], b[4];
+      load4<ALIGNED>(static_cast<const T*>(p.x), i, p.n, a);
+      load4<ALIGNED>(static_cast<const T*>(p.x), i + 4, p.n, b);
+#pragma unroll
+      for (int j = 0; j < 4; j++) { v[j] = a[j]; v[4 + j] = b[j]; }
+    }
     if (OP == OP_RELU) {
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
+      for (int j = 0; j < 8; j++) {
         keep[j] = v[j] > 0.f;           // quantization_cuda_kernel.cu:253
         o[j] = keep[j] ? v[j] : 0.f;
       }
     } else if (OP == OP_LEAKY_RELU) {
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
+      for (int j = 0; j < 8; j++) {
         keep[j] = v[j] > 0.f;           // quantization_cuda_kernel.cu:356-361
         o[j] = keep[j] ? v[j] : __fmul_rn(v[j], p.p);
       }
     } else {
       if (OP == OP_RELU_DROPOUT) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) v[j] = v[j] > 0.f ? v[j] : 0.f;   // the ReLU that precedes the dropout
+        for (int j = 0; j < 8; j++) v[j] = v[j] > 0.f ? v[j] : 0.f;   // the ReLU that precedes the dropout
       }
-      float u[4];
+      float u[8];
       if (p.u != nullptr) {
-        load4<ALIGNED>(p.u, i, p.n, u);
+        float a[4], b[4];
+        load4<ALIGNED>(p.u, i, p.n, a);
+        load4<ALIGNED>(p.u, i + 4, p.n, b);
+#pragma unroll
+        for (int j = 0; j < 4; j++) { u[j] = a[j]; u[4 + j] = b[j]; }
       } else {
-        const unsigned long long q = p.q0 + (unsigned long long)((c << 5) + lane);  // global element index / 4
+        const unsigned long long q = p.q0 + (unsigned long long)((c << 5) + lane);  // global element index / 8
         uint32_t w[4];
         philox4x32_10((uint32_t)q, (uint32_t)(q >> 32), p.off_lo, p.off_hi, p.key, w);
 #pragma unroll
-        for (int j = 0; j < 4; j++) u[j] = u32_to_unit(w[j]);
+        for (int j = 0; j < 8; j++) {
+          const uint32_t h = (w[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+          u[j] = __fmaf_rn((float)h, 1.52587890625e-05f, 7.62939453125e-06f);   // (h + 0.5) / 65536, exact
+        }
       }
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
+      for (int j = 0; j < 8; j++) {
         keep[j] = (u[j] > p.p) && (i + j < p.n);  // quantization_cuda_kernel.cu:466-469
         // quantization_cuda_kernel.cu:490: src * keep * pinv, two fp32 multiplies
         o[j] = __fmul_rn(__fmul_rn(v[j], keep[j] ? 1.f : 0.f), p.pinv);
@@ -130,11 +147,15 @@ __global__ void __launch_bounds__(256) mask_forward_kernel(const __grid_constant
         if (OP == OP_RELU_DROPOUT) keep[j] = keep[j] && v[j] > 0.f;
       }
     }
-    store4<ALIGNED>(static_cast<T*>(p.out), i, p.n, o);
+    {
+      const float a[4] = {o[0], o[1], o[2], o[3]}, b[4] = {o[4], o[5], o[6], o[7]};
+      store4<ALIGNED>(static_cast<T*>(p.out), i, p.n, a);
+      store4<ALIGNED>(static_cast<T*>(p.out), i + 4, p.n, b);
+    }
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
+    for (int j = 0; j < 8; j++) {
       const uint32_t w = __ballot_sync(0xffffffffu, keep[j]);
-      if (lane == j) p.mask[(c << 2) + j] = w;
+      if (lane == j) p.mask[(c << 3) + j] = w;
     }
   }
 }
@@ -142,17 +163,24 @@ __global__ void __launch_bounds__(256) mask_forward_kernel(const __grid_constant
 template <int OP, bool ALIGNED, typename T>
 __global__ void __launch_bounds__(256) mask_backward_kernel(const __grid_constant__ MaskParams p) {
   const int lane = threadIdx.x & 31;
-  const long long nchunks = (p.n + 127) >> 7;
+  const long long nchunks = (p.n + 255) >> 8;
   const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long c = warp0; c < nchunks; c += nwarps) {
-    const long long i = (c << 7) + 4 * lane;
-    float g[4], o[4];
-    load4<ALIGNED>(static_cast<const T*>(p.x), i, p.n, g);
-    const uint4 mw = __ldg(reinterpret_cast<const uint4*>(p.mask) + c);
-    const uint32_t m[4] = {mw.x, mw.y, mw.z, mw.w};
+    const long long i = (c << 8) + 8 * lane;
+    float g[8], o[8];
+    {
+      float a[4], b[4];
+      load4<ALIGNED>(static_cast<const T*>(p.x), i, p.n, a);
+      load4<ALIGNED>(static_cast<const T*>(p.x), i + 4, p.n, b);
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
+      for (int j = 0; j < 4; j++) { g[j] = a[j]; g[4 + j] = b[j]; }
+    }
+    const uint4 m0 = __ldg(reinterpret_cast<const uint4*>(p.mask) + 2 * c);
+    const uint4 m1 = __ldg(reinterpret_cast<const uint4*>(p.mask) + 2 * c + 1);
+    const uint32_t m[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
       const bool keep = (m[j] >> lane) & 1u;
       if (OP == OP_RELU) {
         o[j] = keep ? g[j] : 0.f;                      // quantization_cuda_kernel.cu:303-308
@@ -165,7 +193,9 @@ __global__ void __launch_bounds__(256) mask_backward_kernel(const __grid_constan
         o[j] = keep ? q : 0.f;
       }
     }
-    store4<ALIGNED>(static_cast<T*>(p.out), i, p.n, o);
+    const float a[4] = {o[0], o[1], o[2], o[3]}, b[4] = {o[4], o[5], o[6], o[7]};
+    store4<ALIGNED>(static_cast<T*>(p.out), i, p.n, a);
+    store4<ALIGNED>(static_cast<T*>(p.out), i + 4, p.n, b);
   }
 }
 
@@ -180,7 +210,7 @@ static int launch_mask(bool forward, const MaskParams& p, cudaStream_t st) {
   EXB_REQUIRE(aligned16(p.mask), "mask activation: mask must be 16-byte aligned");
   const unsigned vb = 4 * sizeof(T);   // one 4-element vector access
   const bool al = aligned_to(p.x, vb) && aligned_to(p.out, vb) && (p.u == nullptr || aligned16(p.u));
-  const long long nchunks = (p.n + 127) >> 7;
+  const long long nchunks = (p.n + 255) >> 8;
   long long blocks = (nchunks + 7) / 8;
   const long long cap = (long long)sm_count() * 8;
   if (blocks > cap) blocks = cap;
@@ -210,7 +240,7 @@ using namespace exb;
 
 extern "C" {
 
-int64_t exact_mask_words(int64_t n) { return n <= 0 ? 0 : ((n + 127) / 128) * 4; }
+int64_t exact_mask_words(int64_t n) { return n <= 0 ? 0 : ((n + 255) / 256) * 8; }
 
 int exact_act_quantized_relu_forward(const float* x, int64_t n, float* out, uint32_t* mask, void* stream) {
   EXB_REQUIRE(n >= 0, "relu: negative size");
@@ -247,7 +277,7 @@ int exact_act_quantized_dropout_forward(const float* x, int64_t n, float prob, c
                                         uint64_t seed, uint64_t offset, int64_t index_offset, float* out,
                                         uint32_t* mask, void* stream) {
   EXB_REQUIRE(n >= 0, "dropout: negative size");
-  EXB_REQUIRE(index_offset >= 0 && index_offset % 4 == 0, "dropout: index_offset must be a non-negative multiple of 4");
+  EXB_REQUIRE(index_offset >= 0 && index_offset % 8 == 0, "dropout: index_offset must be a non-negative multiple of 8");
   EXB_REQUIRE(prob >= 0.f && prob <= 1.f, "dropout: p must be in [0, 1] (got %f)", (double)prob);
   MaskParams p{};
   p.x = x; p.u = uniforms; p.out = out; p.mask = mask; p.n = n;
@@ -255,7 +285,7 @@ int exact_act_quantized_dropout_forward(const float* x, int64_t n, float prob, c
   p.pinv = (float)(1.0 / (1.0 - (double)prob));  // quantization_cuda_kernel.cu:455
   p.p1m = (float)(1.0 - (double)prob);
   p.off_lo = (uint32_t)offset; p.off_hi = (uint32_t)(offset >> 32);
-  p.q0 = (unsigned long long)index_offset >> 2;
+  p.q0 = (unsigned long long)index_offset >> 3;
   p.key = make_philox_key(seed);
   return launch_mask<OP_DROPOUT>(true, p, (cudaStream_t)stream);
 }
@@ -264,7 +294,7 @@ int exact_act_quantized_relu_dropout_forward(const float* x, int64_t n, float pr
                                              uint64_t seed, uint64_t offset, int64_t index_offset, float* out,
                                              uint32_t* mask, void* stream) {
   EXB_REQUIRE(n >= 0, "relu_dropout: negative size");
-  EXB_REQUIRE(index_offset >= 0 && index_offset % 4 == 0, "relu_dropout: index_offset must be a non-negative multiple of 4");
+  EXB_REQUIRE(index_offset >= 0 && index_offset % 8 == 0, "relu_dropout: index_offset must be a non-negative multiple of 8");
   EXB_REQUIRE(prob >= 0.f && prob <= 1.f, "relu_dropout: p must be in [0, 1] (got %f)", (double)prob);
   MaskParams p{};
   p.x = x; p.u = uniforms; p.out = out; p.mask = mask; p.n = n;
@@ -272,7 +302,7 @@ int exact_act_quantized_relu_dropout_forward(const float* x, int64_t n, float pr
   p.pinv = (float)(1.0 / (1.0 - (double)prob));  // quantization_cuda_kernel.cu:455
   p.p1m = (float)(1.0 - (double)prob);
   p.off_lo = (uint32_t)offset; p.off_hi = (uint32_t)(offset >> 32);
-  p.q0 = (unsigned long long)index_offset >> 2;
+  p.q0 = (unsigned long long)index_offset >> 3;
   p.key = make_philox_key(seed);
   return launch_mask<OP_RELU_DROPOUT>(true, p, (cudaStream_t)stream);
 }
@@ -301,12 +331,12 @@ int exact_act_quantized_forward_f16(int op, const void* x, int64_t n, float para
   cudaStream_t st = (cudaStream_t)stream;
   if (op == EXACT_ACT_RELU) return launch_mask<OP_RELU, __half>(true, p, st);
   if (op == EXACT_ACT_LEAKY_RELU) return launch_mask<OP_LEAKY_RELU, __half>(true, p, st);
-  EXB_REQUIRE(index_offset >= 0 && index_offset % 4 == 0, "dropout: index_offset must be a non-negative multiple of 4");
+  EXB_REQUIRE(index_offset >= 0 && index_offset % 8 == 0, "dropout: index_offset must be a non-negative multiple of 8");
   EXB_REQUIRE(param >= 0.f && param <= 1.f, "dropout: p must be in [0, 1] (got %f)", (double)param);
   p.u = uniforms;
   dropout_constants(p, param);
   p.off_lo = (uint32_t)offset; p.off_hi = (uint32_t)(offset >> 32);
-  p.q0 = (unsigned long long)index_offset >> 2;
+  p.q0 = (unsigned long long)index_offset >> 3;
   p.key = make_philox_key(seed);
   if (op == EXACT_ACT_DROPOUT) return launch_mask<OP_DROPOUT, __half>(true, p, st);
   return launch_mask<OP_RELU_DROPOUT, __half>(true, p, st);

@@ -124,7 +124,8 @@ EXACT_API int exact_act_quantized_forward_f16(int op, const void* x, int64_t n, 
 EXACT_API int exact_act_quantized_backward_f16(int op, const void* grad_out, const uint32_t* mask, int64_t n, float param,
                                                void* grad_in, void* stream);
 
-/* Number of 32-bit mask words the 1-bit-mask activations need for n elements. */
+/* Number of 32-bit mask words the 1-bit-mask activations need for n elements: 8 * ceil(n / 256); the mask must be
+ * 16-byte aligned. */
 EXACT_API int64_t exact_mask_words(int64_t n);
 
 /* quantization.act_quantized_relu forward / backward (quantization.cc:66-84;
@@ -146,9 +147,10 @@ EXACT_API int exact_act_quantized_leaky_relu_backward(const float* grad_out, con
 
 /* quantization.act_quantized_dropout forward / backward (quantization.cc:111-134;
  * quantization_cuda_kernel.cu:442-594): keep = u > p, out = (x * keep) * float(1 / (1 - p));
- * grad_in = keep ? grad_out / float(1 - p) : 0.  `uniforms` [n] supplies u, or NULL draws
- * Philox4x32-10 uniforms in (0, 1] keyed by (seed, offset, (index_offset + element index) / 4);
- * index_offset (multiple of 4) is the global index of element 0 when rows are sharded. */
+ * grad_in = keep ? grad_out / float(1 - p) : 0.  `uniforms` [n] supplies u, or NULL draws them: one
+ * Philox4x32-10 block keyed by (seed, offset, (index_offset + element index) / 8) gives eight 16-bit values h,
+ * u = (h + 0.5) / 65536 (the probability is resolved to 2^-16);
+ * index_offset (multiple of 8) is the global index of element 0 when rows are sharded. */
 EXACT_API int exact_act_quantized_dropout_forward(const float* x, int64_t n, float p,
                                                   const float* uniforms, uint64_t seed, uint64_t offset,
                                                   int64_t index_offset, float* out, uint32_t* mask,

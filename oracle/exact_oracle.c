@@ -380,17 +380,20 @@ ORC_API void orc_noise_b200_rows(uint64_t seed, uint64_t offset, int64_t row_off
   }
 }
 
-/* Production dropout uniforms of the B200 library: one Philox call per 4 consecutive elements,
- * counter = (i/4 lo, i/4 hi, offset lo, offset hi), u = r * 2^-32 + 2^-33 in (0, 1]. */
+/* Production dropout uniforms of the B200 library: one Philox call per 8 consecutive elements,
+ * counter = (i/8 lo, i/8 hi, offset lo, offset hi); element i takes the 16-bit field i % 8 of the 128-bit block
+ * (word (i % 8) / 2, low half first), u = (h + 0.5) * 2^-16 in (0, 1). */
 ORC_API void orc_uniform_b200(uint64_t seed, uint64_t offset, int64_t n, float *u) {
   const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
 #pragma omp parallel for schedule(static)
-  for (int64_t q = 0; q < (n + 3) / 4; q++) {
+  for (int64_t q = 0; q < (n + 7) / 8; q++) {
     uint32_t out[4];
     philox4x32_10((uint32_t)q, (uint32_t)((uint64_t)q >> 32), (uint32_t)offset,
                   (uint32_t)(offset >> 32), k0, k1, out);
-    for (int j = 0; j < 4 && q * 4 + j < n; j++)
-      u[q * 4 + j] = fmaf((float)out[j], 2.3283064365386963e-10f, 1.1641532182693481e-10f);
+    for (int j = 0; j < 8 && q * 8 + j < n; j++) {
+      uint32_t h = (out[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+      u[q * 8 + j] = fmaf((float)h, 1.52587890625e-05f, 7.62939453125e-06f);
+    }
   }
 }
 

@@ -37,7 +37,7 @@ def test_host_only_entry_points():
     assert lib.exact_packed_bytes(169343, 256, 2) == 42336 * 256
     assert lib.exact_packed_bytes(5, 3, 8) == 15
     assert lib.exact_packed_bytes(5, 3, 3) == -1
-    assert lib.exact_mask_words(0) == 0 and lib.exact_mask_words(129) == 8
+    assert lib.exact_mask_words(0) == 0 and lib.exact_mask_words(129) == 8 and lib.exact_mask_words(257) == 16
 
 
 def test_bad_arguments_are_rejected_before_any_launch():
