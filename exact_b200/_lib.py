@@ -56,6 +56,8 @@ SIGNATURES = {
                                                 c_ptr]),
     "exact_act_quantized_backward_f16": (c_int, [c_int, c_ptr, c_ptr, c_i64, c_f32, c_ptr, c_ptr]),
     "exact_spmm_f16": (c_int, [c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64, c_i64, c_int, c_ptr, c_ptr]),
+    "exact_rows_scale_colsum_workspace_bytes": (c_i64, [c_i64]),
+    "exact_rows_scale_colsum": (c_int, [c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_i64, c_ptr]),
     "exact_bn_backward_workspace_bytes": (c_i64, [c_i64]),
     "exact_bn_backward_from_packed": (c_int, [c_ptr, c_i64, c_i64, c_ptr, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int,
                                               c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr]),

@@ -135,7 +135,7 @@ def linear_backward(grad_output, input, weight, bias=None, need_grad_input=True)
     """backward_func.cc:83-93.  The input gradient is left out (None) when the caller has no use for it."""
     grad_input = linear_forward(grad_output, weight.t()) if need_grad_input else None
     grad_weight = rows_reduce_mm(grad_output, input)
-    grad_bias = grad_output.sum(0) if bias is not None else None
+    grad_bias = rows_scale_colsum(grad_output)[1] if bias is not None else None
     return grad_input, grad_weight, grad_bias
 
 
@@ -189,3 +189,28 @@ def batch_norm_backward_from_packed(grad_out, quantized, weight, running_mean, r
                 _lib.ptr(q_min), _lib.ptr(w), _lib.ptr(mean), _lib.ptr(invstd), 1 if train else 0, _lib.ptr(ws), ws_bytes,
                 _lib.ptr(grad_input), _lib.ptr(grad_weight), _lib.ptr(grad_bias), _lib.stream_ptr())
     return grad_input, grad_weight, grad_bias
+
+
+def rows_scale_colsum(g, rowscale=None, want_scaled=False, want_colsum=True, pad_to=4):
+    """One pass over g [N, K] -> (g * rowscale[:, None] zero-padded to a multiple of `pad_to` columns or None,
+    g.sum(0) or None): the operand D^-1 g of the transposed mean aggregation (spmm.cc:128-137) and the bias gradient
+    (backward_func.cc:88-90).  Small or non-fp32 inputs take the framework's ops."""
+    N, K = g.shape
+    if not (g.is_cuda and g.dtype == torch.float32 and g.dim() == 2 and g.stride(1) == 1 and N >= 1024):
+        scaled = None
+        if want_scaled:
+            scaled = g.new_zeros((N, (K + pad_to - 1) // pad_to * pad_to))
+            scaled[:, :K] = g if rowscale is None else g * rowscale.unsqueeze(1)
+        return scaled, (g.sum(0) if want_colsum else None)
+    lib = _lib.load()
+    Kout = (K + pad_to - 1) // pad_to * pad_to if want_scaled else K
+    out = torch.empty((N, Kout), dtype=torch.float32, device=g.device) if want_scaled else None
+    colsum = torch.empty(K, dtype=torch.float32, device=g.device) if want_colsum else None
+    ws_bytes = int(lib.exact_rows_scale_colsum_workspace_bytes(Kout)) if want_colsum else 0
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=g.device) if want_colsum else None
+    if rowscale is not None:
+        rowscale = rowscale.to(torch.float32).contiguous()
+    nbytes = 4 * N * K + (4 * N * Kout if want_scaled else 0)
+    _lib.invoke("exact_rows_scale_colsum", nbytes, _lib.ptr(g), N, K, g.stride(0), _lib.ptr(rowscale), _lib.ptr(out), Kout,
+                Kout, _lib.ptr(colsum), _lib.ptr(ws), ws_bytes, _lib.stream_ptr())
+    return out, colsum

@@ -223,7 +223,7 @@ def linear_backward_from_compressed(quantized, weight, bias, randmat, ori_input_
         else:
             grad_weight = grad_weight.contiguous()
         grad_input = ext_backward_func.linear_forward(grad_output, weight.t()) if need_grad_input else None
-        grad_bias = grad_output.sum(0) if bias is not None else None
+        grad_bias = ext_backward_func.rows_scale_colsum(grad_output)[1] if bias is not None else None
         return grad_input, grad_weight, grad_bias
     if (projected and not config.grad_weight_in_projected_space and config.fused_rp and config.compress_activation
             and not config.simulate and not config.swap and len(ori_input_shape) == 2
@@ -241,7 +241,7 @@ def linear_backward_from_compressed(quantized, weight, bias, randmat, ori_input_
         # materialised and the large GEMM shrinks from 2*N*out*D to 2*N*out*k flops.
         grad_weight = ext_backward_func.rows_reduce_mm(grad_output, input).mm(randmat.t())
         grad_input = ext_backward_func.linear_forward(grad_output, weight.t()) if need_grad_input else None
-        grad_bias = grad_output.sum(0) if bias is not None else None
+        grad_bias = ext_backward_func.rows_scale_colsum(grad_output)[1] if bias is not None else None
     else:
         if projected:
             input = rp2input(input, ori_input_shape, randmat)

@@ -237,6 +237,13 @@ class qsage_layer(Function):
         k_agg, k_x = proj_agg[1], proj_x[1]
         both_projected = randmat_agg is not None and (w_r is None or randmat_x is not None)
         wg = {}
+        pre = {}
+
+        def bias_grad():
+            # grad_output.sum(0) (backward_func.cc:88-90); already formed when the pass that scales g also summed it
+            if "colsum" not in pre:
+                pre["colsum"] = ext_backward_func.rows_scale_colsum(g)[1]
+            return pre["colsum"]
 
         def weight_grads():
             grad_w_r = None
@@ -248,7 +255,7 @@ class qsage_layer(Function):
                 ga, gx = ext_backward_func.grad_weight_from_packed(g, q_agg, k_agg, q_x if w_r is not None else None,
                                                                    k_x)
                 grad_w_l = ga.mm(randmat_agg.t())
-                grad_b = g.sum(0) if b_l is not None else None
+                grad_b = bias_grad() if b_l is not None else None
                 if w_r is not None:
                     grad_w_r = gx.mm(randmat_x.t())
             else:
@@ -275,7 +282,19 @@ class qsage_layer(Function):
                 inv = _inverse_degree(ctx.src) if ctx.reduce == "mean" else None
                 gp, wp = g, w_l
                 prescaled = False
-                if pad:
+                from .dist import ShardedSparseTensor
+                if not isinstance(ctx.src, ShardedSparseTensor) and (inv is not None or pad):
+                    # one pass over g: D^-1 g (zero-padded to whole column groups) and, for the bias, g.sum(0).
+                    # (A row-sharded source scales the rows inside its exchange kernels instead.)
+                    gp, colsum = ext_backward_func.rows_scale_colsum(g, inv, want_scaled=True,
+                                                                     want_colsum=b_l is not None)
+                    if colsum is not None:
+                        pre["colsum"] = colsum
+                    prescaled, inv = inv is not None, None
+                    if pad:
+                        wp = w_l.new_zeros((out_f + pad, in_f))
+                        wp[:out_f].copy_(w_l)
+                elif pad:
                     gp = g.new_zeros((g.size(0), out_f + pad))
                     if inv is not None:
                         torch.mul(g, inv.unsqueeze(1), out=gp[:, :out_f])   # pad and scale in one pass

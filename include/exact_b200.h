@@ -256,6 +256,19 @@ EXACT_API int exact_cols_scatter(const float* x, int64_t n, int64_t K, int64_t l
 EXACT_API int exact_rows_scatter(const float* y, int64_t n_total, int64_t Kp, int64_t shard, int64_t col0, int64_t ldd,
                                  void* const* dst, int n_dst, void* stream);
 
+/* One pass over the gradient g [n, K] (pitch ldg) of a layer's output for the two things its backward needs besides the
+ * GEMMs (no single counterpart in the reference, which leaves both to the framework):
+ *   colsum[c] = sum_r g[r, c]          the bias gradient, grad_output.sum(0) of backward_func.cc:88-90 (or NULL);
+ *   out[r, c] = g[r, c] * rowscale[r]  for c < K, zero for K <= c < Kout (pitch ldo): the operand D^-1 g of the
+ *                                      transposed mean aggregation (spmm.cc:128-137), or NULL.  rowscale NULL: ones.
+ * Column sums are added in a fixed order (run-to-run identical).  16-byte accesses when K, Kout and the pitches are
+ * multiples of 4 and the pointers 16-byte aligned, scalar ones otherwise.  workspace (needed for colsum):
+ * exact_rows_scale_colsum_workspace_bytes(Kout), 256-byte aligned. */
+EXACT_API int64_t exact_rows_scale_colsum_workspace_bytes(int64_t Kout);
+EXACT_API int exact_rows_scale_colsum(const float* g, int64_t n, int64_t K, int64_t ldg, const float* rowscale, float* out,
+                                      int64_t Kout, int64_t ldo, float* colsum, void* workspace,
+                                      int64_t workspace_bytes, void* stream);
+
 /* Batch-norm backward straight from the packed input: native_batch_norm_backward as called by the reference's
  * qbatch_norm.backward (exact/exact/ops.py:248-251) with the dequantize_activation of ops.py:238 folded into
  * both of its passes, so the [N, D] reconstruction is never written.

@@ -396,3 +396,15 @@ def spmm_f16(rowptr, col, val, mat, reduce="sum"):
     out = np.empty((M, K), np.uint16)
     lib().orc_spmm_f16(_p(rowptr), _p(col), _p(val), _p(mat), i64(M), i64(K), cint({"sum": 0, "mean": 1}[reduce]), _p(out))
     return out.view(np.float16)
+
+
+def rows_scale_colsum(g, rowscale=None, pad_to=4):
+    """(g * rowscale[:, None] in fp32, zero-padded to a multiple of `pad_to` columns; g.sum(0) in float64): the
+    operand D^-1 g of the transposed mean aggregation (spmm.cc:128-137: the weights 1 / max(count, 1) applied to the
+    rows of the gradient) and the bias gradient grad_output.sum(0) (backward_func.cc:88-90)."""
+    g = _f32(g)
+    N, K = g.shape
+    Kout = (K + pad_to - 1) // pad_to * pad_to
+    out = np.zeros((N, Kout), np.float32)
+    out[:, :K] = g if rowscale is None else g * _f32(rowscale)[:, None]
+    return out, g.astype(np.float64).sum(0)
