@@ -174,7 +174,7 @@ grad_weight_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_consta
     for (long long it = 0; it < nblk; it++) {
       const int rs = (int)(it % p.raw_stages), s = (int)(it % p.stages);
       const uint32_t rph = (uint32_t)(it / p.raw_stages) & 1u, ph = (uint32_t)(it / p.stages) & 1u;
-      // the same verdict in every lane, so that a warp leaves the loop as a whole
+      // the same outcome in every lane, so that a warp leaves the loop as a whole
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_rfull[rs]), rph, abort_flag))) { ok = false; break; }
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, abort_flag))) { ok = false; break; }
       const float* raw = reinterpret_cast<const float*>(tiles_ptr + (size_t)rs * p.raw_bytes);
@@ -285,7 +285,7 @@ grad_weight_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_consta
         load_items(it + 1);
         load_stats(it + 1);
       }
-      // the same verdict in every lane, so that a warp leaves the loop as a whole
+      // the same outcome in every lane, so that a warp leaves the loop as a whole
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, abort_flag))) { ok = false; break; }
       uint8_t* btile = tiles_ptr + mma_off + (size_t)s * p.stage_bytes + p.a_bytes;
       const float* inv_s = &s_scale[sb][pw][0][0];
