@@ -1,88 +1,54 @@
-"""Small helpers kept from the reference's exact/exact/utils.py (memory accounting and index casts)."""
-import json
-from collections import OrderedDict
-
-import numpy as np
+"""Host-side helpers of the activation-compression path that the reference keeps in exact/exact/utils.py: index
+narrowing, pinned-host parking of saved tensors, memory accounting."""
 import torch
+
+_INT32_MAX = 2 ** 31 - 1
+_ITEMSIZE = {torch.int64: 8, torch.float64: 8, torch.float32: 4, torch.int32: 4, torch.bfloat16: 2,
+             torch.float16: 2, torch.int16: 2, torch.int8: 1, torch.uint8: 1, torch.bool: 1}
 
 
 def cast_low_bit_int(idx_vec):
-    """utils.py:9-19.  The B200 SpMM reads int32 or int64 indices, so int16 is never produced."""
+    """Index vector narrowed to int32 when its values allow it (the reference also narrows to int16, utils.py:9-19;
+    the SpMM here reads int32 or int64 indices only)."""
     if idx_vec is None:
-        return idx_vec
-    assert idx_vec.dtype == torch.int64
-    if idx_vec.numel() == 0 or int(idx_vec.max()) < np.iinfo(np.int32).max:
-        return idx_vec.to(torch.int32)
-    return idx_vec
-
-
-def cast_adj(data):
-    """utils.py:22-28: narrow every index array of data.adj_t in place."""
-    data.adj_t.to_int32_()
+        return None
+    if idx_vec.dtype != torch.int64:
+        raise TypeError("cast_low_bit_int expects int64 indices")
+    fits = idx_vec.numel() == 0 or int(idx_vec.max()) < _INT32_MAX
+    return idx_vec.to(torch.int32) if fits else idx_vec
 
 
 def swap_to_cpu(tensor):
-    """utils.py:31-34."""
-    tensor_cpu = torch.empty(tensor.shape, dtype=tensor.dtype, device="cpu", pin_memory=True)
-    tensor_cpu.copy_(tensor, non_blocking=True)
-    return tensor_cpu
+    """A pinned host copy of `tensor`, enqueued without waiting (config.swap; utils.py:31-34)."""
+    host = torch.empty_like(tensor, device="cpu", pin_memory=True)
+    return host.copy_(tensor, non_blocking=True)
 
 
 def get_memory_usage(gpu, print_info=False):
-    """utils.py:37-44."""
-    allocated = torch.cuda.memory_allocated(gpu)
-    reserved = torch.cuda.memory_reserved(gpu)
+    """Bytes torch has allocated on `gpu` (utils.py:37-44); optionally prints allocated and reserved MB."""
+    used = torch.cuda.memory_allocated(gpu)
     if print_info:
-        print("allocated: %.2f MB" % (allocated / 1024 / 1024), flush=True)
-        print("reserved:  %.2f MB" % (reserved / 1024 / 1024), flush=True)
-    return allocated
-
-
-_BYTES = {torch.int64: 8, torch.float64: 8, torch.float32: 4, torch.int32: 4, torch.bfloat16: 2,
-          torch.float16: 2, torch.int16: 2, torch.int8: 1, torch.uint8: 1, torch.bool: 1}
+        mb = 1.0 / (1024 * 1024)
+        print(f"allocated: {used * mb:.2f} MB", flush=True)
+        print(f"reserved:  {torch.cuda.memory_reserved(gpu) * mb:.2f} MB", flush=True)
+    return used
 
 
 def compute_tensor_bytes(tensors):
-    """utils.py:47-66."""
-    if not isinstance(tensors, (list, tuple)):
-        tensors = [tensors]
-    ret = 0
-    for x in tensors:
-        if x.dtype not in _BYTES:
-            raise ValueError(x.dtype)
-        ret += int(np.prod(x.size())) * _BYTES[x.dtype]
-    return ret
+    """Total payload bytes of a tensor or a sequence of tensors (utils.py:47-66)."""
+    seq = tensors if isinstance(tensors, (list, tuple)) else (tensors,)
+    total = 0
+    for t in seq:
+        if t.dtype not in _ITEMSIZE:
+            raise ValueError(f"unsupported dtype {t.dtype}")
+        total += t.numel() * _ITEMSIZE[t.dtype]
+    return total
 
 
 def empty_cache(ratio):
-    """utils.py:69-75."""
+    """torch.cuda.empty_cache() when less than `ratio` of the reserved memory is in use (utils.py:69-75)."""
     if ratio is None:
         return
-    allocated = torch.cuda.memory_allocated()
     reserved = torch.cuda.memory_reserved()
-    if reserved > 0 and allocated / reserved < ratio:
+    if reserved > 0 and torch.cuda.memory_allocated() < ratio * reserved:
         torch.cuda.empty_cache()
-
-
-class GlobalExpRecorder:
-    """utils.py:85-103."""
-
-    def __init__(self):
-        self.val_dict = OrderedDict()
-
-    def record(self, key, value, float_round=6):
-        if isinstance(value, (np.int32, np.int64)):
-            value = int(value)
-        if isinstance(value, (float, np.float32, np.float64)):
-            value = round(float(value), float_round)
-        self.val_dict[key] = value
-
-    def dump(self, filename):
-        with open(filename, "a") as fout:
-            fout.write(json.dumps(self.val_dict) + "\n")
-
-    def clear(self):
-        pass
-
-
-exp_recorder = GlobalExpRecorder()
