@@ -186,6 +186,46 @@ def test_oracle_reproduces_reference_kernels():
                     f"spmm case {i} {red} {hv}"
 
 
+GOLDEN_MORE = os.path.join(os.path.dirname(GOLDEN), "ref_vectors_more.npz")
+
+
+@pytest.mark.skipif(not os.path.exists(GOLDEN_MORE), reason="second golden fixture not generated yet")
+def test_oracle_reproduces_reference_half_kernels_minmax_and_value_gradient():
+    """Second fixture written by the reference's unmodified kernels on a B200: the half instantiations of pack /
+    unpack / SpMM (statistics from torch's half tensor ops), the max / min aggregation with its winning-edge
+    positions and the edge-value gradient, reproduced bit for bit."""
+    import hashlib
+    from golden.make_ref_vectors import HALF_PACK_CASES, MORE_SPMM_CASES, make_graph, make_half
+    z = np.load(GOLDEN_MORE)
+    sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).digest()
+    for i in range(len(HALF_PACK_CASES)):
+        N, D, bits, nseed, tseed, offset = (int(v) for v in z[f"hpack{i}_meta"])
+        x = make_half(N, D, nseed)
+        noise = oracle.noise_reference_pack(tseed, offset, N, D, bits)
+        packed, sc, mn = oracle.quantize_activation_f16(x, noise, bits)
+        assert sha(sc.view(np.uint16)) == z[f"hpack{i}_scale"].tobytes(), f"half scale case {i}"
+        assert sha(mn.view(np.uint16)) == z[f"hpack{i}_min"].tobytes(), f"half min case {i}"
+        assert sha(packed) == z[f"hpack{i}_packed"].tobytes(), f"half packed case {i}"
+        up = oracle.unpack_f16(packed, sc, mn, N, D, bits)
+        assert sha(up.view(np.uint16)) == z[f"hpack{i}_unpacked"].tobytes(), f"half unpacked case {i}"
+    for i, (n, K, nnz, seed) in enumerate(MORE_SPMM_CASES):
+        rowptr, col, val = make_graph(n, nnz, seed)
+        mat = np.random.default_rng(seed + 100).standard_normal((n, K)).astype(np.float32)
+        grad = np.random.default_rng(seed + 200).standard_normal((n, K)).astype(np.float32)
+        math, valh = mat.astype(np.float16), (val * 0.5).astype(np.float16)
+        for red in ("sum", "mean"):
+            for hv in (1, 0):
+                out = oracle.spmm_f16(rowptr, col, valh if hv else None, math, red)
+                assert sha(out.view(np.uint16)) == z[f"hspmm{i}_{red}_{hv}"].tobytes(), f"half spmm {i} {red} {hv}"
+            gv = oracle.spmm_value_bw(rowptr, col, mat, grad, red)
+            assert sha(gv) == z[f"valuebw{i}_{red}"].tobytes(), f"value gradient {i} {red}"
+        for red in ("max", "min"):
+            for hv in (1, 0):
+                o, arg = oracle.spmm_minmax(rowptr, col, val if hv else None, mat, red)
+                assert sha(o) == z[f"minmax{i}_{red}_{hv}_out"].tobytes(), f"{red} {i} {hv}"
+                assert sha(np.asarray(arg).astype(np.int64)) == z[f"minmax{i}_{red}_{hv}_arg"].tobytes(), f"{red} arg {i} {hv}"
+
+
 def test_fp16_oracle_equals_torch_half_ops():
     """The fp16 restatement (quantize_activation_f16 / unpack_f16) against the same chain written with torch's
     half tensor ops on CPU, which round every Half (op) Half through fp32 like c10::Half in the reference's
