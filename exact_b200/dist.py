@@ -226,8 +226,8 @@ class ShardedSparseTensor:
         columns of ALL rows (each rank stores its rows' slices into the peers' buffers), multiplies the whole
         adjacency with it, and stores each row block of its result slice into the owner's output buffer.  Two
         all-to-all exchanges of N K / P elements per rank instead of an all-gather of N K (P - 1) / P, equal work
-        on every rank whatever the degree distribution, and gathers over a P times narrower operand.  Per-row
-        sums are regrouped (several edges per load instruction on the narrow slices).  Returns None when the
+        on every rank whatever the degree distribution, and gathers over a P times narrower operand.  The
+        sums of long rows are regrouped (their pieces are added separately).  Returns None when the
         ranks cannot write each other's memory (the caller takes the row-split route; `meanwhile` has then not
         been called).  `meanwhile`: work of the caller that does not depend on the result; it is enqueued on the
         current stream while the first exchange (NVLink-bound stores, issued on a side stream) is in flight."""

@@ -93,7 +93,7 @@ def _aggregate(src, other, reduce, tag="fw", meanwhile=None):
 
 def _aggregate_transposed(src, grad, reduce, rowscale=None, prescaled=False, tag="bw", meanwhile=None):
     """Gradient of reduce(A, other) with respect to `other` (spmm.cc:70-77, 128-137).  Inside the one-node
-    layer the result is an fp32 regrouping of the separate nodes' anyway, so the SpMM may regroup too.
+    layer the result is an fp32 regrouping of the separate nodes' anyway.
     With `rowscale` = 1 / max(deg, 1) the caller asks for A_mean^T g as A^T (D^-1 g): the rows of `grad` are
     scaled on the way into the SpMM and no per-edge weights are read (one load and one multiply per edge
     less: 10.0 against 12.0 ms at 125.8 M edges x 256 columns).  `prescaled`: `grad` already holds D^-1 g."""
