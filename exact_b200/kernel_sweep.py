@@ -197,6 +197,22 @@ def run_bn_bwd(N, D, bits, reps):
             "frac": round(nbytes / (ms * 1e-3) / 1e9 / peak, 4), "peak": peak, "peak_kind": kind}
 
 
+def run_rowops(N, D, reps):
+    """D^-1 g and g.sum(0) in one pass over g against the framework's broadcast multiply + column reduction."""
+    from .cpp_extension import backward_func as B
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev).manual_seed(0)
+    g = torch.randn(N, D, device=dev, generator=gen)
+    inv = torch.rand(N, device=dev, generator=gen)
+    ms = _time(lambda: B.rows_scale_colsum(g, inv, want_scaled=True, want_colsum=True), reps, None)
+    ms_old = _time(lambda: (g * inv.unsqueeze(1), g.sum(0)), reps, None)
+    nbytes = 8 * N * D
+    peak, kind = _peak()
+    return {"op": "rows_scale_colsum", "N": N, "D": D, "ms": round(ms, 4), "multiply_plus_sum_ms": round(ms_old, 4),
+            "GB/s": round(nbytes / (ms * 1e-3) / 1e9, 1), "frac": round(nbytes / (ms * 1e-3) / 1e9 / peak, 4),
+            "peak": peak, "peak_kind": kind}
+
+
 def run_mask(N, D, p, reps):
     """ReLU + dropout of a hidden layer in one pass (forward) and its backward: GB/s on 8 bytes + 1 bit per element."""
     dev = torch.device("cuda")
@@ -351,7 +367,7 @@ def main_sharded(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp", "linear", "mask", "grad_weight", "bn_bwd"])
+    ap.add_argument("--op", default="all", choices=["all", "pack", "unpack", "spmm", "rp_pack", "unpack_rp", "linear", "mask", "grad_weight", "bn_bwd", "rowops"])
     ap.add_argument("--kept-frac", type=float, nargs="*", default=[0.5, 0.125])
     ap.add_argument("--N", type=int, nargs="*", default=[100_000, 1_000_000, 10_000_000])
     ap.add_argument("--D", type=int, nargs="*", default=[64, 128, 256, 602])
@@ -384,6 +400,12 @@ def main():
         for N in a.N:
             for bits in a.bits:
                 print(json.dumps(run_grad_weight(N, 256, 32, bits, a.reps)), flush=True)
+        return
+    if a.op == "rowops":
+        for N in a.N:
+            for D in a.D:
+                if N * D * 4 <= a.max_bytes:
+                    print(json.dumps(run_rowops(N, D, a.reps)), flush=True)
         return
     if a.op == "bn_bwd":
         for N in a.N:
