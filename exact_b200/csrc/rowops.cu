@@ -36,18 +36,34 @@ __global__ void __launch_bounds__(kRowOpsThreads) rows_scale_colsum_kernel(const
 #pragma unroll
     for (int x = 0; x < VEC; x++) acc[x] = 0.f;
     if (col_ok) {
-      for (long long r = (long long)blockIdx.x * p.ry + ty; r < p.n; r += (long long)gridDim.x * p.ry) {
-        float v[VEC];
+      // four rows per step: four loads in flight per thread (one per step left the kernel waiting on memory:
+      // 59 % DRAM throughput at 0.18 issue slots per cycle)
+      constexpr int kRowsPerStep = 4;
+      const long long rstride = (long long)gridDim.x * p.ry;
+      for (long long r0 = (long long)blockIdx.x * p.ry + ty; r0 < p.n; r0 += rstride * kRowsPerStep) {
+        float v[kRowsPerStep][VEC], s[kRowsPerStep];
 #pragma unroll
-        for (int x = 0; x < VEC; x++) v[x] = 0.f;
-        if (in_g) Ld<float, VEC>::load(p.g + r * p.ldg + c, v);
+        for (int u = 0; u < kRowsPerStep; u++) {
+          const long long r = r0 + u * rstride;
 #pragma unroll
-        for (int x = 0; x < VEC; x++) acc[x] = __fadd_rn(acc[x], v[x]);
-        if (p.out != nullptr) {
-          const float s = p.rowscale != nullptr ? __ldg(p.rowscale + r) : 1.f;
+          for (int x = 0; x < VEC; x++) v[u][x] = 0.f;
+          s[u] = 1.f;
+          if (r < p.n) {
+            if (in_g) Ld<float, VEC>::load(p.g + r * p.ldg + c, v[u]);
+            if (p.out != nullptr && p.rowscale != nullptr) s[u] = __ldg(p.rowscale + r);
+          }
+        }
 #pragma unroll
-          for (int x = 0; x < VEC; x++) v[x] = __fmul_rn(v[x], s);
-          StF32<VEC>::store(p.out + r * p.ldo + c, v);
+        for (int u = 0; u < kRowsPerStep; u++) {
+          const long long r = r0 + u * rstride;
+          if (r >= p.n) break;
+#pragma unroll
+          for (int x = 0; x < VEC; x++) acc[x] = __fadd_rn(acc[x], v[u][x]);
+          if (p.out != nullptr) {
+#pragma unroll
+            for (int x = 0; x < VEC; x++) v[u][x] = __fmul_rn(v[u][x], s[u]);
+            StF32<VEC>::store(p.out + r * p.ldo + c, v[u]);
+          }
         }
       }
     }
