@@ -196,3 +196,21 @@ def test_benchmark_knobs_follow_the_reference_driver():
         assert not config.compress_activation and config.kept_frac == 1.0 and not c["use_qmodule"]
     finally:
         config.compress_activation, config.activation_compression_bits, config.kept_frac = True, [2], 1.0
+
+
+def test_aggregation_mode_follows_the_world_size_unless_forced():
+    from exact_b200 import config
+    from exact_b200.dist import column_split_active, shard_rows
+    old = config.column_split_aggregation
+    try:
+        config.column_split_aggregation = None
+        assert [column_split_active(w) for w in (1, 2, 4, 8, 16)] == [False, False, False, True, True]
+        config.column_split_aggregation = True
+        assert column_split_active(2)
+        config.column_split_aggregation = False
+        assert not column_split_active(8)
+    finally:
+        config.column_split_aggregation = old
+    # shards are multiples of 8 rows (packed streams of the shards concatenate to the single-GPU stream)
+    assert shard_rows(2449029, 8) % 8 == 0 and shard_rows(2449029, 8) * 8 >= 2449029
+    assert shard_rows(10, 4) == 8
