@@ -64,9 +64,9 @@ class QuantizationConfig:
         # Row-sharded runs: aggregate feature-parallel (every rank multiplies the whole adjacency with a column
         # slice of the operand; two all-to-all exchanges written into the peers' buffers) instead of gathering
         # all rows of the operand on every rank.  Needs peer_exchange; the pieces of long rows are then summed
-        # separately.  None: from 8 ranks on (measured per epoch of the 2.45 M-node benchmark: 37.9 against 36.5 ms
-        # at 2 ranks, 23.1 against 21.4 ms at 4; the gathered volume of the row split grows with the ranks, the
-        # two exchanges of the column split shrink).  True / False: always / never.
+        # separately.  None: from 8 ranks on (measured per epoch of the 2.45 M-node benchmark: 34.9 against 32.9 ms
+        # at 2 ranks, 23.6 against 21.1 ms at 4, 15.2 against 15.4 ms at 8; the gathered volume of the row split
+        # grows with the ranks, the two exchanges of the column split shrink).  True / False: always / never.
         self.column_split_aggregation = None
         # ... on: every rank's SpMM stores its result rows straight into their owners' buffers (the second exchange
         # folded into the kernel); off: a local result followed by a scatter kernel.  Off by default: the narrow
