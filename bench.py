@@ -219,6 +219,8 @@ def run_b200(args):
     config.peer_exchange = not args.no_peer_exchange
     config.column_split_aggregation = False if args.row_split else (True if args.column_split else None)
     config.routed_aggregation_output = bool(args.routed_output)
+    if args.min_slice_columns is not None:
+        config.aggregation_min_slice_columns = args.min_slice_columns
     config.cache_constant_gather = False   # every timed step exchanges its input features again
     net = cls(c["feats"], c["hidden"], c["classes"], c["layers"], dropout=c["dropout"], batch_norm=c["batch_norm"])
     net = (QModule(net) if c["use_qmodule"] else net).to(dev).train()
@@ -736,6 +738,9 @@ def main():
     ap.add_argument("--routed-output", action="store_true",
                     help="N > 1: the SpMM of the feature-parallel aggregation stores its result rows straight into "
                          "their owners' buffers instead of a local result followed by a scatter kernel")
+    ap.add_argument("--min-slice-columns", type=int, default=None,
+                    help="N > 1: config.aggregation_min_slice_columns (narrow operands of the feature-parallel "
+                         "aggregation are cut into fewer, wider column slices times row blocks)")
     ap.add_argument("--cpu-reference", action="store_true",
                     help="--impl reference: time the CPU restatement even when the reference's CUDA kernels are built")
     # the reference drivers' knobs (mem_speed_bench/arxiv/train_full_batch.py:44-48)

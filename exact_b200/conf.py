@@ -68,6 +68,11 @@ class QuantizationConfig:
         # at 2 ranks, 23.6 against 21.1 ms at 4, 15.2 against 15.4 ms at 8; the gathered volume of the row split
         # grows with the ranks, the two exchanges of the column split shrink).  True / False: always / never.
         self.column_split_aggregation = None
+        # Columns a slice of the feature-parallel aggregation should at least have.  Operands with fewer than
+        # world * this many columns are cut into fewer slices (the world size halved until a slice is wide enough)
+        # and the rows into as many blocks: rank (i, j) multiplies row block i with column slice j.  0: always one
+        # slice per rank.
+        self.aggregation_min_slice_columns = 0
         # ... on: every rank's SpMM stores its result rows straight into their owners' buffers (the second exchange
         # folded into the kernel); off: a local result followed by a scatter kernel.  Off by default: the narrow
         # kernel takes the rows in length-sorted order, and rows of 48 - 256 bytes stored over NVLink in that order

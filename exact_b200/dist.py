@@ -150,6 +150,7 @@ class ShardedSparseTensor:
             self.full_t["sum"] = (self.full_t[self.reduce][0], self.full_t[self.reduce][1], None)
         self._col_bufs = {}         # (kind, width) -> [PeerBuffers, PeerBuffers] of the feature-parallel exchange
         self._col_turn = {}
+        self._blocks = {}           # (matrix, Pc) -> CSR of this rank's row block of a two-dimensional split
         self._gather_buf = {}
         self._dense_streak = {}     # tag -> calls left before compaction is tried again after a dense operand
         self._const_gather = None   # (tensor, version, gathered): input features do not change between epochs
@@ -236,25 +237,38 @@ class ShardedSparseTensor:
         P, S, N = self.world, self.shard, self.n_global
         if not (column_split_active(self.world) and x_local.dtype == torch.float32 and K % 4 == 0):
             return None
-        Kp = ((K + P - 1) // P + 3) // 4 * 4
-        inb = self._column_buffers("in", Kp, P * S * Kp * 4, dev)
+        # Pc column slices times Pr = P / Pc row blocks.  Rank (i, j) = i * Pc + j receives slice j (Kp columns) of
+        # ALL rows and multiplies row block i of the adjacency (the rows of ranks i * Pc .. i * Pc + Pc - 1) with
+        # it.  Pc = P, one block: the plain column split.  A gather costs one L2 request per edge up to 128 bytes
+        # of slice, so slices of 8 - 16 columns take as long as one of 32; fewer, wider slices over 1 / Pr of
+        # the edges are faster as long as the wider first exchange (N K / Pc elements into every rank) allows.
+        Pc = self.column_slices(K)
+        Pr = P // Pc
+        blk, sl = self.rank // Pc, self.rank % Pc
+        Kp = ((K + Pc - 1) // Pc + 3) // 4 * 4
+        inb = self._column_buffers("in/%d" % Pc, Kp, P * S * Kp * 4, dev)
         if inb is None:
             return None
-        outb = self._column_buffers("out", Kp, S * P * Kp * 4, dev)
+        outb = self._column_buffers("out/%d" % Pc, Kp, S * Pc * Kp * 4, dev)
         if outb is None:
             return None
         x_local = x_local if (x_local.stride(1) == 1 and x_local.stride(0) % 4 == 0 and x_local.data_ptr() % 16 == 0) \
             else x_local.contiguous()
+
+        def first_exchange():
+            for b in range(Pr):      # slice q of this rank's rows to rank (b, q), every b
+                ext_rows.cols_scatter(x_local, rowscale, self.row_start, Kp, inb.ptrs[b * Pc:(b + 1) * Pc])
+
         if meanwhile is not None and config.overlap_exchange:
             main = torch.cuda.current_stream(dev)
             side = self._side_stream(dev)
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                ext_rows.cols_scatter(x_local, rowscale, self.row_start, Kp, inb.ptrs)
+                first_exchange()
             meanwhile()
             main.wait_stream(side)      # x_local and rowscale stay alive in this frame until both streams have joined
         else:
-            ext_rows.cols_scatter(x_local, rowscale, self.row_start, Kp, inb.ptrs)
+            first_exchange()
             if meanwhile is not None:
                 meanwhile()
         self._order_peer_stores(dev)
@@ -262,31 +276,65 @@ class ShardedSparseTensor:
         if transposed:
             # rows already scaled by 1 / deg (here or by the caller): A_mean^T g = A^T (D^-1 g), no edge weights
             unweighted = unweighted or rowscale is not None
-            t_ptr, t_col, t_w = self.full_t["sum" if (unweighted and "sum" in self.full_t) else self.reduce]
-            args = (t_ptr, t_col, None if unweighted else t_w, slice_all, "sum")
+            which = "sum" if (unweighted and "sum" in self.full_t) else self.reduce
+            ptr, col, w = self._row_block(("t", which), Pc)
+            args = (ptr, col, None if unweighted else w, slice_all, "sum")
         else:
-            args = (self.full_rowptr, self.full_col, self.full_value, slice_all, reduce)
-        if config.slice_major_result:
+            ptr, col, w = self._row_block(("a",), Pc)
+            args = (ptr, col, w, slice_all, reduce)
+        owners = outb.ptrs[blk * Pc:(blk + 1) * Pc]       # the ranks whose rows this rank's block covers
+        if Pr == 1 and config.slice_major_result:
             # the owner's buffer holds P dense [S, Kp] slices, one per source rank: every store of the second
             # exchange is contiguous whatever Kp (row-major, a rank's pieces are Kp * 4 bytes at a pitch of K * 4:
             # 32 - 128 bytes at 8 ranks); the owner interleaves the slices locally afterwards
             col0, ldd = 0, Kp
             ptrs = [p + self.rank * S * Kp * 4 for p in outb.ptrs]
         else:
-            col0, ldd, ptrs = self.rank * Kp, P * Kp, outb.ptrs
-        if config.routed_aggregation_output and P <= 8:
-            # every result row goes from the warp that summed it straight into its owner's buffer
-            ext_spmm._spmm(*args, regroup=True, route=(S, col0, ldd, ptrs))
-        else:
-            y = ext_spmm._spmm(*args, regroup=True)
-            ext_rows.rows_scatter(y, S, col0, ldd, ptrs)
+            col0, ldd, ptrs = sl * Kp, Pc * Kp, owners
+        if ptr.numel() > 1:
+            if Pr == 1 and config.routed_aggregation_output and P <= 8:
+                # every result row goes from the warp that summed it straight into its owner's buffer
+                ext_spmm._spmm(*args, regroup=True, route=(S, col0, ldd, ptrs))
+            else:
+                y = ext_spmm._spmm(*args, regroup=True)
+                ext_rows.rows_scatter(y, S, col0, ldd, ptrs)
         self._order_peer_stores(dev)
-        if config.slice_major_result:
+        if Pr == 1 and config.slice_major_result:
             out = outb.local_tensor().view(torch.float32).view(P, S, Kp)[:, :n_loc].permute(1, 0, 2).reshape(n_loc, P * Kp)
             return out if K == P * Kp else out[:, :K].contiguous()
-        out = outb.local_tensor().view(torch.float32).view(S, P * Kp)[:n_loc]
+        out = outb.local_tensor().view(torch.float32).view(S, Pc * Kp)[:n_loc]
         # the buffer is written again two aggregations of this width later: callers consume the result at once
-        return out if K == P * Kp else out[:, :K].contiguous()
+        return out if K == Pc * Kp else out[:, :K].contiguous()
+
+    def column_slices(self, K):
+        """Number of column slices Pc (a divisor of the world size) the feature-parallel aggregation of a
+        K-column operand uses: the world size halved until a slice has config.aggregation_min_slice_columns
+        columns (0: always the world size)."""
+        Pc = self.world
+        m = config.aggregation_min_slice_columns
+        while m > 0 and Pc > 1 and Pc % 2 == 0 and -(-K // Pc) < m:
+            Pc //= 2
+        return Pc
+
+    def _row_block(self, key, Pc):
+        """CSR (rowptr, col, weights) of the rows this rank multiplies when the operand is cut into Pc column
+        slices: the whole matrix for Pc = world, else the rows of the Pc ranks of its block (a contiguous row
+        range: a slice of the arrays, copied once)."""
+        if key[0] == "t":
+            full = self.full_t[key[1]]
+        else:
+            full = (self.full_rowptr, self.full_col, self.full_value)
+        if Pc == self.world:
+            return full
+        got = self._blocks.get((key, Pc))
+        if got is None:
+            rowptr, col, w = full
+            b0 = min((self.rank // Pc) * Pc * self.shard, self.n_global)
+            b1 = min(b0 + Pc * self.shard, self.n_global)
+            e0, e1 = int(rowptr[b0]), int(rowptr[b1])
+            got = ((rowptr[b0:b1 + 1] - e0).contiguous(), col[e0:e1].clone(), None if w is None else w[e0:e1].clone())
+            self._blocks[(key, Pc)] = got
+        return got
 
     def _side_stream(self, dev):
         st = getattr(self, "_side", None)
@@ -296,7 +344,10 @@ class ShardedSparseTensor:
 
     def describe_exchange(self):
         if self._col_bufs:
-            return "feature-parallel aggregation: two all-to-all exchanges written into the peers' buffers"
+            cuts = sorted({int(k[0].split("/")[1]) for k in self._col_bufs if "/" in str(k[0])}, reverse=True)
+            grid = ", ".join("%dx%d" % (c, self.world // c) for c in cuts)
+            return ("feature-parallel aggregation: two all-to-all exchanges written into the peers' buffers"
+                    + (f" (column slices x row blocks: {grid})" if grid else ""))
         if self._peers:
             return "compact rows written into the peers' buffers"
         return "rows through the collective library" + (" (zero-compacted)" if config.compact_gather else "")

@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--routed", type=int, default=0)
     ap.add_argument("--overlap", type=int, default=0)
     ap.add_argument("--slicemajor", type=int, default=0)
+    ap.add_argument("--minslice", type=int, default=0)
     a = ap.parse_args()
 
     import torch
@@ -52,6 +53,7 @@ def main():
     config.routed_aggregation_output = bool(a.routed)
     config.overlap_exchange = bool(a.overlap)
     config.slice_major_result = bool(a.slicemajor)
+    config.aggregation_min_slice_columns = a.minslice
     config.cache_constant_gather = False
     if a.world > 1:
         adj = xdist.shard_graph(full, "mean", a.rank, a.world)
@@ -105,9 +107,11 @@ def main():
         forms = {k: (v[0], v[2]) for k, v in form.state.items()}
     peers_used = bool(getattr(adj, "_peers", None)) or bool(getattr(adj, "_col_bufs", None))
     exchange = adj.describe_exchange() if a.world > 1 else "none"
+    col_keys = sorted(getattr(adj, "_col_bufs", {}).keys()) if a.world > 1 else []
     torch.save({"losses": losses, "grads0": grads0, "params": [p.detach().cpu() for p in params],
                 "packed": first["packed"].cpu()[:-1], "scale": first["scale"].cpu(), "min": first["min"].cpu(),
-                "rows": (r0, r1), "forms": forms, "peers_used": peers_used, "exchange": exchange},
+                "rows": (r0, r1), "forms": forms, "peers_used": peers_used, "exchange": exchange,
+                "col_keys": col_keys},
                os.path.join(a.out, f"w{a.world}_{a.name}_r{a.rank}.pt"))
     if a.world > 1:
         adj.close()

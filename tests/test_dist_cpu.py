@@ -159,3 +159,105 @@ def test_compacted_gather_equals_dense_gather(tmp_path):
         assert np.array_equal(p["off"].numpy(), sparse)
         assert np.array_equal(p["dense"].numpy(), dense) and np.array_equal(p["dense_again"].numpy(), dense)
         assert p["streak_after_sparse"] == 0 and p["streak_after_dense"] == 16 and p["streak_after_second"] == 15
+
+
+# ---- feature-parallel aggregation with row blocks: the ranks are threads, the peers' buffers shared tensors -----
+def _aggregate_on_threads(world, min_slice, K, n, reduce, with_values, transposed, monkeypatch):
+    import threading
+
+    from exact_b200 import SparseTensor, config
+    from exact_b200 import dist as xdist
+
+    rowptr, col, val = random_csr(n, n, 6 * n, 3, with_values)
+    row = np.repeat(np.arange(n), np.diff(rowptr))
+    full = SparseTensor(row=torch.from_numpy(row), col=torch.from_numpy(col),
+                        value=None if val is None else torch.from_numpy(val), sparse_sizes=(n, n), is_sorted=True)
+    shared, lock, barrier = {}, threading.Lock(), threading.Barrier(world)
+
+    class Buf:
+        def __init__(self, tensors, rank):
+            self.ptrs, self.rank = tensors, rank
+
+        def local_tensor(self):
+            return self.ptrs[self.rank]
+
+    def column_buffers(self, kind, width, nbytes, device):
+        key = (kind, width)
+        turn = self._col_turn.get(key, 0)
+        self._col_turn[key] = turn + 1
+        self._col_bufs[key] = True
+        with lock:
+            tensors = shared.setdefault((kind, width, turn & 1), [torch.full((nbytes // 4,), float("nan")) for _ in range(world)])
+        return Buf(tensors, self.rank)
+
+    def cols_scatter(x, rowscale, row0, Kp, dsts):
+        m, Kx = x.shape
+        xs = x if rowscale is None else x * rowscale.reshape(-1, 1)
+        for q, d in enumerate(dsts):
+            piece = torch.zeros(m, Kp)
+            part = xs[:, q * Kp:(q + 1) * Kp]
+            piece[:, :part.size(1)] = part
+            d.view(-1, Kp)[row0:row0 + m] = piece
+
+    def rows_scatter(y, shard, col0, ldd, dsts):
+        assert y.size(0) <= shard * len(dsts)
+        for p, d in enumerate(dsts):
+            rows = y[p * shard:(p + 1) * shard]
+            d.view(-1, ldd)[:rows.size(0), col0:col0 + y.size(1)] = rows
+
+    def spmm(rowptr, col, value, mat, reduce, regroup=False, route=None):
+        assert route is None
+        return _oracle_spmm(rowptr, col, value, mat, reduce)
+
+    monkeypatch.setattr(xdist.ShardedSparseTensor, "_column_buffers", column_buffers)
+    monkeypatch.setattr(xdist.ShardedSparseTensor, "_order_peer_stores", lambda self, dev: barrier.wait(timeout=60))
+    monkeypatch.setattr(xdist.ext_rows, "cols_scatter", cols_scatter)
+    monkeypatch.setattr(xdist.ext_rows, "rows_scatter", rows_scatter)
+    monkeypatch.setattr(xdist.ext_spmm, "_spmm", spmm)
+    monkeypatch.setattr(config, "column_split_aggregation", True)
+    monkeypatch.setattr(config, "aggregation_min_slice_columns", min_slice)
+    x_full = torch.from_numpy(normal(n, K, 4))
+    scale_full = torch.from_numpy(np.abs(normal(n, 1, 6)).reshape(-1) + 0.5)
+    outs, errors, slices = [None] * world, [], set()
+
+    def rank_main(r):
+        try:
+            adj = xdist.ShardedSparseTensor(full, reduce, r, world)
+            slices.add(adj.column_slices(K))
+            x = x_full[adj.row_start:adj.row_end].clone()
+            for _ in range(3):          # three calls: both buffers of a pair are reused
+                if transposed:
+                    out = adj.aggregate(x, reduce, transposed=True, rowscale=scale_full[adj.row_start:adj.row_end].clone())
+                else:
+                    out = adj.aggregate(x, reduce)
+                outs[r] = out.clone()
+        except Exception as e:   # noqa: BLE001
+            errors.append((r, repr(e)))
+            barrier.abort()
+
+    threads = [threading.Thread(target=rank_main, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    import oracle
+    if transposed:
+        t_ptr, t_col, _ = full.storage.transposed("sum")
+        ref = oracle.spmm(t_ptr.numpy().astype(np.int64), t_col.numpy().astype(np.int64), None,
+                          (x_full * scale_full.reshape(-1, 1)).numpy(), "sum")
+    else:
+        ref = oracle.spmm(rowptr, col, val, x_full.numpy(), reduce)
+    got = torch.cat(outs).numpy()
+    assert got.shape == ref.shape and np.array_equal(got, ref)
+    return slices
+
+
+def test_feature_parallel_aggregation_row_blocks_on_cpu(monkeypatch):
+    # 203 rows on 8 ranks: shards of 32 rows, the last rank's shard is empty, the last row block is short
+    assert _aggregate_on_threads(8, 0, 48, 203, "mean", False, False, monkeypatch) == {8}
+    assert _aggregate_on_threads(8, 20, 48, 203, "mean", False, False, monkeypatch) == {2}
+    assert _aggregate_on_threads(8, 20, 100, 203, "sum", True, False, monkeypatch) == {4}
+    assert _aggregate_on_threads(8, 20, 48, 203, "mean", False, True, monkeypatch) == {2}
+    assert _aggregate_on_threads(8, 64, 48, 203, "mean", False, False, monkeypatch) == {1}
+    assert _aggregate_on_threads(4, 20, 48, 1000, "mean", False, True, monkeypatch) == {2}

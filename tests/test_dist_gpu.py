@@ -95,6 +95,21 @@ def test_sharded_run_with_feature_parallel_aggregation(world, routed, single, tm
     _compare_with_single(parts, single, regrouped=True)
 
 
+@pytest.mark.parametrize("world,minslice,expect", [(8, 20, {"in/2", "in/4", "in/8"}), (2, 64, {"in/1", "in/2"})])
+def test_feature_parallel_aggregation_with_row_blocks(world, minslice, expect, single, tmp_path):
+    """config.aggregation_min_slice_columns: narrow operands are cut into fewer column slices and the rows into
+    blocks (rank (i, j) multiplies row block i with slice j).  Every row is still summed in the order of its
+    edges, so the numbers equal those of one slice per rank bit for bit."""
+    parts = _run(world, tmp_path, "blocks", peer=1, colsplit=1, minslice=minslice)
+    assert all(p["exchange"].startswith("feature-parallel") for p in parts)
+    assert {k[0] for k in parts[0]["col_keys"] if k[0].startswith("in/")} == expect
+    _compare_with_single(parts, single, regrouped=True)
+    plain = _run(world, tmp_path, "slices", peer=1, colsplit=1)
+    assert parts[0]["losses"] == plain[0]["losses"]
+    for p, q in zip(parts, plain):
+        assert all(torch.equal(a, b) for a, b in zip(p["grads0"], q["grads0"]))
+
+
 def test_feature_parallel_aggregation_with_slice_major_result_buffers(single, tmp_path):
     """config.slice_major_result: the second exchange writes dense per-source slices into the owners' buffers,
     interleaved into rows locally."""
