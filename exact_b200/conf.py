@@ -71,8 +71,12 @@ class QuantizationConfig:
         # Columns a slice of the feature-parallel aggregation should at least have.  Operands with fewer than
         # world * this many columns are cut into fewer slices (the world size halved until a slice is wide enough)
         # and the rows into as many blocks: rank (i, j) multiplies row block i with column slice j.  0: always one
-        # slice per rank.
-        self.aggregation_min_slice_columns = 0
+        # slice per rank.  A gather costs one L2 request per edge whatever its width up to 128 bytes, so eight
+        # slices of 6 - 16 columns each take as long as eight of 32; wider slices over fewer rows cost less until
+        # the first exchange (N K / slices elements into every rank) outweighs it.  Measured per epoch of the
+        # 2.45 M-node benchmark at 8 ranks: 15.30 ms with 0, 14.79 ms with 20 (the 48-column operand in 2 slices
+        # x 4 row blocks, those of 80 and 100 columns in 4 x 2), 17.42 ms with 32; same numbers bit for bit.
+        self.aggregation_min_slice_columns = 20
         # ... on: every rank's SpMM stores its result rows straight into their owners' buffers (the second exchange
         # folded into the kernel); off: a local result followed by a scatter kernel.  Off by default: the narrow
         # kernel takes the rows in length-sorted order, and rows of 48 - 256 bytes stored over NVLink in that order
