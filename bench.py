@@ -221,6 +221,8 @@ def run_b200(args):
     config.routed_aggregation_output = bool(args.routed_output)
     if args.min_slice_columns is not None:
         config.aggregation_min_slice_columns = args.min_slice_columns
+    if args.result_chunks is not None:
+        config.aggregation_result_chunks = args.result_chunks
     config.cache_constant_gather = False   # every timed step exchanges its input features again
     net = cls(c["feats"], c["hidden"], c["classes"], c["layers"], dropout=c["dropout"], batch_norm=c["batch_norm"])
     net = (QModule(net) if c["use_qmodule"] else net).to(dev).train()
@@ -741,6 +743,9 @@ def main():
     ap.add_argument("--min-slice-columns", type=int, default=None,
                     help="N > 1: config.aggregation_min_slice_columns (narrow operands of the feature-parallel "
                          "aggregation are cut into fewer, wider column slices times row blocks)")
+    ap.add_argument("--result-chunks", type=int, default=None,
+                    help="N > 1: config.aggregation_result_chunks (pieces a rank's row block of the feature-parallel "
+                         "aggregation is summed in; each piece's stores overlap the next piece's sums)")
     ap.add_argument("--cpu-reference", action="store_true",
                     help="--impl reference: time the CPU restatement even when the reference's CUDA kernels are built")
     # the reference drivers' knobs (mem_speed_bench/arxiv/train_full_batch.py:44-48)

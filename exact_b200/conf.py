@@ -77,6 +77,10 @@ class QuantizationConfig:
         # 2.45 M-node benchmark at 8 ranks: 15.30 ms with 0, 14.79 ms with 20 (the 48-column operand in 2 slices
         # x 4 row blocks, those of 80 and 100 columns in 4 x 2), 17.42 ms with 32; same numbers bit for bit.
         self.aggregation_min_slice_columns = 20
+        # Pieces (of whole owners' rows) a rank's row block of the feature-parallel aggregation is summed in: with
+        # more than one, a piece's result is stored into its owners' buffers on a side stream while the next piece
+        # is summed.  Same numbers.
+        self.aggregation_result_chunks = 1
         # ... on: every rank's SpMM stores its result rows straight into their owners' buffers (the second exchange
         # folded into the kernel); off: a local result followed by a scatter kernel.  Off by default: the narrow
         # kernel takes the rows in length-sorted order, and rows of 48 - 256 bytes stored over NVLink in that order

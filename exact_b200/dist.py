@@ -150,7 +150,7 @@ class ShardedSparseTensor:
             self.full_t["sum"] = (self.full_t[self.reduce][0], self.full_t[self.reduce][1], None)
         self._col_bufs = {}         # (kind, width) -> [PeerBuffers, PeerBuffers] of the feature-parallel exchange
         self._col_turn = {}
-        self._blocks = {}           # (matrix, Pc) -> CSR of this rank's row block of a two-dimensional split
+        self._blocks = {}           # (matrix, first rank, ranks) -> CSR of those ranks' rows
         self._gather_buf = {}
         self._dense_streak = {}     # tag -> calls left before compaction is tried again after a dense operand
         self._const_gather = None   # (tensor, version, gathered): input features do not change between epochs
@@ -273,16 +273,24 @@ class ShardedSparseTensor:
                 meanwhile()
         self._order_peer_stores(dev)
         slice_all = inb.local_tensor().view(torch.float32).view(P * S, Kp)[:N]
+        first = blk * Pc                                  # this rank's row block: the rows of ranks first .. first + Pc - 1
         if transposed:
             # rows already scaled by 1 / deg (here or by the caller): A_mean^T g = A^T (D^-1 g), no edge weights
             unweighted = unweighted or rowscale is not None
-            which = "sum" if (unweighted and "sum" in self.full_t) else self.reduce
-            ptr, col, w = self._row_block(("t", which), Pc)
-            args = (ptr, col, None if unweighted else w, slice_all, "sum")
+            mkey = ("t", "sum" if (unweighted and "sum" in self.full_t) else self.reduce)
+
+            def spmm_rows(o0, on, **kw):
+                ptr, col, w = self._row_range(mkey, o0, on)
+                if ptr.numel() <= 1:
+                    return None
+                return ext_spmm._spmm(ptr, col, None if unweighted else w, slice_all, "sum", regroup=True, **kw)
         else:
-            ptr, col, w = self._row_block(("a",), Pc)
-            args = (ptr, col, w, slice_all, reduce)
-        owners = outb.ptrs[blk * Pc:(blk + 1) * Pc]       # the ranks whose rows this rank's block covers
+            def spmm_rows(o0, on, **kw):
+                ptr, col, w = self._row_range(("a",), o0, on)
+                if ptr.numel() <= 1:
+                    return None
+                return ext_spmm._spmm(ptr, col, w, slice_all, reduce, regroup=True, **kw)
+        owners = outb.ptrs[first:first + Pc]              # the ranks whose rows this rank's block covers
         if Pr == 1 and config.slice_major_result:
             # the owner's buffer holds P dense [S, Kp] slices, one per source rank: every store of the second
             # exchange is contiguous whatever Kp (row-major, a rank's pieces are Kp * 4 bytes at a pitch of K * 4:
@@ -291,13 +299,31 @@ class ShardedSparseTensor:
             ptrs = [p + self.rank * S * Kp * 4 for p in outb.ptrs]
         else:
             col0, ldd, ptrs = sl * Kp, Pc * Kp, owners
-        if ptr.numel() > 1:
-            if Pr == 1 and config.routed_aggregation_output and P <= 8:
-                # every result row goes from the warp that summed it straight into its owner's buffer
-                ext_spmm._spmm(*args, regroup=True, route=(S, col0, ldd, ptrs))
-            else:
-                y = ext_spmm._spmm(*args, regroup=True)
+        chunks = min(max(int(config.aggregation_result_chunks), 1), Pc)
+        while Pc % chunks:
+            chunks -= 1
+        if Pr == 1 and config.routed_aggregation_output and P <= 8:
+            # every result row goes from the warp that summed it straight into its owner's buffer
+            spmm_rows(first, Pc, route=(S, col0, ldd, ptrs))
+        elif chunks == 1:
+            y = spmm_rows(first, Pc)
+            if y is not None:
                 ext_rows.rows_scatter(y, S, col0, ldd, ptrs)
+        else:
+            # the block in `chunks` pieces of whole owners: the stores of a piece's result into its owners' buffers
+            # (NVLink-bound, on a side stream) run while the next piece is summed (L2-bound)
+            main = torch.cuda.current_stream(dev)
+            side = self._side_stream(dev)
+            per = Pc // chunks
+            for c in range(chunks):
+                y = spmm_rows(first + c * per, per)
+                if y is None:
+                    continue
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    ext_rows.rows_scatter(y, S, col0, ldd, ptrs[c * per:(c + 1) * per])
+                y.record_stream(side)
+            main.wait_stream(side)
         self._order_peer_stores(dev)
         if Pr == 1 and config.slice_major_result:
             out = outb.local_tensor().view(torch.float32).view(P, S, Kp)[:, :n_loc].permute(1, 0, 2).reshape(n_loc, P * Kp)
@@ -316,24 +342,24 @@ class ShardedSparseTensor:
             Pc //= 2
         return Pc
 
-    def _row_block(self, key, Pc):
-        """CSR (rowptr, col, weights) of the rows this rank multiplies when the operand is cut into Pc column
-        slices: the whole matrix for Pc = world, else the rows of the Pc ranks of its block (a contiguous row
-        range: a slice of the arrays, copied once)."""
+    def _row_range(self, key, first, count):
+        """CSR (rowptr, col, weights) of the rows of ranks first .. first + count - 1 of the adjacency (key
+        ("a",)) or its transpose (key ("t", reduce)): the whole matrix for all ranks, else a slice of the arrays
+        (the rows are a contiguous range), copied once."""
         if key[0] == "t":
             full = self.full_t[key[1]]
         else:
             full = (self.full_rowptr, self.full_col, self.full_value)
-        if Pc == self.world:
+        if first == 0 and count == self.world:
             return full
-        got = self._blocks.get((key, Pc))
+        got = self._blocks.get((key, first, count))
         if got is None:
             rowptr, col, w = full
-            b0 = min((self.rank // Pc) * Pc * self.shard, self.n_global)
-            b1 = min(b0 + Pc * self.shard, self.n_global)
+            b0 = min(first * self.shard, self.n_global)
+            b1 = min(b0 + count * self.shard, self.n_global)
             e0, e1 = int(rowptr[b0]), int(rowptr[b1])
             got = ((rowptr[b0:b1 + 1] - e0).contiguous(), col[e0:e1].clone(), None if w is None else w[e0:e1].clone())
-            self._blocks[(key, Pc)] = got
+            self._blocks[(key, first, count)] = got
         return got
 
     def _side_stream(self, dev):

@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--overlap", type=int, default=0)
     ap.add_argument("--slicemajor", type=int, default=0)
     ap.add_argument("--minslice", type=int, default=0)
+    ap.add_argument("--chunks", type=int, default=1)
     a = ap.parse_args()
 
     import torch
@@ -54,6 +55,7 @@ def main():
     config.overlap_exchange = bool(a.overlap)
     config.slice_major_result = bool(a.slicemajor)
     config.aggregation_min_slice_columns = a.minslice
+    config.aggregation_result_chunks = a.chunks
     config.cache_constant_gather = False
     if a.world > 1:
         adj = xdist.shard_graph(full, "mean", a.rank, a.world)

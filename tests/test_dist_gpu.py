@@ -110,6 +110,19 @@ def test_feature_parallel_aggregation_with_row_blocks(world, minslice, expect, s
         assert all(torch.equal(a, b) for a, b in zip(p["grads0"], q["grads0"]))
 
 
+@pytest.mark.parametrize("world,minslice,chunks", [(8, 20, 2), (8, 0, 4), (2, 0, 2)])
+def test_feature_parallel_aggregation_with_result_in_pieces(world, minslice, chunks, single, tmp_path):
+    """config.aggregation_result_chunks: a rank's row block is summed in pieces of whole owners' rows and each
+    piece's result is stored into its owners' buffers on a side stream while the next piece is summed.  The
+    numbers are those of one piece."""
+    parts = _run(world, tmp_path, "pieces", peer=1, colsplit=1, minslice=minslice, chunks=chunks)
+    _compare_with_single(parts, single, regrouped=True)
+    plain = _run(world, tmp_path, "onepiece", peer=1, colsplit=1)
+    assert parts[0]["losses"] == plain[0]["losses"]
+    for p, q in zip(parts, plain):
+        assert all(torch.equal(a, b) for a, b in zip(p["grads0"], q["grads0"]))
+
+
 def test_feature_parallel_aggregation_with_slice_major_result_buffers(single, tmp_path):
     """config.slice_major_result: the second exchange writes dense per-source slices into the owners' buffers,
     interleaved into rows locally."""
