@@ -74,9 +74,10 @@ class QuantizationConfig:
         # slice per rank.  A gather costs one L2 request per edge whatever its width up to 128 bytes, so eight
         # slices of 6 - 16 columns each take as long as eight of 32; wider slices over fewer rows cost less until
         # the first exchange (N K / slices elements into every rank) outweighs it.  Measured per epoch of the
-        # 2.45 M-node benchmark at 8 ranks: 15.30 ms with 0, 14.79 ms with 20 (the 48-column operand in 2 slices
-        # x 4 row blocks, those of 80 and 100 columns in 4 x 2), 17.42 ms with 32; same numbers bit for bit.
-        self.aggregation_min_slice_columns = 20
+        # 2.45 M-node benchmark at 8 ranks: 15.30 ms with 0, 14.45 ms with 12 (the operands of 48 and 80 columns in
+        # 4 slices x 2 row blocks), 14.79 - 14.92 ms with 20 (48 columns in 2 x 4, 80 and 100 in 4 x 2), 15.41 ms with
+        # 24, 17.42 ms with 32; same numbers bit for bit.
+        self.aggregation_min_slice_columns = 12
         # Pieces (of whole owners' rows) a rank's row block of the feature-parallel aggregation is summed in: with
         # more than one, a piece's result is stored into its owners' buffers on a side stream while the next piece
         # is summed.  Same numbers.  Measured per epoch at 8 ranks: 14.9 ms with 1, 15.5 ms with 2, 16.5 ms with 4
