@@ -95,7 +95,7 @@ def test_sharded_run_with_feature_parallel_aggregation(world, routed, single, tm
     _compare_with_single(parts, single, regrouped=True)
 
 
-@pytest.mark.parametrize("world,minslice,expect", [(8, 20, {"in/2", "in/4", "in/8"}), (2, 64, {"in/1", "in/2"})])
+@pytest.mark.parametrize("world,minslice,expect", [(8, 12, {"in/4", "in/8"}), (8, 20, {"in/2", "in/4", "in/8"}), (2, 64, {"in/1", "in/2"})])
 def test_feature_parallel_aggregation_with_row_blocks(world, minslice, expect, single, tmp_path):
     """config.aggregation_min_slice_columns: narrow operands are cut into fewer column slices and the rows into
     blocks (rank (i, j) multiplies row block i with slice j).  Every row is still summed in the order of its
