@@ -333,7 +333,10 @@ def run_b200(args):
     for e in freed:
         e.record(torch.cuda.current_stream())
     e2e_step()
+    _lib.HOST_CLOCK = [0, 0]
     ms_e2e = timed(e2e_step, args.steps)
+    host_ns, host_calls = _lib.HOST_CLOCK
+    _lib.HOST_CLOCK = None
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- pack / unpack kernels against the HBM roofline (first half of the metric) -------------------
@@ -370,6 +373,11 @@ def run_b200(args):
         "peak_device_memory_GB": round(peak_mem / 1e9, 2),   # rank 0, device-resident leg (graph, features, training state)
         "kernel_ms_per_step": {k: round(v["ms"] / args.steps, 3) for k, v in sorted(ksum.items())},
         "library_gemm_calls_per_step": library_calls,
+        # host side of this library's calls during the end-to-end leg (rank 0): the binding plus the C entry point
+        # (argument checks, descriptor encoding, launch), not the device time
+        "host": {"calls_per_step": round(host_calls / args.steps, 1),
+                 "us_per_call": round(host_ns / max(host_calls, 1) / 1e3, 2),
+                 "ms_per_step": round(host_ns / args.steps / 1e6, 3)},
         "roofline": roofline, "kernels": kern, "cpu_baseline": cpu, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

@@ -4,6 +4,7 @@ There is no CPU or eager-PyTorch fallback: if the library is missing or a call f
 is raised.
 """
 import ctypes
+import time
 import os
 import threading
 
@@ -237,6 +238,7 @@ def poll_status(device=None):
 # ---- launch accounting and optional per-kernel CUDA-event timing ----------------------------------
 LAUNCHES = 0      # kernels of this library launched so far (each kernel-launching entry point = 1)
 TIMER = None      # a KernelTimer while a benchmark wants per-kernel device times
+HOST_CLOCK = None  # [ns, calls] while a benchmark wants the host time spent inside invoke() (binding + C entry point)
 
 
 LIBRARY_CALLS = {}   # name -> calls: dense work of the path handed to a library kernel (torch) instead of this library's
@@ -293,6 +295,7 @@ def invoke(name, nbytes, *args, device=None, **extra):
                          else torch.cuda.current_device()}
     dev = resolve_device(noted, torch.cuda.current_device())
     LAUNCHES += 1
+    t0 = time.perf_counter_ns() if HOST_CLOCK is not None else 0
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         args = tuple(stream if a is STREAM else a for a in args)
@@ -300,6 +303,9 @@ def invoke(name, nbytes, *args, device=None, **extra):
             rc = TIMER.bracket(name, nbytes, lambda: fn(*args), extra)
         else:
             rc = fn(*args)
+    if HOST_CLOCK is not None:
+        HOST_CLOCK[0] += time.perf_counter_ns() - t0
+        HOST_CLOCK[1] += 1
     check(rc, name)
     if name in STATUS_CALLS:
         STATUS_PENDING[dev] = True
